@@ -1,0 +1,556 @@
+"""ctypes binding of include/sdxlq.h plus the host-side mirror of the reference interface."""
+from __future__ import annotations
+
+import ctypes
+import enum
+import os
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from . import build as _build
+
+# --------------------------------------------------------------------------------------------
+# Enumerations: numeric values of the reference enums (tensor.hpp:17-48, ops.hpp:15).
+# --------------------------------------------------------------------------------------------
+
+
+class ScalarType(enum.IntEnum):
+    Float8E4M3 = 0
+    Float8E5M2 = 1
+    Int8 = 2
+    Float16 = 3
+    Float32 = 4
+    Int32 = 5
+
+
+class FP8ScaleMode(enum.IntEnum):
+    None_ = 0
+    TensorWide = 1
+    PerOutputChannel = 2
+
+
+class FP8StorageLayout(enum.IntEnum):
+    RowMajorNK = 0
+    KMajorKN = 1
+
+
+class LinearActivation(enum.IntEnum):
+    None_ = 0
+    SiLU = 1
+    GELU = 2
+    QuickGELU = 3
+    GEGLU = 4
+
+
+ACT_NONE, ACT_SILU, ACT_GELU, ACT_QUICK_GELU, ACT_GEGLU = 0, 1, 2, 3, 4
+
+STATUS_OK, STATUS_INVALID, STATUS_UNSUPPORTED, STATUS_TIMEOUT, STATUS_CUDA, STATUS_WORKSPACE = range(6)
+
+
+class CudaError(RuntimeError):
+    """The reference's sdxl::cuda::CudaError (include/sdxl/cuda/runtime.hpp:18-21)."""
+
+    def __init__(self, message: str, status: int = STATUS_INVALID):
+        super().__init__(message)
+        self.status = status
+
+
+# --------------------------------------------------------------------------------------------
+# C structures
+# --------------------------------------------------------------------------------------------
+
+
+class _CWeight(ctypes.Structure):
+    _fields_ = [
+        ("data", ctypes.c_void_p),
+        ("dtype", ctypes.c_int32),
+        ("layout", ctypes.c_int32),
+        ("n", ctypes.c_uint64),
+        ("k", ctypes.c_uint64),
+        ("scales", ctypes.c_void_p),
+        ("scale_count", ctypes.c_uint64),
+        ("scale_mode", ctypes.c_int32),
+        ("convrot_group_size", ctypes.c_uint32),
+    ]
+
+
+class _CLinearDesc(ctypes.Structure):
+    _fields_ = [
+        ("x", ctypes.c_void_p),
+        ("m", ctypes.c_uint64),
+        ("weight", _CWeight),
+        ("bias", ctypes.c_void_p),
+        ("activation", ctypes.c_int32),
+        ("reserved0", ctypes.c_int32),
+        ("y", ctypes.c_void_p),
+        ("xq", ctypes.c_void_p),
+        ("xq_scales", ctypes.c_void_p),
+        ("acc_out", ctypes.c_void_p),
+    ]
+
+
+class _CStats(ctypes.Structure):
+    _fields_ = [
+        ("linear_calls", ctypes.c_uint64),
+        ("tensor_core_calls", ctypes.c_uint64),
+        ("dp4a_fallback_calls", ctypes.c_uint64),
+        ("tensor_core_plan_misses", ctypes.c_uint64),
+        ("tensor_core_execution_failures", ctypes.c_uint64),
+    ]
+
+
+class _CKernelTimes(ctypes.Structure):
+    _fields_ = [("milliseconds", ctypes.c_double * 4), ("launches", ctypes.c_uint64 * 4)]
+
+
+KERNEL_CLASSES = ("quant_int8", "quant_fp8", "gemm", "small")
+
+EXPORTED_SYMBOLS = [
+    "sdxlq_context_create", "sdxlq_context_destroy", "sdxlq_context_set_stream", "sdxlq_context_check",
+    "sdxlq_last_error", "sdxlq_status_string", "sdxlq_get_stats", "sdxlq_linear", "sdxlq_linear_grouped",
+    "sdxlq_group_plan_create", "sdxlq_group_plan_run", "sdxlq_group_plan_destroy",
+    "sdxlq_group_plan_launches", "sdxlq_quantize_act_int8", "sdxlq_quantize_act_fp8",
+    "sdxlq_pack_weight_int8", "sdxlq_pack_weight_fp8", "sdxlq_valid_convrot_group_size",
+    "sdxlq_workspace_bytes", "sdxlq_build_info", "sdxlq_context_set_tile_n",
+    "sdxlq_selftest_bounded_wait", "sdxlq_profile_enable", "sdxlq_profile_read",
+]
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def library_path() -> str:
+    return _build.LIBRARY
+
+
+def load_library() -> ctypes.CDLL:
+    """Loads libsdxlq.so; fails loudly when it has not been built (there is no fallback)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not os.path.exists(path):
+        raise CudaError(f"{path} is missing: build it with `python -m` build step "
+                        "(__graft_entry__.build()); there is no CPU fallback", STATUS_CUDA)
+    lib = ctypes.CDLL(path)
+    vp, i32, u32, u64, sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_size_t
+    lib.sdxlq_context_create.argtypes = [ctypes.c_int, vp, sz, ctypes.POINTER(vp)]
+    lib.sdxlq_context_destroy.argtypes = [vp]
+    lib.sdxlq_context_destroy.restype = None
+    lib.sdxlq_context_set_stream.argtypes = [vp, vp]
+    lib.sdxlq_context_check.argtypes = [vp]
+    lib.sdxlq_last_error.argtypes = [vp]
+    lib.sdxlq_last_error.restype = ctypes.c_char_p
+    lib.sdxlq_status_string.argtypes = [ctypes.c_int]
+    lib.sdxlq_status_string.restype = ctypes.c_char_p
+    lib.sdxlq_get_stats.argtypes = [vp, ctypes.POINTER(_CStats)]
+    lib.sdxlq_linear.argtypes = [vp, ctypes.POINTER(_CLinearDesc)]
+    lib.sdxlq_linear_grouped.argtypes = [vp, ctypes.POINTER(_CLinearDesc), sz]
+    lib.sdxlq_group_plan_create.argtypes = [vp, ctypes.POINTER(_CLinearDesc), sz, ctypes.POINTER(vp)]
+    lib.sdxlq_group_plan_run.argtypes = [vp, vp]
+    lib.sdxlq_group_plan_destroy.argtypes = [vp]
+    lib.sdxlq_group_plan_destroy.restype = None
+    lib.sdxlq_group_plan_launches.argtypes = [vp]
+    lib.sdxlq_quantize_act_int8.argtypes = [vp, vp, i32, u64, u64, u32, vp, vp]
+    lib.sdxlq_quantize_act_fp8.argtypes = [vp, vp, u64, i32, vp, vp]
+    lib.sdxlq_pack_weight_int8.argtypes = [vp, vp, i32, u64, u64, u32, vp, vp]
+    lib.sdxlq_pack_weight_fp8.argtypes = [vp, vp, i32, u64, u64, i32, i32, i32, vp, vp]
+    lib.sdxlq_valid_convrot_group_size.argtypes = [sz]
+    lib.sdxlq_workspace_bytes.argtypes = [ctypes.POINTER(_CLinearDesc), sz]
+    lib.sdxlq_workspace_bytes.restype = sz
+    lib.sdxlq_build_info.restype = ctypes.c_char_p
+    lib.sdxlq_context_set_tile_n.argtypes = [vp, ctypes.c_int]
+    lib.sdxlq_selftest_bounded_wait.argtypes = [vp, ctypes.c_longlong]
+    lib.sdxlq_profile_enable.argtypes = [vp, ctypes.c_int]
+    lib.sdxlq_profile_read.argtypes = [vp, ctypes.POINTER(_CKernelTimes)]
+    _lib = lib
+    return lib
+
+
+def valid_convrot_group_size(group_size: int) -> bool:
+    """valid_convrot_group_size (src/cuda/int8_convrot.cu:489-496): power of four in 4..256."""
+    if group_size < 4 or group_size > 256:
+        return False
+    while group_size > 1:
+        if group_size % 4:
+            return False
+        group_size //= 4
+    return True
+
+
+# --------------------------------------------------------------------------------------------
+# Host-side mirror of the reference types
+# --------------------------------------------------------------------------------------------
+
+_TORCH_FP8 = {ScalarType.Float8E4M3: torch.float8_e4m3fn, ScalarType.Float8E5M2: torch.float8_e5m2}
+
+
+@dataclass
+class Weight:
+    """A packed projection weight: what the reference keeps on a weight ``cuda::Tensor``
+    (data, ScalarType, [N,K], dequant scale pointer/count/mode, FP8 layout, ConvRot group)."""
+
+    data: torch.Tensor                     # int8 / uint8 (FP8 bytes) / float16, logical [N, K]
+    type: ScalarType
+    n: int
+    k: int
+    scales: Optional[torch.Tensor] = None  # float32 [N] or [1]
+    scale_mode: FP8ScaleMode = FP8ScaleMode.None_
+    layout: FP8StorageLayout = FP8StorageLayout.RowMajorNK
+    convrot_group_size: int = 0
+
+    def has_dequant_scale(self) -> bool:
+        return self.scales is not None
+
+    def dequant_scale_count(self) -> int:
+        return 0 if self.scales is None else int(self.scales.numel())
+
+    def uses_convrot(self) -> bool:
+        return self.convrot_group_size != 0
+
+    def c_struct(self) -> _CWeight:
+        return _CWeight(
+            self.data.data_ptr(), int(self.type), int(self.layout), self.n, self.k,
+            self.scales.data_ptr() if self.scales is not None else None,
+            self.dequant_scale_count(), int(self.scale_mode), self.convrot_group_size)
+
+
+@dataclass
+class QuantizationMetadata:
+    """sdxl::QuantizationMetadata (include/sdxl/model.hpp:17-23) for a prequantised weight."""
+
+    weight_scale: Optional[torch.Tensor] = None
+    input_scale: Optional[torch.Tensor] = None
+    convrot: bool = False
+    per_row: bool = False
+    convrot_group_size: int = 0
+
+
+@dataclass
+class INT8WeightLoadOptions:
+    """sdxl::cuda::INT8WeightLoadOptions (include/sdxl/cuda/weights.hpp:54-66)."""
+
+    quantize_floating_weights: bool = True
+    require_prequantized: bool = False
+    strict: bool = False
+    require_tensor_cores: bool = False
+    enable_convrot: bool = True
+    convrot_group_size: int = 256
+
+
+@dataclass
+class FP8WeightLoadOptions:
+    """The fields of sdxl::cuda::FP8WeightLoadOptions (weights.hpp:45-51) that select kernels."""
+
+    format: ScalarType = ScalarType.Float8E4M3
+    scale_mode: FP8ScaleMode = FP8ScaleMode.TensorWide
+    preserve_native_fp8: bool = True
+    layout: FP8StorageLayout = FP8StorageLayout.RowMajorNK
+
+
+@dataclass
+class LinearCall:
+    """One projection of a grouped launch."""
+
+    x: Optional[torch.Tensor]
+    weight: Weight
+    bias: Optional[torch.Tensor] = None
+    activation: int = ACT_NONE
+    y: Optional[torch.Tensor] = None
+    xq: Optional[torch.Tensor] = None
+    xq_scales: Optional[torch.Tensor] = None
+    acc_out: Optional[torch.Tensor] = None
+    keep: list = field(default_factory=list)
+
+
+class Context:
+    """Owns an ``sdxlq_context``: device, stream and scratch workspace (the part of the
+    reference ``Runtime`` the operator needs, include/sdxl/cuda/runtime.hpp:120-163)."""
+
+    def __init__(self, device: int = 0, stream: Optional[torch.cuda.Stream] = None,
+                 workspace_bytes: int = 0):
+        self._lib = load_library()
+        self._handle = ctypes.c_void_p()
+        self.device = device
+        self.stream = stream
+        stream_ptr = ctypes.c_void_p(stream.cuda_stream) if stream is not None else \
+            ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        status = self._lib.sdxlq_context_create(device, stream_ptr, workspace_bytes, ctypes.byref(self._handle))
+        if status != STATUS_OK:
+            raise CudaError(f"sdxlq_context_create failed: {self._lib.sdxlq_status_string(status).decode()}", status)
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None) and self._handle.value:
+            self._lib.sdxlq_context_destroy(self._handle)
+            self._handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self) -> ctypes.c_void_p:
+        return self._handle
+
+    def raise_for(self, status: int) -> None:
+        if status != STATUS_OK:
+            raise CudaError(self._lib.sdxlq_last_error(self._handle).decode(), status)
+
+    def set_stream(self, stream: torch.cuda.Stream) -> None:
+        self.stream = stream
+        self.raise_for(self._lib.sdxlq_context_set_stream(self._handle, ctypes.c_void_p(stream.cuda_stream)))
+
+    def check(self) -> None:
+        """Synchronises and raises CudaError on a device-side timeout or CUDA error."""
+        self.raise_for(self._lib.sdxlq_context_check(self._handle))
+
+    def set_tile_n(self, tile_n: int) -> None:
+        self.raise_for(self._lib.sdxlq_context_set_tile_n(self._handle, tile_n))
+
+    def int8_execution_stats(self) -> dict:
+        stats = _CStats()
+        self.raise_for(self._lib.sdxlq_get_stats(self._handle, ctypes.byref(stats)))
+        return {name: int(getattr(stats, name)) for name, _ in _CStats._fields_}
+
+    def profile(self, enabled: bool) -> None:
+        """Turns per-kernel CUDA-event timing on or off."""
+        self.raise_for(self._lib.sdxlq_profile_enable(self._handle, int(enabled)))
+
+    def kernel_times(self) -> dict:
+        """{class: (milliseconds, launches)} since the last read; synchronises the stream."""
+        times = _CKernelTimes()
+        self.raise_for(self._lib.sdxlq_profile_read(self._handle, ctypes.byref(times)))
+        return {name: (float(times.milliseconds[i]), int(times.launches[i])) for i, name in enumerate(KERNEL_CLASSES)}
+
+    def selftest_bounded_wait(self, limit_cycles: int) -> None:
+        self.raise_for(self._lib.sdxlq_selftest_bounded_wait(self._handle, limit_cycles))
+
+
+def _ptr(tensor: Optional[torch.Tensor]):
+    return None if tensor is None else tensor.data_ptr()
+
+
+class Ops:
+    """The projection operators of sdxl::cuda::Ops (include/sdxl/cuda/ops.hpp:17-30)."""
+
+    def __init__(self, context: Context):
+        self.ctx = context
+        self._lib = context._lib
+
+    # -- descriptor ---------------------------------------------------------------------------
+    def _desc(self, call: LinearCall) -> _CLinearDesc:
+        weight = call.weight
+        x = call.x
+        if x is not None:
+            if x.dtype != torch.float16 or x.dim() < 2:
+                kind = "INT8" if weight.type == ScalarType.Int8 else "FP8 UNet" if weight.type in _TORCH_FP8 else "CUDA"
+                raise CudaError(f"{kind} linear requires FP16 model activations and a rank-2 weight")
+            if not x.is_contiguous():
+                raise CudaError("CUDA linear expects contiguous activations")
+            if x.shape[-1] != weight.k:
+                raise CudaError("CUDA linear feature mismatch")
+            m = x.numel() // weight.k
+            lead = tuple(x.shape[:-1])
+        else:
+            if call.xq is None:
+                raise CudaError("linear: no input")
+            m = call.xq.numel() // weight.k
+            lead = tuple(call.xq.shape[:-1])
+        if call.bias is not None:
+            if call.bias.dtype != torch.float16 or call.bias.dim() != 1 or call.bias.shape[0] != weight.n:
+                raise CudaError("CUDA linear bias mismatch")
+        n_out = weight.n // 2 if call.activation == ACT_GEGLU else weight.n
+        if call.y is None:
+            device = (x if x is not None else call.xq).device
+            call.y = torch.empty(lead + (n_out,), dtype=torch.float16, device=device)
+        return _CLinearDesc(_ptr(x), m, weight.c_struct(), _ptr(call.bias), int(call.activation), 0,
+                            _ptr(call.y), _ptr(call.xq), _ptr(call.xq_scales), _ptr(call.acc_out))
+
+    # -- Ops::linear / Ops::linear_activation ----------------------------------------------------
+    def linear(self, input: torch.Tensor, weight: Weight, bias: Optional[torch.Tensor] = None, *,
+               xq: Optional[torch.Tensor] = None, xq_scales: Optional[torch.Tensor] = None,
+               acc_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        call = LinearCall(input, weight, bias, ACT_NONE, out, xq, xq_scales, acc_out)
+        desc = self._desc(call)
+        self.ctx.raise_for(self._lib.sdxlq_linear(self.ctx.handle, ctypes.byref(desc)))
+        return call.y
+
+    def linear_activation(self, input: torch.Tensor, weight: Weight, bias: torch.Tensor,
+                          activation: int, *, xq: Optional[torch.Tensor] = None,
+                          xq_scales: Optional[torch.Tensor] = None,
+                          acc_out: Optional[torch.Tensor] = None,
+                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        call = LinearCall(input, weight, bias, int(activation), out, xq, xq_scales, acc_out)
+        desc = self._desc(call)
+        self.ctx.raise_for(self._lib.sdxlq_linear(self.ctx.handle, ctypes.byref(desc)))
+        return call.y
+
+    # -- grouped launches --------------------------------------------------------------------------
+    def _desc_array(self, calls: Sequence[LinearCall]):
+        array = (_CLinearDesc * len(calls))()
+        for i, call in enumerate(calls):
+            array[i] = self._desc(call)
+        return array
+
+    def linear_grouped(self, calls: Sequence[LinearCall]) -> list:
+        array = self._desc_array(calls)
+        self.ctx.raise_for(self._lib.sdxlq_linear_grouped(self.ctx.handle, array, len(calls)))
+        return [call.y for call in calls]
+
+    def plan(self, calls: Sequence[LinearCall]) -> "GroupPlan":
+        return GroupPlan(self, calls)
+
+    def workspace_bytes(self, calls: Sequence[LinearCall]) -> int:
+        array = self._desc_array(calls)
+        return int(self._lib.sdxlq_workspace_bytes(array, len(calls)))
+
+    # -- Ops::quantize_fp8 / quantize_e4m3 / quantize_e5m2 ------------------------------------------
+    def quantize_fp8(self, input: torch.Tensor, fp8_type: ScalarType) -> Weight:
+        """quantize_tensor_fp8 (src/cuda/fp8_kernels.cu:157-190). Returns the FP8 tensor with its
+        tensor-wide dequantisation scale attached, like the reference (a rank-2 result can be
+        used as a weight, as the reference's operator test does)."""
+        if input.dtype != torch.float16 or fp8_type not in _TORCH_FP8:
+            raise CudaError("FP8 activation quantization requires float16 input and an FP8 destination")
+        source = input.contiguous()
+        q = torch.empty(source.shape, dtype=torch.uint8, device=source.device)
+        scale = torch.empty(1, dtype=torch.float32, device=source.device)
+        self.ctx.raise_for(self._lib.sdxlq_quantize_act_fp8(
+            self.ctx.handle, source.data_ptr(), source.numel(), int(fp8_type), q.data_ptr(), scale.data_ptr()))
+        n = source.shape[0] if source.dim() == 2 else source.numel() // source.shape[-1]
+        return Weight(q, ScalarType(fp8_type), n, source.shape[-1], scale, FP8ScaleMode.TensorWide)
+
+    def quantize_e4m3(self, input: torch.Tensor) -> Weight:
+        return self.quantize_fp8(input, ScalarType.Float8E4M3)
+
+    def quantize_e5m2(self, input: torch.Tensor) -> Weight:
+        return self.quantize_fp8(input, ScalarType.Float8E5M2)
+
+    # -- activation quantiser of int8_convrot_linear -----------------------------------------------
+    def quantize_int8(self, input: torch.Tensor, convrot_group_size: int):
+        """The H1+H2 step of int8_convrot_linear (src/cuda/int8_convrot.cu:602-628) on its own:
+        returns (xq int8 [M,K], scales float32 [M])."""
+        if input.dtype not in (torch.float16, torch.float32) or input.dim() < 2:
+            raise CudaError("native INT8 linear received incompatible tensors")
+        source = input.contiguous()
+        k = source.shape[-1]
+        m = source.numel() // k
+        xq = torch.empty(source.shape, dtype=torch.int8, device=source.device)
+        scales = torch.empty(m, dtype=torch.float32, device=source.device)
+        dtype = ScalarType.Float16 if source.dtype == torch.float16 else ScalarType.Float32
+        self.ctx.raise_for(self._lib.sdxlq_quantize_act_int8(
+            self.ctx.handle, source.data_ptr(), int(dtype), m, k, convrot_group_size, xq.data_ptr(),
+            scales.data_ptr()))
+        return xq, scales
+
+    # -- load-time packers ------------------------------------------------------------------------
+    def upload_or_quantize_int8_weight(self, source: torch.Tensor,
+                                       metadata: Optional[QuantizationMetadata],
+                                       options: INT8WeightLoadOptions) -> Weight:
+        """upload_or_quantize_int8_weight (src/cuda/int8_convrot.cu:498-577) for a weight that is
+        already on the device: same option/metadata rules, same error messages."""
+        if source.dim() != 2:
+            raise CudaError("native INT8 weight must be rank 2")
+        rows, columns = int(source.shape[0]), int(source.shape[1])
+        if rows == 0 or columns == 0:
+            raise CudaError("native INT8 weight cannot be empty")
+        prequantized = source.dtype == torch.int8
+        if options.require_prequantized and not prequantized:
+            raise CudaError("INT8 prequantized-only profile received a floating-point linear weight")
+        if not prequantized and not options.quantize_floating_weights:
+            raise CudaError("on-the-fly INT8 quantization is disabled")
+        use_convrot = options.enable_convrot and options.convrot_group_size > 0 and \
+            columns % options.convrot_group_size == 0
+        group = options.convrot_group_size if use_convrot else 0
+        if prequantized:
+            if metadata is None or metadata.weight_scale is None:
+                raise CudaError("prequantized INT8 weight is missing weight_scale")
+            use_convrot = metadata.convrot
+            group = metadata.convrot_group_size if use_convrot else 0
+            if use_convrot and (not valid_convrot_group_size(group) or columns % group != 0):
+                raise CudaError("prequantized ConvRot metadata is incompatible with weight shape")
+            if metadata.weight_scale.numel() != rows:
+                raise CudaError("prequantized INT8 weight_scale is not per-output-row")
+        elif use_convrot and not valid_convrot_group_size(group):
+            raise CudaError("INT8 ConvRot group size must be a power of four between 4 and 256")
+        if not prequantized and source.dtype not in (torch.float16, torch.float32):
+            source = source.to(torch.float32)
+        source = source.contiguous()
+        weight = torch.empty((rows, columns), dtype=torch.int8, device=source.device)
+        if prequantized:
+            scales = metadata.weight_scale.to(device=source.device, dtype=torch.float32).reshape(rows).contiguous()
+            dtype = ScalarType.Int8
+        else:
+            scales = torch.empty(rows, dtype=torch.float32, device=source.device)
+            dtype = ScalarType.Float16 if source.dtype == torch.float16 else ScalarType.Float32
+        self.ctx.raise_for(self._lib.sdxlq_pack_weight_int8(
+            self.ctx.handle, source.data_ptr(), int(dtype), rows, columns, group, weight.data_ptr(),
+            scales.data_ptr()))
+        return Weight(weight, ScalarType.Int8, rows, columns, scales, FP8ScaleMode.PerOutputChannel,
+                      FP8StorageLayout.RowMajorNK, group if use_convrot else 0)
+
+    def upload_fp8_weight(self, source: torch.Tensor, options: FP8WeightLoadOptions) -> Weight:
+        """The FP8 branch of WeightStore::upload_tensor (src/cuda/weights.cu:301-415)."""
+        if options.format not in _TORCH_FP8:
+            raise CudaError("CUDA weight upload target must be FP8, float16, or float32")
+        if options.scale_mode == FP8ScaleMode.PerOutputChannel and source.dim() != 2:
+            raise CudaError("per-output-channel FP8 scaling requires a rank-2 matrix")
+        if source.dim() != 2:
+            raise CudaError("FP8 linear weights are rank 2")
+        rows, columns = int(source.shape[0]), int(source.shape[1])
+        if source.dtype == _TORCH_FP8[options.format] and options.preserve_native_fp8:
+            src_dtype = options.format
+            source = source.contiguous().view(torch.uint8)
+        elif source.dtype == torch.float16:
+            src_dtype = ScalarType.Float16
+        else:
+            source = source.to(torch.float32)
+            src_dtype = ScalarType.Float32
+        source = source.contiguous()
+        count = rows if options.scale_mode == FP8ScaleMode.PerOutputChannel else 1
+        shape = (columns, rows) if options.layout == FP8StorageLayout.KMajorKN else (rows, columns)
+        packed = torch.empty(shape, dtype=torch.uint8, device=source.device)
+        scales = torch.empty(count, dtype=torch.float32, device=source.device)
+        self.ctx.raise_for(self._lib.sdxlq_pack_weight_fp8(
+            self.ctx.handle, source.data_ptr(), int(src_dtype), rows, columns, int(options.format),
+            int(options.scale_mode), int(options.layout), packed.data_ptr(), scales.data_ptr()))
+        return Weight(packed, ScalarType(options.format), rows, columns, scales, options.scale_mode, options.layout)
+
+    @staticmethod
+    def fp16_weight(source: torch.Tensor) -> Weight:
+        source = source.to(torch.float16).contiguous()
+        return Weight(source, ScalarType.Float16, int(source.shape[0]), int(source.shape[1]))
+
+
+class GroupPlan:
+    """Build-once / run-many grouped launch (sdxlq_group_plan_*)."""
+
+    def __init__(self, ops: Ops, calls: Sequence[LinearCall]):
+        self.ops = ops
+        self.calls = list(calls)       # keeps every tensor alive for the plan's lifetime
+        self._lib = ops._lib
+        self._handle = ctypes.c_void_p()
+        array = ops._desc_array(self.calls)
+        ops.ctx.raise_for(self._lib.sdxlq_group_plan_create(ops.ctx.handle, array, len(self.calls),
+                                                            ctypes.byref(self._handle)))
+
+    @property
+    def launches(self) -> int:
+        return int(self._lib.sdxlq_group_plan_launches(self._handle))
+
+    def run(self) -> list:
+        self.ops.ctx.raise_for(self._lib.sdxlq_group_plan_run(self.ops.ctx.handle, self._handle))
+        return [call.y for call in self.calls]
+
+    def close(self) -> None:
+        if self._handle.value:
+            self._lib.sdxlq_group_plan_destroy(self._handle)
+            self._handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

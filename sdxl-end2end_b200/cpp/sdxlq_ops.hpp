@@ -1,0 +1,217 @@
+// C++20 host shim over the C ABI (include/sdxlq.h): the projection operators of the reference's
+// `sdxl::cuda::Ops` (include/sdxl/cuda/ops.hpp:17-30 of the reference) with the same names,
+// argument meaning and error behaviour, so that `Ops::linear` / `Ops::linear_activation`
+// (src/cuda/ops_blas.cpp:244-397) can forward here.
+//
+// Header-only. `TensorRef` carries exactly the fields the reference's `cuda::Tensor` exposes to
+// the operator (include/sdxl/cuda/tensor.hpp:99-157): data pointer, shape, ScalarType, TensorRole
+// and the quantisation metadata (dequant scale pointer / count / mode, FP8 storage layout,
+// ConvRot group size). It does not own memory: outputs come from the allocator the integrator
+// passes in (the reference's `Tensor::allocate` on the runtime arena).
+#pragma once
+
+#include "sdxlq.h"
+
+#include <cstddef>
+#include <cstdint>
+#include <functional>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+namespace sdxlq {
+
+// sdxl::cuda::CudaError (include/sdxl/cuda/runtime.hpp:18-21).
+class CudaError : public std::runtime_error {
+public:
+    explicit CudaError(const std::string& message, int status = SDXLQ_ERR_INVALID_ARGUMENT)
+        : std::runtime_error(message), status_(status) {}
+    [[nodiscard]] int status() const noexcept { return status_; }
+
+private:
+    int status_;
+};
+
+enum class ScalarType : std::uint8_t { Float8E4M3, Float8E5M2, Int8, Float16, Float32, Int32 };
+enum class TensorRole : std::uint8_t { Model, SamplerState, VAE, FP8ScaleMetadata, QuantizationMetadata, HostInterop };
+enum class FP8ScaleMode : std::uint8_t { None, TensorWide, PerOutputChannel };
+enum class FP8StorageLayout : std::uint8_t { RowMajorNK, KMajorKN };
+enum class LinearActivation : std::uint8_t { None, SiLU, GELU, QuickGELU, GEGLU };
+
+[[nodiscard]] inline bool is_fp8(ScalarType type) noexcept {
+    return type == ScalarType::Float8E4M3 || type == ScalarType::Float8E5M2;
+}
+
+[[nodiscard]] inline std::size_t scalar_size(ScalarType type) noexcept {
+    switch (type) {
+    case ScalarType::Float8E4M3:
+    case ScalarType::Float8E5M2:
+    case ScalarType::Int8: return 1;
+    case ScalarType::Float16: return 2;
+    default: return 4;
+    }
+}
+
+// valid_convrot_group_size (src/cuda/int8_convrot.cu:489-496).
+[[nodiscard]] inline bool valid_convrot_group_size(std::size_t group_size) noexcept {
+    return sdxlq_valid_convrot_group_size(group_size) != 0;
+}
+
+struct TensorRef {
+    void* data = nullptr;
+    std::vector<std::size_t> shape;
+    ScalarType type = ScalarType::Float16;
+    TensorRole role = TensorRole::Model;
+    const float* dequant_scale_data = nullptr;
+    std::size_t dequant_scale_count = 0;
+    FP8ScaleMode dequant_scale_mode = FP8ScaleMode::None;
+    FP8StorageLayout fp8_storage_layout = FP8StorageLayout::RowMajorNK;
+    std::size_t convrot_group_size = 0;
+
+    [[nodiscard]] bool defined() const noexcept { return data != nullptr; }
+    [[nodiscard]] std::size_t rank() const noexcept { return shape.size(); }
+    [[nodiscard]] std::size_t size(std::size_t dimension) const { return shape.at(dimension); }
+    [[nodiscard]] std::size_t elements() const noexcept {
+        std::size_t total = 1;
+        for (const std::size_t extent : shape) total *= extent;
+        return total;
+    }
+    [[nodiscard]] bool has_dequant_scale() const noexcept { return dequant_scale_data != nullptr; }
+};
+
+// sdxl::cuda::INT8ExecutionStats (include/sdxl/cuda/runtime.hpp:106-112).
+struct INT8ExecutionStats {
+    std::size_t linear_calls = 0;
+    std::size_t cublaslt_imma_calls = 0;       // tensor-core (tcgen05) calls here
+    std::size_t dp4a_fallback_calls = 0;
+    std::size_t tensor_core_plan_misses = 0;
+    std::size_t tensor_core_execution_failures = 0;
+};
+
+// The slice of sdxl::cuda::Runtime the operator needs: device, stream, scratch, counters.
+class Runtime final {
+public:
+    Runtime(int device, void* stream, std::size_t workspace_bytes = 0) {
+        const int status = sdxlq_context_create(device, stream, workspace_bytes, &context_);
+        if (status != SDXLQ_OK) throw CudaError(std::string("sdxlq_context_create: ") + sdxlq_status_string(status), status);
+    }
+    ~Runtime() { sdxlq_context_destroy(context_); }
+    Runtime(const Runtime&) = delete;
+    Runtime& operator=(const Runtime&) = delete;
+
+    [[nodiscard]] sdxlq_context* context() const noexcept { return context_; }
+    void synchronize() const { check(sdxlq_context_check(context_)); }
+    [[nodiscard]] INT8ExecutionStats int8_execution_stats() const {
+        sdxlq_int8_stats raw{};
+        check(sdxlq_get_stats(context_, &raw));
+        return INT8ExecutionStats{raw.linear_calls, raw.tensor_core_calls, raw.dp4a_fallback_calls,
+                                  raw.tensor_core_plan_misses, raw.tensor_core_execution_failures};
+    }
+    void check(int status) const {
+        if (status != SDXLQ_OK) throw CudaError(sdxlq_last_error(context_), status);
+    }
+
+private:
+    sdxlq_context* context_ = nullptr;
+};
+
+class Ops final {
+public:
+    // `allocate(bytes)` returns stream-ordered device memory for an output tensor.
+    using Allocator = std::function<void*(std::size_t)>;
+
+    Ops(const Runtime& runtime, Allocator allocate) : runtime_(&runtime), allocate_(std::move(allocate)) {}
+
+    // Ops::linear (src/cuda/ops_blas.cpp:244-386).
+    [[nodiscard]] TensorRef linear(const TensorRef& input, const TensorRef& weight,
+                                   const TensorRef* bias = nullptr) const {
+        return run(input, weight, bias, LinearActivation::None);
+    }
+
+    // Ops::linear_activation (src/cuda/ops_blas.cpp:388-397).
+    [[nodiscard]] TensorRef linear_activation(const TensorRef& input, const TensorRef& weight,
+                                              const TensorRef& bias, LinearActivation activation) const {
+        return run(input, weight, &bias, activation);
+    }
+
+    // Ops::quantize_fp8 / quantize_e4m3 / quantize_e5m2 (src/cuda/ops_blas.cpp:231-242).
+    [[nodiscard]] TensorRef quantize_fp8(const TensorRef& input, ScalarType fp8_type) const {
+        if (input.type != ScalarType::Float16 || !is_fp8(fp8_type)) {
+            throw CudaError("FP8 activation quantization requires float16 input and an FP8 destination");
+        }
+        TensorRef destination;
+        destination.shape = input.shape;
+        destination.type = fp8_type;
+        destination.role = TensorRole::Model;
+        destination.data = allocate_(input.elements());
+        float* scale = static_cast<float*>(allocate_(sizeof(float)));
+        runtime_->check(sdxlq_quantize_act_fp8(runtime_->context(), input.data, input.elements(),
+                                               static_cast<std::int32_t>(fp8_type),
+                                               static_cast<std::uint8_t*>(destination.data), scale));
+        destination.dequant_scale_data = scale;
+        destination.dequant_scale_count = 1;
+        destination.dequant_scale_mode = FP8ScaleMode::TensorWide;
+        return destination;
+    }
+    [[nodiscard]] TensorRef quantize_e4m3(const TensorRef& input) const { return quantize_fp8(input, ScalarType::Float8E4M3); }
+    [[nodiscard]] TensorRef quantize_e5m2(const TensorRef& input) const { return quantize_fp8(input, ScalarType::Float8E5M2); }
+
+private:
+    [[nodiscard]] TensorRef run(const TensorRef& input, const TensorRef& weight, const TensorRef* bias,
+                                LinearActivation activation) const {
+        // The type / role / rank checks of Ops::linear, with its messages.
+        if (weight.type == ScalarType::Int8) {
+            if (input.type != ScalarType::Float16 || input.role != TensorRole::Model || input.rank() < 2 ||
+                weight.rank() != 2) {
+                throw CudaError("INT8 linear requires FP16/FP32 model activations and a rank-2 INT8 weight");
+            }
+        } else if (is_fp8(weight.type)) {
+            if (input.type != ScalarType::Float16 || input.role != TensorRole::Model || input.rank() < 2 ||
+                weight.rank() != 2) {
+                throw CudaError("FP8 UNet linear requires FP16 model activations and a rank-2 FP8 weight");
+            }
+        } else if (input.type != ScalarType::Float16 || weight.type != input.type || weight.role != input.role) {
+            throw CudaError("CUDA linear expects matching FP16/FP32 tensors and roles, or FP8 weights");
+        }
+        if (input.rank() < 2 || weight.rank() != 2) throw CudaError("CUDA linear rank mismatch");
+        const std::size_t k = input.shape.back();
+        const std::size_t n = weight.size(0);
+        if (weight.size(1) != k) throw CudaError("CUDA linear feature mismatch");
+        if (bias != nullptr && (bias->type != ScalarType::Float16 || bias->role != input.role ||
+                                bias->rank() != 1 || bias->size(0) != n)) {
+            throw CudaError("CUDA linear bias mismatch");
+        }
+        const std::size_t m = input.elements() / k;
+
+        TensorRef output;
+        output.shape = input.shape;
+        output.shape.back() = activation == LinearActivation::GEGLU ? n / 2 : n;
+        output.type = ScalarType::Float16;
+        output.role = input.role;
+        output.data = allocate_(output.elements() * sizeof(std::uint16_t));
+
+        sdxlq_linear_desc desc{};
+        desc.x = input.data;
+        desc.m = m;
+        desc.weight.data = weight.data;
+        desc.weight.dtype = static_cast<std::int32_t>(weight.type);
+        desc.weight.layout = static_cast<std::int32_t>(weight.fp8_storage_layout);
+        desc.weight.n = n;
+        desc.weight.k = k;
+        desc.weight.scales = weight.dequant_scale_data;
+        desc.weight.scale_count = weight.dequant_scale_count;
+        desc.weight.scale_mode = static_cast<std::int32_t>(weight.dequant_scale_mode);
+        desc.weight.convrot_group_size = static_cast<std::uint32_t>(weight.convrot_group_size);
+        desc.bias = bias != nullptr ? bias->data : nullptr;
+        desc.activation = static_cast<std::int32_t>(activation);
+        desc.y = output.data;
+        runtime_->check(sdxlq_linear(runtime_->context(), &desc));
+        return output;
+    }
+
+    const Runtime* runtime_ = nullptr;
+    Allocator allocate_;
+};
+
+}  // namespace sdxlq

@@ -1,0 +1,864 @@
+// C ABI of the quantized-Linear operator: validation, dispatch, tensor-map encoding, grouped
+// plans. Mirrors the host logic of Ops::linear / Ops::linear_activation
+// (src/cuda/ops_blas.cpp:244-397 of the reference), int8_convrot_linear
+// (src/cuda/int8_convrot.cu:579-751) and native_fp8_linear (ops_blas.cpp:153-225); where the
+// reference throws CudaError this layer returns a status code and records a message.
+
+#include "../../include/sdxlq.h"
+
+#include "internal.cuh"
+#include "quantize.cuh"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <new>
+#include <string>
+#include <tuple>
+#include <vector>
+
+namespace sdxlq {
+cudaError_t launch_umma_gemm(const GemmLaunchParams& params, uint32_t grid, size_t dynamic_smem,
+                             cudaStream_t stream, size_t* attribute_bytes);
+cudaError_t launch_small_linear(const void* a, const void* b, const EpilogueParams& ep, uint32_t k_major,
+                                cudaStream_t stream);
+cudaError_t launch_bounded_wait_probe(uint32_t* error_word, long long limit_cycles, cudaStream_t stream);
+}  // namespace sdxlq
+
+using namespace sdxlq;
+
+namespace {
+
+constexpr size_t kDefaultWorkspace = size_t(256) << 20;
+constexpr uint32_t kMaxFp8Jobs = 4096;
+constexpr size_t kSmemLimit = 232448;      // 227 KiB opt-in shared memory per CTA on sm_100
+constexpr size_t kControlBytes = 5120;     // barriers, staged column operands, alignment slack
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+size_t align_up(size_t value, size_t alignment) { return (value + alignment - 1) / alignment * alignment; }
+
+}  // namespace
+
+struct sdxlq_context {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    uint8_t* workspace = nullptr;
+    size_t workspace_bytes = 0;
+    uint32_t* control = nullptr;           // [0] error word, then 2 x kMaxFp8Jobs amax words
+    uint32_t fp8_parity = 0;
+    uint32_t fp8_dirty[2] = {0, 0};        // amax words of each parity left non-zero
+    int sm_count = 148;
+    size_t umma_smem_attribute = 0;
+    long long wait_limit_cycles = 4000000000LL;
+    int forced_tile_n = 0;
+    EncodeTiledFn encode = nullptr;
+    sdxlq_int8_stats stats{};
+    std::string last_error = "";
+    // Optional per-kernel timing: CUDA event pairs recorded around each launch on the stream.
+    bool profiling = false;
+    struct TimedLaunch { int kernel_class; cudaEvent_t start; cudaEvent_t stop; };
+    std::vector<TimedLaunch> timed;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> event_pool;
+};
+
+namespace {
+
+// Records an event pair around the launches issued while it is alive (profiling mode only).
+class LaunchTimer {
+public:
+    LaunchTimer(sdxlq_context* ctx, int kernel_class) : ctx_(ctx) {
+        if (!ctx_->profiling) return;
+        std::pair<cudaEvent_t, cudaEvent_t> events{nullptr, nullptr};
+        if (!ctx_->event_pool.empty()) {
+            events = ctx_->event_pool.back();
+            ctx_->event_pool.pop_back();
+        } else if (cudaEventCreate(&events.first) != cudaSuccess || cudaEventCreate(&events.second) != cudaSuccess) {
+            return;
+        }
+        entry_ = {kernel_class, events.first, events.second};
+        active_ = cudaEventRecord(entry_.start, ctx_->stream) == cudaSuccess;
+    }
+    ~LaunchTimer() {
+        if (!active_) return;
+        cudaEventRecord(entry_.stop, ctx_->stream);
+        ctx_->timed.push_back(entry_);
+    }
+    LaunchTimer(const LaunchTimer&) = delete;
+    LaunchTimer& operator=(const LaunchTimer&) = delete;
+
+private:
+    sdxlq_context* ctx_;
+    sdxlq_context::TimedLaunch entry_{};
+    bool active_ = false;
+};
+
+int fail(sdxlq_context* ctx, int status, const std::string& message) {
+    if (ctx != nullptr) ctx->last_error = message;
+    return status;
+}
+
+int fail_cuda(sdxlq_context* ctx, cudaError_t error, const char* where) {
+    return fail(ctx, SDXLQ_ERR_CUDA, std::string(where) + ": " + cudaGetErrorString(error));
+}
+
+bool is_fp8(int32_t dtype) { return dtype == SDXLQ_FP8_E4M3 || dtype == SDXLQ_FP8_E5M2; }
+
+bool valid_group(size_t group_size) {
+    if (group_size < 4 || group_size > 256) return false;
+    while (group_size > 1) {
+        if (group_size % 4 != 0) return false;
+        group_size /= 4;
+    }
+    return true;
+}
+
+uint32_t group_stages(uint32_t group_size) {
+    uint32_t stages = 0;
+    while (group_size > 1) { group_size /= 4; ++stages; }
+    return stages;
+}
+
+// ---- validation: the checks of Ops::linear, int8_convrot_linear, fp8_weight_only_linear ----
+int validate(sdxlq_context* ctx, const sdxlq_linear_desc& d) {
+    const sdxlq_weight& w = d.weight;
+    if (w.data == nullptr || d.y == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: null weight or output pointer");
+    if (d.x == nullptr && d.xq == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: null input pointer");
+    if (w.n == 0 || w.k == 0) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: empty weight");
+    if (d.m > 0x7FFFFFFFull || w.n > 0x7FFFFFFFull || w.k > 0x7FFFFFFFull) {
+        return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE, "linear dimensions exceed kernel integer range");
+    }
+    if (d.activation < SDXLQ_ACT_NONE || d.activation > SDXLQ_ACT_GEGLU) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: unknown activation");
+    }
+    if (d.activation != SDXLQ_ACT_NONE && d.bias == nullptr) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "fused linear bias activation requires a bias");
+    }
+    if (d.activation == SDXLQ_ACT_GEGLU && w.n % 2 != 0) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "fused linear bias GEGLU requires matching even-width FP16 tensors");
+    }
+    if (w.dtype == SDXLQ_INT8) {
+        if (w.scales == nullptr || w.scale_mode != SDXLQ_SCALE_PER_OUTPUT_CHANNEL) {
+            return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "native INT8 linear received incompatible tensors");
+        }
+        if (w.scale_count != w.n) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "native INT8 linear feature or scale mismatch");
+        if (w.convrot_group_size != 0 && (!valid_group(w.convrot_group_size) || w.k % w.convrot_group_size != 0)) {
+            return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "native INT8 linear has invalid ConvRot group metadata");
+        }
+        if (w.k % 4 != 0) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "native INT8 Tensor Core linear requires K divisible by 4");
+        if (w.layout != SDXLQ_ROW_MAJOR_NK) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "INT8 weights are row-major [N,K]");
+        if (d.xq != nullptr && d.xq_scales == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: xq without xq_scales");
+    } else if (is_fp8(w.dtype)) {
+        if (w.scales == nullptr || (w.scale_count != 1 && w.scale_count != w.n)) {
+            return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "FP8 weight has invalid scaling metadata");
+        }
+        if (w.scale_mode != SDXLQ_SCALE_TENSOR_WIDE && w.scale_mode != SDXLQ_SCALE_PER_OUTPUT_CHANNEL) {
+            return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "FP8 weight has invalid scaling metadata");
+        }
+        if (w.layout != SDXLQ_ROW_MAJOR_NK && w.layout != SDXLQ_K_MAJOR_KN) {
+            return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "FP8 weight has an unknown storage layout");
+        }
+        if (d.xq != nullptr && d.xq_scales == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: xq without xq_scales");
+        if (d.acc_out != nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "acc_out is only defined for INT8 weights");
+    } else if (w.dtype == SDXLQ_FP16) {
+        if (w.layout != SDXLQ_ROW_MAJOR_NK) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "FP16 weights are row-major [N,K]");
+        if (d.x == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: null input pointer");
+        if (d.acc_out != nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "acc_out is only defined for INT8 weights");
+    } else {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "CUDA linear expects INT8, FP8 or FP16 weights");
+    }
+    return SDXLQ_OK;
+}
+
+// ---- tile shape ------------------------------------------------------------------------------
+uint32_t choose_tile_n(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool geglu) {
+    const uint32_t step = geglu ? 32 : 16;
+    if (ctx->forced_tile_n >= 16) {
+        uint32_t forced = std::min<uint32_t>(kMaxTileN, static_cast<uint32_t>(ctx->forced_tile_n));
+        return std::max(step, forced / step * step);
+    }
+    const uint32_t tiles_m = (m + kTileM - 1) / kTileM;
+    const uint32_t sms = static_cast<uint32_t>(ctx->sm_count);
+    uint32_t best = step;
+    double best_cost = 1e300;
+    for (uint32_t tile_n = kMaxTileN; tile_n >= step; tile_n -= step) {
+        // GEGLU: a tile holds tile_n/2 value columns and tile_n/2 gate columns.
+        const uint32_t columns = geglu ? n / 2 : n;
+        const uint32_t per_tile = geglu ? tile_n / 2 : tile_n;
+        const uint32_t tiles_n = (columns + per_tile - 1) / per_tile;
+        const uint64_t tiles = static_cast<uint64_t>(tiles_m) * tiles_n;
+        const uint64_t waves = (tiles + sms - 1) / sms;
+        const double cost = static_cast<double>(waves) * (tile_n + 32.0);
+        if (cost < best_cost) { best_cost = cost; best = tile_n; }
+        if (tile_n == step) break;
+    }
+    return best;
+}
+
+CUtensorMapDataType tensor_map_type(uint32_t kind) {
+    return kind == KIND_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+}
+
+bool encode_operand(const sdxlq_context* ctx, CUtensorMap* map, uint32_t kind, const void* pointer,
+                    uint64_t rows, uint64_t k, uint32_t box_rows) {
+    const uint64_t element = kind == KIND_F16 ? 2 : 1;
+    const cuuint64_t dims[2] = {k, rows};
+    const cuuint64_t strides[1] = {k * element};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileKBytes / element), box_rows};
+    const cuuint32_t element_strides[2] = {1, 1};
+    const CUresult result = ctx->encode(map, tensor_map_type(kind), 2, const_cast<void*>(pointer), dims, strides,
+                                        box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return result == CUDA_SUCCESS;
+}
+
+// ---- a prepared set of projections -------------------------------------------------------------
+struct SmallCall {
+    const void* a;
+    const void* b;
+    EpilogueParams ep;
+    uint32_t k_major;
+};
+
+struct Prepared {
+    std::vector<QuantInt8Job> int8_jobs;
+    std::vector<QuantFp8Job> fp8_jobs;
+    std::vector<GemmProblem> problems;
+    std::vector<TileRef> tiles;
+    std::vector<SmallCall> small;
+    uint32_t int8_blocks = 0;
+    uint32_t int8_threads = 256;
+    uint32_t fp8_blocks = 0;
+    uint32_t max_tile_n = 0;
+    uint32_t int8_linears = 0;
+    uint32_t int8_small = 0;
+    size_t scratch_bytes = 0;
+};
+
+using QuantKey = std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>;
+
+uint32_t best_int8_block(uint32_t threads_per_row) {
+    uint32_t best = 256;
+    double best_use = -1.0;
+    for (uint32_t threads = 128; threads <= 256; threads += 32) {
+        const uint32_t rows = threads / threads_per_row;
+        if (rows == 0) continue;
+        const double use = static_cast<double>(rows * threads_per_row) / threads;
+        if (use > best_use + 1e-9) { best_use = use; best = threads; }
+    }
+    return best;
+}
+
+int add_int8_job(sdxlq_context* ctx, Prepared& prep, const void* x, bool x_is_f32, uint64_t m, uint64_t k,
+                 uint32_t group, int8_t* xq, float* scales, bool grouped) {
+    QuantInt8Job job{};
+    job.x = x;
+    job.xq = xq;
+    job.scales = scales;
+    job.m = static_cast<uint32_t>(m);
+    job.k = static_cast<uint32_t>(k);
+    job.stages = group_stages(group);
+    job.threads_per_row = 4 * static_cast<uint32_t>((k + 255) / 256);
+    if (job.threads_per_row > 256) return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE, "INT8 activation rows longer than 16384 are not supported");
+    const uint32_t threads = grouped ? 256 : best_int8_block(job.threads_per_row);
+    if (!grouped) prep.int8_threads = threads;
+    job.rows_per_block = threads / job.threads_per_row;
+    job.x_is_f32 = x_is_f32 ? 1 : 0;
+    const size_t element = x_is_f32 ? 4 : 2;
+    job.vector_ok = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && ((k * element) % 16 == 0) &&
+                    (reinterpret_cast<uintptr_t>(xq) % 8 == 0) && (k % 8 == 0);
+    job.first_block = prep.int8_blocks;
+    job.num_blocks = static_cast<uint32_t>((m + job.rows_per_block - 1) / job.rows_per_block);
+    prep.int8_blocks += job.num_blocks;
+    prep.int8_jobs.push_back(job);
+    return SDXLQ_OK;
+}
+
+void add_fp8_job(Prepared& prep, const void* x, uint64_t count, uint32_t fmt, uint8_t* q, float* scale_out) {
+    QuantFp8Job job{};
+    job.x = x;
+    job.q = q;
+    job.scale_out = scale_out;
+    job.count = count;
+    job.fmt = fmt;
+    job.vector_ok = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(q) % 8 == 0);
+    job.first_block = prep.fp8_blocks;
+    const uint64_t wanted = (count + 8191) / 8192;
+    job.num_blocks = static_cast<uint32_t>(std::max<uint64_t>(1, std::min<uint64_t>(1184, wanted)));
+    prep.fp8_blocks += job.num_blocks;
+    prep.fp8_jobs.push_back(job);
+}
+
+int prepare(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count, bool grouped, Prepared& prep) {
+    std::map<QuantKey, std::pair<const void*, const float*>> shared_inputs;
+    size_t scratch = 0;
+    for (size_t index = 0; index < count; ++index) {
+        const sdxlq_linear_desc& d = descs[index];
+        const int status = validate(ctx, d);
+        if (status != SDXLQ_OK) return status;
+        if (d.m == 0) continue;
+        const sdxlq_weight& w = d.weight;
+        const uint32_t kind = w.dtype == SDXLQ_INT8 ? KIND_I8
+                              : w.dtype == SDXLQ_FP8_E4M3 ? KIND_E4M3
+                              : w.dtype == SDXLQ_FP8_E5M2 ? KIND_E5M2 : KIND_F16;
+        const void* a = d.x;
+        const float* a_scales = nullptr;
+        if (kind == KIND_I8 || kind == KIND_E4M3 || kind == KIND_E5M2) {
+            if (d.xq != nullptr) {
+                a = d.xq;
+                a_scales = d.xq_scales;
+            } else {
+                const uint32_t tag = kind == KIND_I8 ? w.convrot_group_size : 0;
+                const QuantKey key{d.x, d.m, w.k, kind, tag};
+                auto found = shared_inputs.find(key);
+                if (found == shared_inputs.end()) {
+                    const size_t q_offset = align_up(scratch, 256);
+                    const size_t q_bytes = static_cast<size_t>(d.m) * w.k;
+                    const size_t s_offset = align_up(q_offset + q_bytes, 256);
+                    const size_t s_bytes = kind == KIND_I8 ? static_cast<size_t>(d.m) * sizeof(float) : sizeof(float);
+                    scratch = s_offset + s_bytes;
+                    if (scratch > ctx->workspace_bytes) {
+                        return fail(ctx, SDXLQ_ERR_WORKSPACE, "workspace too small for the quantised activations");
+                    }
+                    uint8_t* q = ctx->workspace + q_offset;
+                    float* s = reinterpret_cast<float*>(ctx->workspace + s_offset);
+                    if (kind == KIND_I8) {
+                        const int job_status = add_int8_job(ctx, prep, d.x, false, d.m, w.k, w.convrot_group_size,
+                                                            reinterpret_cast<int8_t*>(q), s, grouped);
+                        if (job_status != SDXLQ_OK) return job_status;
+                    } else {
+                        if (prep.fp8_jobs.size() >= kMaxFp8Jobs) {
+                            return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE, "too many distinct FP8 inputs in one grouped call");
+                        }
+                        add_fp8_job(prep, d.x, static_cast<uint64_t>(d.m) * w.k, kind == KIND_E4M3 ? 0 : 1, q, s);
+                    }
+                    found = shared_inputs.emplace(key, std::make_pair(static_cast<const void*>(q), static_cast<const float*>(s))).first;
+                }
+                a = found->second.first;
+                a_scales = found->second.second;
+            }
+        }
+
+        EpilogueParams ep{};
+        ep.y = static_cast<__half*>(d.y);
+        ep.acc_out = d.acc_out;
+        ep.a_scales = a_scales;
+        ep.w_scales = w.scales;
+        ep.bias = static_cast<const __half*>(d.bias);
+        ep.m = static_cast<uint32_t>(d.m);
+        ep.n = static_cast<uint32_t>(w.n);
+        ep.k = static_cast<uint32_t>(w.k);
+        const bool geglu = d.activation == SDXLQ_ACT_GEGLU;
+        ep.n_out = geglu ? ep.n / 2 : ep.n;
+        ep.kind = kind;
+        ep.activation = static_cast<uint32_t>(d.activation);
+        ep.w_scale_per_channel = (kind != KIND_F16 && w.scale_count != 1) ? 1 : 0;
+        ep.vector_store_ok = (reinterpret_cast<uintptr_t>(d.y) % 16 == 0) && (ep.n_out % 8 == 0);
+        ep.vector_meta_ok = (reinterpret_cast<uintptr_t>(w.scales) % 16 == 0) &&
+                            (reinterpret_cast<uintptr_t>(d.bias) % 16 == 0) &&
+                            (!geglu || ep.n_out % 8 == 0);
+
+        const uint64_t element = kind == KIND_F16 ? 2 : 1;
+        const bool tma_ok = w.layout == SDXLQ_ROW_MAJOR_NK && (w.k * element) % 16 == 0 &&
+                            reinterpret_cast<uintptr_t>(a) % 16 == 0 &&
+                            reinterpret_cast<uintptr_t>(w.data) % 16 == 0;
+        if (kind == KIND_I8) ++prep.int8_linears;
+        if (!tma_ok) {
+            if (kind == KIND_I8) ++prep.int8_small;
+            prep.small.push_back(SmallCall{a, w.data, ep, w.layout == SDXLQ_K_MAJOR_KN ? 1u : 0u});
+            continue;
+        }
+
+        GemmProblem problem{};
+        problem.ep = ep;
+        problem.tile_n = choose_tile_n(ctx, ep.m, ep.n, geglu);
+        const uint32_t per_tile = geglu ? problem.tile_n / 2 : problem.tile_n;
+        problem.tiles_m = (ep.m + kTileM - 1) / kTileM;
+        problem.tiles_n = (ep.n_out + per_tile - 1) / per_tile;
+        problem.k_blocks = static_cast<uint32_t>((w.k * element + kTileKBytes - 1) / kTileKBytes);
+        const uint32_t format = kind == KIND_I8 ? 1u : (kind == KIND_E5M2 ? 1u : 0u);
+        // c_format: 2 = S32 for kind::i8, 1 = F32 otherwise; operands K-major; M = 128.
+        problem.idesc = ((kind == KIND_I8 ? 2u : 1u) << 4) | (format << 7) | (format << 10) |
+                        ((problem.tile_n >> 3) << 17) | ((kTileM >> 4) << 24);
+        if (!encode_operand(ctx, &problem.tmap_a, kind, a, ep.m, w.k, kTileM) ||
+            !encode_operand(ctx, &problem.tmap_b, kind, w.data, w.n, w.k, per_tile)) {
+            return fail(ctx, SDXLQ_ERR_CUDA, "cuTensorMapEncodeTiled rejected an operand");
+        }
+        prep.max_tile_n = std::max(prep.max_tile_n, problem.tile_n);
+        const uint32_t problem_index = static_cast<uint32_t>(prep.problems.size());
+        prep.problems.push_back(problem);
+        if (grouped) {
+            // n-major inside an m-tile keeps the CTAs of one wave on the same weight rows.
+            for (uint32_t tn = 0; tn < problem.tiles_n; ++tn) {
+                for (uint32_t tm = 0; tm < problem.tiles_m; ++tm) {
+                    prep.tiles.push_back(TileRef{problem_index, static_cast<uint16_t>(tm), static_cast<uint16_t>(tn)});
+                }
+            }
+        }
+    }
+    if (grouped && prep.problems.size() > 1) {
+        // Longest tiles first so that the round-robin walk of the persistent CTAs ends evenly.
+        std::stable_sort(prep.tiles.begin(), prep.tiles.end(), [&](const TileRef& l, const TileRef& r) {
+            const GemmProblem& pl = prep.problems[l.problem];
+            const GemmProblem& pr = prep.problems[r.problem];
+            return static_cast<uint64_t>(pl.k_blocks) * (pl.tile_n + 128) > static_cast<uint64_t>(pr.k_blocks) * (pr.tile_n + 128);
+        });
+    }
+    prep.scratch_bytes = scratch;
+    return SDXLQ_OK;
+}
+
+struct GemmGeometry {
+    uint32_t stage_bytes;
+    uint32_t num_stages;
+    size_t dynamic_smem;
+};
+
+GemmGeometry gemm_geometry(uint32_t max_tile_n) {
+    GemmGeometry g{};
+    g.stage_bytes = (kTileM + max_tile_n) * kTileKBytes;
+    g.num_stages = static_cast<uint32_t>(std::min<size_t>(8, (kSmemLimit - kControlBytes) / g.stage_bytes));
+    g.dynamic_smem = kControlBytes + static_cast<size_t>(g.num_stages) * g.stage_bytes;
+    return g;
+}
+
+// Picks the amax scratch words of this call's parity and returns the launch header. The words
+// of one parity are all zero when a call starts: the cast kernel of the following call (other
+// parity) clears them again.
+QuantFp8Launch bind_fp8(sdxlq_context* ctx, const std::vector<QuantFp8Job>& jobs, const QuantFp8Job* device_jobs) {
+    const uint32_t parity = ctx->fp8_parity;
+    QuantFp8Launch launch{};
+    launch.amax_bits = ctx->control + 64 + parity * kMaxFp8Jobs;
+    launch.jobs = device_jobs;
+    launch.num_jobs = static_cast<uint32_t>(jobs.size());
+    launch.clear_bits = ctx->control + 64 + (parity ^ 1u) * kMaxFp8Jobs;
+    launch.clear_count = ctx->fp8_dirty[parity ^ 1u];
+    if (!jobs.empty()) launch.single = jobs[0];
+    ctx->fp8_dirty[parity ^ 1u] = 0;
+    ctx->fp8_dirty[parity] = static_cast<uint32_t>(jobs.size());
+    ctx->fp8_parity = parity ^ 1u;
+    return launch;
+}
+
+int run_small(sdxlq_context* ctx, const Prepared& prep) {
+    for (const SmallCall& call : prep.small) {
+        LaunchTimer timer(ctx, SDXLQ_KERNEL_SMALL);
+        const cudaError_t status = launch_small_linear(call.a, call.b, call.ep, call.k_major, ctx->stream);
+        if (status != cudaSuccess) return fail_cuda(ctx, status, "small linear launch");
+    }
+    return SDXLQ_OK;
+}
+
+void count_stats(sdxlq_context* ctx, const Prepared& prep) {
+    ctx->stats.linear_calls += prep.int8_linears;
+    ctx->stats.tensor_core_calls += prep.int8_linears - prep.int8_small;
+    ctx->stats.dp4a_fallback_calls += prep.int8_small;
+}
+
+}  // namespace
+
+struct sdxlq_group_plan {
+    Prepared prep;
+    GemmProblem* device_problems = nullptr;
+    TileRef* device_tiles = nullptr;
+    QuantInt8Job* device_int8_jobs = nullptr;
+    QuantFp8Job* device_fp8_jobs = nullptr;
+    int device = 0;
+};
+
+extern "C" {
+
+int sdxlq_context_create(int device, void* stream, size_t workspace_bytes, sdxlq_context** out) {
+    if (out == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    cudaError_t status = cudaSetDevice(device);
+    if (status != cudaSuccess) return SDXLQ_ERR_CUDA;
+    cudaDeviceProp properties{};
+    status = cudaGetDeviceProperties(&properties, device);
+    if (status != cudaSuccess) return SDXLQ_ERR_CUDA;
+    if (properties.major != 10) return SDXLQ_ERR_UNSUPPORTED_SHAPE;   // sm_100a kernels only
+    sdxlq_context* ctx = new (std::nothrow) sdxlq_context();
+    if (ctx == nullptr) return SDXLQ_ERR_CUDA;
+    ctx->device = device;
+    ctx->stream = static_cast<cudaStream_t>(stream);
+    ctx->sm_count = properties.multiProcessorCount;
+    ctx->workspace_bytes = workspace_bytes == 0 ? kDefaultWorkspace : workspace_bytes;
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult query{};
+    status = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &query);
+    if (status != cudaSuccess || entry == nullptr) { delete ctx; return SDXLQ_ERR_CUDA; }
+    ctx->encode = reinterpret_cast<EncodeTiledFn>(entry);
+    if (cudaMalloc(&ctx->workspace, ctx->workspace_bytes) != cudaSuccess) { delete ctx; return SDXLQ_ERR_WORKSPACE; }
+    const size_t control_bytes = (64 + 2 * kMaxFp8Jobs) * sizeof(uint32_t);
+    if (cudaMalloc(&ctx->control, control_bytes) != cudaSuccess ||
+        cudaMemset(ctx->control, 0, control_bytes) != cudaSuccess) {
+        cudaFree(ctx->workspace);
+        cudaFree(ctx->control);
+        delete ctx;
+        return SDXLQ_ERR_CUDA;
+    }
+    if (const char* text = std::getenv("SDXLQ_WAIT_LIMIT_CYCLES")) {
+        const long long parsed = std::atoll(text);
+        if (parsed > 0) ctx->wait_limit_cycles = parsed;
+    }
+    if (const char* text = std::getenv("SDXLQ_TILE_N")) ctx->forced_tile_n = std::atoi(text);
+    *out = ctx;
+    return SDXLQ_OK;
+}
+
+void sdxlq_context_destroy(sdxlq_context* ctx) {
+    if (ctx == nullptr) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (auto& entry : ctx->timed) { cudaEventDestroy(entry.start); cudaEventDestroy(entry.stop); }
+    for (auto& events : ctx->event_pool) { cudaEventDestroy(events.first); cudaEventDestroy(events.second); }
+    cudaFree(ctx->workspace);
+    cudaFree(ctx->control);
+    delete ctx;
+}
+
+int sdxlq_context_set_stream(sdxlq_context* ctx, void* stream) {
+    if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    ctx->stream = static_cast<cudaStream_t>(stream);
+    return SDXLQ_OK;
+}
+
+int sdxlq_context_set_tile_n(sdxlq_context* ctx, int tile_n) {
+    if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    ctx->forced_tile_n = tile_n;
+    return SDXLQ_OK;
+}
+
+int sdxlq_context_check(sdxlq_context* ctx) {
+    if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    cudaError_t status = cudaStreamSynchronize(ctx->stream);
+    if (status != cudaSuccess) return fail_cuda(ctx, status, "stream synchronize");
+    uint32_t word = 0;
+    status = cudaMemcpy(&word, ctx->control, sizeof(word), cudaMemcpyDeviceToHost);
+    if (status != cudaSuccess) return fail_cuda(ctx, status, "error word read");
+    if (word != 0) {
+        cudaMemset(ctx->control, 0, sizeof(uint32_t));
+        char text[96];
+        std::snprintf(text, sizeof(text), "a bounded device-side wait ran out (code 0x%x)", word);
+        return fail(ctx, SDXLQ_ERR_TIMEOUT, text);
+    }
+    return SDXLQ_OK;
+}
+
+const char* sdxlq_last_error(const sdxlq_context* ctx) { return ctx == nullptr ? "" : ctx->last_error.c_str(); }
+
+const char* sdxlq_status_string(int status) {
+    switch (status) {
+    case SDXLQ_OK: return "ok";
+    case SDXLQ_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case SDXLQ_ERR_UNSUPPORTED_SHAPE: return "unsupported shape";
+    case SDXLQ_ERR_TIMEOUT: return "device wait timed out";
+    case SDXLQ_ERR_CUDA: return "CUDA error";
+    case SDXLQ_ERR_WORKSPACE: return "workspace too small";
+    default: return "unknown status";
+    }
+}
+
+int sdxlq_get_stats(const sdxlq_context* ctx, sdxlq_int8_stats* out) {
+    if (ctx == nullptr || out == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    *out = ctx->stats;
+    return SDXLQ_OK;
+}
+
+int sdxlq_valid_convrot_group_size(size_t group_size) { return valid_group(group_size) ? 1 : 0; }
+
+const char* sdxlq_build_info(void) { return "sdxlq sm_100a tcgen05/TMA cta_group::1 128xN"; }
+
+size_t sdxlq_workspace_bytes(const sdxlq_linear_desc* descs, size_t count) {
+    if (descs == nullptr) return 0;
+    std::map<QuantKey, int> seen;
+    size_t scratch = 0;
+    for (size_t index = 0; index < count; ++index) {
+        const sdxlq_linear_desc& d = descs[index];
+        const sdxlq_weight& w = d.weight;
+        if (d.m == 0 || d.xq != nullptr || w.dtype == SDXLQ_FP16) continue;
+        const uint32_t kind = w.dtype == SDXLQ_INT8 ? KIND_I8 : (w.dtype == SDXLQ_FP8_E4M3 ? KIND_E4M3 : KIND_E5M2);
+        const QuantKey key{d.x, d.m, w.k, kind, kind == KIND_I8 ? w.convrot_group_size : 0u};
+        if (!seen.emplace(key, 1).second) continue;
+        const size_t q_offset = align_up(scratch, 256);
+        const size_t s_offset = align_up(q_offset + static_cast<size_t>(d.m) * w.k, 256);
+        scratch = s_offset + (kind == KIND_I8 ? static_cast<size_t>(d.m) * sizeof(float) : sizeof(float));
+    }
+    return scratch;
+}
+
+int sdxlq_linear(sdxlq_context* ctx, const sdxlq_linear_desc* desc) {
+    if (ctx == nullptr || desc == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    Prepared prep;
+    int status = prepare(ctx, desc, 1, false, prep);
+    if (status != SDXLQ_OK) return status;
+    if (!prep.int8_jobs.empty()) {
+        QuantInt8Launch launch{};
+        launch.jobs = nullptr;
+        launch.num_jobs = 1;
+        launch.single = prep.int8_jobs[0];
+        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_INT8);
+        const cudaError_t error = launch_rotate_quantize_int8(launch, prep.int8_blocks, prep.int8_threads, ctx->stream);
+        if (error != cudaSuccess) return fail_cuda(ctx, error, "INT8 activation quantise launch");
+    }
+    if (!prep.fp8_jobs.empty()) {
+        const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, nullptr);
+        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8);
+        const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream);
+        if (error != cudaSuccess) return fail_cuda(ctx, error, "FP8 activation quantise launch");
+    }
+    if (!prep.problems.empty()) {
+        const GemmProblem& problem = prep.problems[0];
+        const GemmGeometry geometry = gemm_geometry(problem.tile_n);
+        GemmLaunchParams params{};
+        params.problems = nullptr;
+        params.tiles = nullptr;
+        params.num_tiles = problem.tiles_m * problem.tiles_n;
+        params.num_stages = geometry.num_stages;
+        params.stage_bytes = geometry.stage_bytes;
+        params.b_offset = kTileM * kTileKBytes;
+        params.error_word = ctx->control;
+        params.wait_limit_cycles = ctx->wait_limit_cycles;
+        params.single = problem;
+        const uint32_t grid = std::min<uint32_t>(params.num_tiles, static_cast<uint32_t>(ctx->sm_count));
+        LaunchTimer timer(ctx, SDXLQ_KERNEL_GEMM);
+        const cudaError_t error = launch_umma_gemm(params, grid, geometry.dynamic_smem, ctx->stream,
+                                                   &ctx->umma_smem_attribute);
+        if (error != cudaSuccess) return fail_cuda(ctx, error, "tensor-core GEMM launch");
+    }
+    status = run_small(ctx, prep);
+    if (status != SDXLQ_OK) return status;
+    count_stats(ctx, prep);
+    return SDXLQ_OK;
+}
+
+int sdxlq_group_plan_create(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count,
+                            sdxlq_group_plan** out) {
+    if (ctx == nullptr || out == nullptr || (descs == nullptr && count != 0)) return SDXLQ_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    sdxlq_group_plan* plan = new (std::nothrow) sdxlq_group_plan();
+    if (plan == nullptr) return SDXLQ_ERR_CUDA;
+    plan->device = ctx->device;
+    int status = prepare(ctx, descs, count, true, plan->prep);
+    if (status != SDXLQ_OK) { delete plan; return status; }
+    Prepared& prep = plan->prep;
+    auto upload = [&](auto** destination, const auto& host) -> bool {
+        using T = std::remove_reference_t<decltype(host[0])>;
+        if (host.empty()) return true;
+        if (cudaMalloc(reinterpret_cast<void**>(destination), host.size() * sizeof(T)) != cudaSuccess) return false;
+        return cudaMemcpy(*destination, host.data(), host.size() * sizeof(T), cudaMemcpyHostToDevice) == cudaSuccess;
+    };
+    if (!upload(&plan->device_problems, prep.problems) || !upload(&plan->device_tiles, prep.tiles) ||
+        !upload(&plan->device_int8_jobs, prep.int8_jobs) || !upload(&plan->device_fp8_jobs, prep.fp8_jobs)) {
+        sdxlq_group_plan_destroy(plan);
+        return fail(ctx, SDXLQ_ERR_CUDA, "grouped plan: device table allocation failed");
+    }
+    *out = plan;
+    return SDXLQ_OK;
+}
+
+int sdxlq_group_plan_run(sdxlq_context* ctx, sdxlq_group_plan* plan) {
+    if (ctx == nullptr || plan == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    Prepared& prep = plan->prep;
+    if (!prep.int8_jobs.empty()) {
+        QuantInt8Launch launch{};
+        launch.jobs = plan->device_int8_jobs;
+        launch.num_jobs = static_cast<uint32_t>(prep.int8_jobs.size());
+        launch.single = prep.int8_jobs[0];
+        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_INT8);
+        const cudaError_t error = launch_rotate_quantize_int8(launch, prep.int8_blocks, 256, ctx->stream);
+        if (error != cudaSuccess) return fail_cuda(ctx, error, "grouped INT8 activation quantise launch");
+    }
+    if (!prep.fp8_jobs.empty()) {
+        const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, plan->device_fp8_jobs);
+        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8);
+        const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream);
+        if (error != cudaSuccess) return fail_cuda(ctx, error, "grouped FP8 activation quantise launch");
+    }
+    if (!prep.problems.empty()) {
+        const GemmGeometry geometry = gemm_geometry(prep.max_tile_n);
+        GemmLaunchParams params{};
+        params.problems = plan->device_problems;
+        params.tiles = plan->device_tiles;
+        params.num_tiles = static_cast<uint32_t>(prep.tiles.size());
+        params.num_stages = geometry.num_stages;
+        params.stage_bytes = geometry.stage_bytes;
+        params.b_offset = kTileM * kTileKBytes;
+        params.error_word = ctx->control;
+        params.wait_limit_cycles = ctx->wait_limit_cycles;
+        params.single = prep.problems[0];
+        const uint32_t grid = std::min<uint32_t>(params.num_tiles, static_cast<uint32_t>(ctx->sm_count));
+        LaunchTimer timer(ctx, SDXLQ_KERNEL_GEMM);
+        const cudaError_t error = launch_umma_gemm(params, grid, geometry.dynamic_smem, ctx->stream,
+                                                   &ctx->umma_smem_attribute);
+        if (error != cudaSuccess) return fail_cuda(ctx, error, "grouped tensor-core GEMM launch");
+    }
+    const int status = run_small(ctx, prep);
+    if (status != SDXLQ_OK) return status;
+    count_stats(ctx, prep);
+    return SDXLQ_OK;
+}
+
+int sdxlq_group_plan_launches(const sdxlq_group_plan* plan) {
+    if (plan == nullptr) return 0;
+    const Prepared& prep = plan->prep;
+    return (prep.int8_jobs.empty() ? 0 : 1) + (prep.fp8_jobs.empty() ? 0 : 2) + (prep.problems.empty() ? 0 : 1) +
+           static_cast<int>(prep.small.size());
+}
+
+void sdxlq_group_plan_destroy(sdxlq_group_plan* plan) {
+    if (plan == nullptr) return;
+    cudaSetDevice(plan->device);
+    cudaFree(plan->device_problems);
+    cudaFree(plan->device_tiles);
+    cudaFree(plan->device_int8_jobs);
+    cudaFree(plan->device_fp8_jobs);
+    delete plan;
+}
+
+int sdxlq_linear_grouped(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count) {
+    sdxlq_group_plan* plan = nullptr;
+    int status = sdxlq_group_plan_create(ctx, descs, count, &plan);
+    if (status != SDXLQ_OK) return status;
+    status = sdxlq_group_plan_run(ctx, plan);
+    // The device tables must outlive the kernels that read them.
+    if (cudaStreamSynchronize(ctx->stream) != cudaSuccess && status == SDXLQ_OK) status = SDXLQ_ERR_CUDA;
+    sdxlq_group_plan_destroy(plan);
+    return status;
+}
+
+int sdxlq_quantize_act_int8(sdxlq_context* ctx, const void* x, int32_t x_dtype, uint64_t m, uint64_t k,
+                            uint32_t convrot_group_size, int8_t* xq, float* scales) {
+    if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    if (x == nullptr || xq == nullptr || scales == nullptr || k == 0) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "quantize_act_int8: null pointer or empty row");
+    }
+    if (x_dtype != SDXLQ_FP16 && x_dtype != SDXLQ_FP32) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "native INT8 linear received incompatible tensors");
+    }
+    if (convrot_group_size != 0 && (!valid_group(convrot_group_size) || k % convrot_group_size != 0)) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "native INT8 linear has invalid ConvRot group metadata");
+    }
+    if (m > 0x7FFFFFFFull || k > 0x7FFFFFFFull) return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE, "quantize_act_int8: dimensions too large");
+    if (m == 0) return SDXLQ_OK;
+    Prepared prep;
+    const int status = add_int8_job(ctx, prep, x, x_dtype == SDXLQ_FP32, m, k, convrot_group_size, xq, scales, false);
+    if (status != SDXLQ_OK) return status;
+    QuantInt8Launch launch{};
+    launch.num_jobs = 1;
+    launch.single = prep.int8_jobs[0];
+    LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_INT8);
+    const cudaError_t error = launch_rotate_quantize_int8(launch, prep.int8_blocks, prep.int8_threads, ctx->stream);
+    if (error != cudaSuccess) return fail_cuda(ctx, error, "INT8 activation quantise launch");
+    return SDXLQ_OK;
+}
+
+int sdxlq_quantize_act_fp8(sdxlq_context* ctx, const void* x_f16, uint64_t count, int32_t fmt, uint8_t* q,
+                           float* scale) {
+    if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    if (x_f16 == nullptr || q == nullptr || scale == nullptr || !is_fp8(fmt)) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "FP8 activation quantization requires float16 input and an FP8 destination");
+    }
+    Prepared prep;
+    add_fp8_job(prep, x_f16, count, fmt == SDXLQ_FP8_E4M3 ? 0 : 1, q, scale);
+    const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, nullptr);
+    LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8);
+    const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream);
+    if (error != cudaSuccess) return fail_cuda(ctx, error, "FP8 activation quantise launch");
+    return SDXLQ_OK;
+}
+
+int sdxlq_pack_weight_int8(sdxlq_context* ctx, const void* src, int32_t src_dtype, uint64_t n, uint64_t k,
+                           uint32_t convrot_group_size, int8_t* dst, float* scales) {
+    if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    if (src == nullptr || dst == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "pack_weight_int8: null pointer");
+    if (n == 0 || k == 0) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "native INT8 weight cannot be empty");
+    if (src_dtype == SDXLQ_INT8) {
+        const cudaError_t error = cudaMemcpyAsync(dst, src, n * k, cudaMemcpyDeviceToDevice, ctx->stream);
+        if (error != cudaSuccess) return fail_cuda(ctx, error, "prequantised INT8 weight copy");
+        return SDXLQ_OK;
+    }
+    if (src_dtype != SDXLQ_FP16 && src_dtype != SDXLQ_FP32) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "native INT8 loading requires I8, F16 or F32 weights");
+    }
+    if (convrot_group_size != 0 && !valid_group(convrot_group_size)) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "INT8 ConvRot group size must be a power of four between 4 and 256");
+    }
+    if (convrot_group_size != 0 && k % convrot_group_size != 0) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "ConvRot group size does not divide the weight's input features");
+    }
+    return sdxlq_quantize_act_int8(ctx, src, src_dtype, n, k, convrot_group_size, dst, scales);
+}
+
+int sdxlq_pack_weight_fp8(sdxlq_context* ctx, const void* src, int32_t src_dtype, uint64_t n, uint64_t k,
+                          int32_t fmt, int32_t scale_mode, int32_t layout, uint8_t* dst, float* scales) {
+    if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    if (src == nullptr || dst == nullptr || scales == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "pack_weight_fp8: null pointer");
+    if (!is_fp8(fmt)) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "CUDA weight upload target must be FP8");
+    if (scale_mode != SDXLQ_SCALE_TENSOR_WIDE && scale_mode != SDXLQ_SCALE_PER_OUTPUT_CHANNEL) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "per-output-channel FP8 scaling requires a rank-2 matrix");
+    }
+    if (n == 0 || k == 0 || n > 0x7FFFFFFFull || k > 0x7FFFFFFFull) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "pack_weight_fp8: bad shape");
+    if (src_dtype != SDXLQ_FP16 && src_dtype != SDXLQ_FP32 && !is_fp8(src_dtype)) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "pack_weight_fp8: unsupported source type");
+    }
+    const uint32_t per_channel = scale_mode == SDXLQ_SCALE_PER_OUTPUT_CHANNEL ? 1 : 0;
+    const uint32_t scale_count = per_channel ? static_cast<uint32_t>(n) : 1;
+    if (src_dtype == fmt && layout == SDXLQ_ROW_MAJOR_NK) {
+        // Native FP8 checkpoint: bytes are kept, scales are 1 (weights.cu:331-347).
+        cudaError_t error = cudaMemcpyAsync(dst, src, n * k, cudaMemcpyDeviceToDevice, ctx->stream);
+        if (error == cudaSuccess) error = launch_fill_f32(scales, scale_count, 1.0f, ctx->stream);
+        if (error != cudaSuccess) return fail_cuda(ctx, error, "native FP8 weight copy");
+        return SDXLQ_OK;
+    }
+    const cudaError_t error = launch_fp8_weight_pack(src, src_dtype, static_cast<uint32_t>(n), static_cast<uint32_t>(k),
+                                                     fmt == SDXLQ_FP8_E4M3 ? 0 : 1, per_channel,
+                                                     layout == SDXLQ_K_MAJOR_KN ? 1 : 0, dst, scales, ctx->stream);
+    if (error != cudaSuccess) return fail_cuda(ctx, error, "FP8 weight pack launch");
+    return SDXLQ_OK;
+}
+
+int sdxlq_profile_enable(sdxlq_context* ctx, int enabled) {
+    if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    ctx->profiling = enabled != 0;
+    return SDXLQ_OK;
+}
+
+int sdxlq_profile_read(sdxlq_context* ctx, sdxlq_kernel_times* out) {
+    if (ctx == nullptr || out == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    const cudaError_t status = cudaStreamSynchronize(ctx->stream);
+    if (status != cudaSuccess) return fail_cuda(ctx, status, "stream synchronize");
+    std::memset(out, 0, sizeof(*out));
+    for (auto& entry : ctx->timed) {
+        float milliseconds = 0.0f;
+        if (cudaEventElapsedTime(&milliseconds, entry.start, entry.stop) == cudaSuccess &&
+            entry.kernel_class >= 0 && entry.kernel_class < SDXLQ_KERNEL_CLASSES) {
+            out->milliseconds[entry.kernel_class] += milliseconds;
+            out->launches[entry.kernel_class] += entry.kernel_class == SDXLQ_KERNEL_QUANT_FP8 ? 2 : 1;
+        }
+        ctx->event_pool.emplace_back(entry.start, entry.stop);
+    }
+    ctx->timed.clear();
+    return SDXLQ_OK;
+}
+
+// Launches a one-thread kernel that waits, with the given limit, on a barrier nothing ever
+// signals. The wait runs out, the kernel records the timeout code and returns; the next
+// sdxlq_context_check reports SDXLQ_ERR_TIMEOUT and the context stays usable.
+int sdxlq_selftest_bounded_wait(sdxlq_context* ctx, long long limit_cycles) {
+    if (ctx == nullptr || limit_cycles <= 0 || limit_cycles > 2000000000LL) return SDXLQ_ERR_INVALID_ARGUMENT;
+    const cudaError_t error = launch_bounded_wait_probe(ctx->control, limit_cycles, ctx->stream);
+    if (error != cudaSuccess) return fail_cuda(ctx, error, "bounded wait probe launch");
+    return SDXLQ_OK;
+}
+
+}  // extern "C"

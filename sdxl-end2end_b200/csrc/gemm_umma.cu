@@ -1,0 +1,509 @@
+// Persistent, warp-specialised tcgen05 GEMM with fused dequant + bias + activation epilogue.
+//
+//   Y[M, N] = epilogue( A[M, K] * B[N, K]^T )      A, B both K-major, 8-bit (INT8 / FP8) or FP16
+//
+// Replaces, for every projection of the path, the reference's cuBLASLt call plus the kernels
+// it runs afterwards: INT8 (src/cuda/int8_convrot.cu:634-698 GEMM, :388-402 dequant), FP8
+// (src/cuda/ops_blas.cpp:153-225), FP16 (ops_blas.cpp:300-385), then add_last_dim_bias /
+// bias_activation_in_place / bias_geglu (src/cuda/ops_kernels.cu:76-82, 142-183).
+//
+// One CTA per SM walks a tile list (all tiles of all problems of a grouped launch):
+//   warp 0    TMA producer  : cp.async.bulk.tensor 2D loads into a ring of 128B-swizzled stages
+//   warp 1    MMA issuer    : tcgen05.mma (kind::i8 / kind::f8f6f4 / kind::f16), accumulators
+//                             in TMEM, two accumulator buffers so the next tile's main loop
+//                             overlaps this tile's epilogue
+//   warps 2-9 epilogue      : tcgen05.ld -> scales, bias, activation / GEGLU -> FP16 stores
+// Every wait is bounded: when one runs out the CTA raises an abort word, all roles leave their
+// loops, TMEM is released and the kernel returns with an error code in global memory.
+
+#include "internal.cuh"
+#include "ptx.cuh"
+
+namespace sdxlq {
+
+namespace {
+
+constexpr uint32_t kMaxStages = 8;
+constexpr uint32_t kEpilogueWarps = 8;                       // two per TMEM lane quadrant
+constexpr uint32_t kThreads = 64 + 32 * kEpilogueWarps;      // producer warp + MMA warp + epilogue
+
+struct alignas(16) Control {
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort;
+    uint32_t pad[2];
+    // Per-tile epilogue operands staged by the epilogue warps, one slot per accumulator buffer:
+    // the weight scale and the bias of every accumulator column of the tile.
+    alignas(16) float column_scale[2][kMaxTileN];
+    alignas(16) __half column_bias[2][kMaxTileN];
+};
+
+// What the producer and the MMA issuer need to know about a tile, held in registers.
+struct TileWork {
+    const GemmProblem* problem;
+    uint32_t tile_m;
+    uint32_t tile_n_index;
+    uint32_t tile_n;
+    uint32_t k_blocks;
+    uint32_t idesc;
+    uint32_t kind;
+    uint32_t geglu;
+    uint32_t n_out;
+};
+
+// Single-problem launches read the problem from the kernel parameters (constant bank);
+// grouped launches read the tile list and the problem table from global memory.
+__device__ __forceinline__ TileWork fetch_tile(const GemmLaunchParams& params, uint32_t index) {
+    TileWork work;
+    if (params.problems == nullptr) {
+        work.problem = &params.single;
+        work.tile_m = index % params.single.tiles_m;
+        work.tile_n_index = index / params.single.tiles_m;
+        work.tile_n = params.single.tile_n;
+        work.k_blocks = params.single.k_blocks;
+        work.idesc = params.single.idesc;
+        work.kind = params.single.ep.kind;
+        work.geglu = params.single.ep.activation == ACT_GEGLU ? 1u : 0u;
+        work.n_out = params.single.ep.n_out;
+    } else {
+        const TileRef ref = params.tiles[index];
+        const GemmProblem* problem = params.problems + ref.problem;
+        work.problem = problem;
+        work.tile_m = ref.tile_m;
+        work.tile_n_index = ref.tile_n;
+        work.tile_n = problem->tile_n;
+        work.k_blocks = problem->k_blocks;
+        work.idesc = problem->idesc;
+        work.kind = problem->ep.kind;
+        work.geglu = problem->ep.activation == ACT_GEGLU ? 1u : 0u;
+        work.n_out = problem->ep.n_out;
+    }
+    return work;
+}
+
+__device__ __forceinline__ void raise_abort(Control* control, uint32_t* error_word, uint32_t code) {
+    *reinterpret_cast<volatile uint32_t*>(&control->abort) = 1;
+    atomicCAS(error_word, 0u, code);
+}
+
+__device__ __forceinline__ void epilogue_barrier() {
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+}
+
+// Stages the weight scale and bias of each accumulator column of a tile into shared memory.
+// Column j of a GEGLU tile is value column n0 + j for j < tile_n / 2 and gate column
+// n_out + n0 + (j - tile_n / 2) otherwise. Columns past the matrix edge get scale 0, bias 0.
+__device__ __forceinline__ void stage_columns(const EpilogueParams& ep, uint32_t tile_n, uint32_t tile_n_index,
+                                              float* column_scale, __half* column_bias, uint32_t thread) {
+    const bool geglu = ep.activation == ACT_GEGLU;
+    const bool scaled = ep.kind != KIND_F16;
+    const bool per_channel = scaled && ep.w_scale_per_channel != 0;
+    const uint32_t half = tile_n / 2;
+    const uint32_t per_tile = geglu ? half : tile_n;
+    const uint32_t n0 = tile_n_index * per_tile;
+    const float shared_scale = (scaled && !per_channel) ? __ldg(ep.w_scales) : 1.0f;
+    for (uint32_t j = thread; j < tile_n; j += 32 * kEpilogueWarps) {
+        const uint32_t local = (geglu && j >= half) ? j - half : j;
+        const bool valid = n0 + local < ep.n_out;
+        const uint32_t column = (geglu && j >= half) ? ep.n_out + n0 + local : n0 + local;
+        float scale = 0.0f;
+        __half bias = __half(0);
+        if (valid) {
+            scale = per_channel ? __ldg(ep.w_scales + column) : shared_scale;
+            if (ep.bias != nullptr) bias = ep.bias[column];
+        }
+        column_scale[j] = scale;
+        column_bias[j] = bias;
+    }
+}
+
+__device__ __forceinline__ uint32_t pack_halves(__half lo, __half hi) {
+    return static_cast<uint32_t>(__half_as_ushort(lo)) | (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
+}
+
+__device__ __forceinline__ __half packed_half(const uint32_t word, int index) {
+    return __ushort_as_half(static_cast<unsigned short>(index == 0 ? (word & 0xFFFFu) : (word >> 16)));
+}
+
+// W FP16 results of one output row, packed two per word -> global memory.
+template <int W>
+__device__ __forceinline__ void store_row_chunk(__half* y, uint32_t n_out, bool vector_ok, uint32_t row,
+                                                uint32_t col0, const uint32_t (&words)[W / 2]) {
+    __half* destination = y + static_cast<size_t>(row) * n_out + col0;
+    if (vector_ok && col0 + W <= n_out) {
+#pragma unroll
+        for (int i = 0; i < W / 8; ++i) {
+            reinterpret_cast<uint4*>(destination)[i] =
+                make_uint4(words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < W; ++i) {
+            if (col0 + i < n_out) destination[i] = packed_half(words[i >> 1], i & 1);
+        }
+    }
+}
+
+// Reads W staged scales / biases starting at column j0 (a multiple of 8) with 16-byte loads.
+template <int W>
+__device__ __forceinline__ void read_staged(const float* column_scale, const __half* column_bias, uint32_t j0,
+                                            float (&scale)[W], uint32_t (&bias_words)[W / 2]) {
+#pragma unroll
+    for (int i = 0; i < W / 4; ++i) {
+        const float4 v = *reinterpret_cast<const float4*>(column_scale + j0 + 4 * i);
+        scale[4 * i] = v.x; scale[4 * i + 1] = v.y; scale[4 * i + 2] = v.z; scale[4 * i + 3] = v.w;
+    }
+#pragma unroll
+    for (int i = 0; i < W / 8; ++i) {
+        const uint4 v = *reinterpret_cast<const uint4*>(column_bias + j0 + 8 * i);
+        bias_words[4 * i] = v.x; bias_words[4 * i + 1] = v.y; bias_words[4 * i + 2] = v.z; bias_words[4 * i + 3] = v.w;
+    }
+}
+
+template <uint32_t Kind>
+__device__ __forceinline__ __half project(uint32_t acc_bits, float a_scale, float w_scale) {
+    return project_to_half(acc_bits, Kind == 1 ? static_cast<uint32_t>(KIND_E4M3) : Kind, a_scale, w_scale);
+}
+
+// Everything one epilogue warp needs for its share of a tile, passed by value to the
+// out-of-line epilogue variants.
+struct EpilogueTile {
+    __half* y;
+    int32_t* acc_out;
+    const float* column_scale;      // shared memory
+    const __half* column_bias;      // shared memory
+    float a_scale;
+    uint32_t n, n_out;
+    uint32_t tile_n, n0;            // accumulator columns of the tile; first output column
+    uint32_t row, tmem_row;
+    uint32_t chunk_first;           // 0 or 1: which of the two warps of the quadrant
+    uint32_t flags;                 // bit 0 row in range, bit 1 has bias, bit 2 vector stores
+};
+
+// Drains this warp's share of one accumulator tile. Kind: 0 INT8, 1 FP8 (either format), 3 FP16.
+template <uint32_t Kind, uint32_t Act>
+__device__ __noinline__ void epilogue_tile(const EpilogueTile t) {
+    const bool row_ok = (t.flags & 1u) != 0;
+    const bool has_bias = (t.flags & 2u) != 0;
+    const bool store_vector = (t.flags & 4u) != 0;
+    int32_t* const acc_out = Kind == KIND_I8 ? t.acc_out : nullptr;
+    if (Act != ACT_GEGLU) {
+        constexpr int W = 16;
+        for (uint32_t c0 = t.chunk_first * W; c0 < t.tile_n; c0 += 2 * W) {
+            const uint32_t col0 = t.n0 + c0;
+            if (col0 >= t.n) break;
+            uint32_t acc[W];
+            ptx::tmem_ld_32x32b_x16(t.tmem_row + c0, acc);
+            float w_scale[W];
+            uint32_t bias_words[W / 2];
+            read_staged<W>(t.column_scale, t.column_bias, c0, w_scale, bias_words);
+            ptx::tmem_ld_wait();
+            if (acc_out != nullptr && row_ok) {
+                int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n + col0;
+#pragma unroll
+                for (int i = 0; i < W; ++i) {
+                    if (col0 + i < t.n) raw[i] = static_cast<int32_t>(acc[i]);
+                }
+            }
+            uint32_t out_words[W / 2];
+#pragma unroll
+            for (int i = 0; i < W; i += 2) {
+                const __half y0 = project<Kind>(acc[i], t.a_scale, w_scale[i]);
+                const __half y1 = project<Kind>(acc[i + 1], t.a_scale, w_scale[i + 1]);
+                const __half r0 = finish_scalar(y0, has_bias, packed_half(bias_words[i >> 1], 0), Act);
+                const __half r1 = finish_scalar(y1, has_bias, packed_half(bias_words[i >> 1], 1), Act);
+                out_words[i >> 1] = pack_halves(r0, r1);
+            }
+            if (row_ok) store_row_chunk<W>(t.y, t.n_out, store_vector, t.row, col0, out_words);
+        }
+    } else {
+        constexpr int W = 8;
+        const uint32_t half = t.tile_n / 2;
+        for (uint32_t c0 = t.chunk_first * W; c0 < half; c0 += 2 * W) {
+            const uint32_t col0 = t.n0 + c0;
+            if (col0 >= t.n_out) break;
+            uint32_t acc_value[W], acc_gate[W];
+            ptx::tmem_ld_32x32b_x8(t.tmem_row + c0, acc_value);
+            ptx::tmem_ld_32x32b_x8(t.tmem_row + half + c0, acc_gate);
+            float w_value[W], w_gate[W];
+            uint32_t b_value[W / 2], b_gate[W / 2];
+            read_staged<W>(t.column_scale, t.column_bias, c0, w_value, b_value);
+            read_staged<W>(t.column_scale, t.column_bias, half + c0, w_gate, b_gate);
+            ptx::tmem_ld_wait();
+            if (acc_out != nullptr && row_ok) {
+                int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n;
+#pragma unroll
+                for (int i = 0; i < W; ++i) {
+                    if (col0 + i < t.n_out) {
+                        raw[col0 + i] = static_cast<int32_t>(acc_value[i]);
+                        raw[t.n_out + col0 + i] = static_cast<int32_t>(acc_gate[i]);
+                    }
+                }
+            }
+            uint32_t out_words[W / 2];
+#pragma unroll
+            for (int i = 0; i < W; i += 2) {
+                __half r[2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const __half y_value = project<Kind>(acc_value[i + j], t.a_scale, w_value[i + j]);
+                    const __half y_gate = project<Kind>(acc_gate[i + j], t.a_scale, w_gate[i + j]);
+                    r[j] = finish_geglu(y_value, packed_half(b_value[i >> 1], j), y_gate, packed_half(b_gate[i >> 1], j));
+                }
+                out_words[i >> 1] = pack_halves(r[0], r[1]);
+            }
+            if (row_ok) store_row_chunk<W>(t.y, t.n_out, store_vector, t.row, col0, out_words);
+        }
+    }
+}
+
+template <uint32_t Kind>
+__device__ __forceinline__ void epilogue_dispatch(uint32_t activation, const EpilogueTile& t) {
+    switch (activation) {
+    case ACT_NONE: epilogue_tile<Kind, ACT_NONE>(t); break;
+    case ACT_SILU: epilogue_tile<Kind, ACT_SILU>(t); break;
+    case ACT_GELU: epilogue_tile<Kind, ACT_GELU>(t); break;
+    case ACT_QUICK_GELU: epilogue_tile<Kind, ACT_QUICK_GELU>(t); break;
+    default: epilogue_tile<Kind, ACT_GEGLU>(t); break;
+    }
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads, 1)
+sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
+    extern __shared__ __align__(16) uint8_t dynamic_smem[];
+    Control* control = reinterpret_cast<Control*>(dynamic_smem);
+    const uint32_t stages_base = (ptx::smem_u32(dynamic_smem) + sizeof(Control) + 1023u) & ~1023u;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t num_stages = params.num_stages;
+    const uint32_t stage_bytes = params.stage_bytes;
+    const uint32_t b_offset = params.b_offset;
+    const uint32_t num_tiles = params.num_tiles;
+    volatile uint32_t* abort_word = &control->abort;
+    const long long limit = params.wait_limit_cycles;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < num_stages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&control->full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&control->empty[s]), 1);
+        }
+        for (uint32_t b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&control->tmem_full[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&control->tmem_empty[b]), kEpilogueWarps);
+        }
+        control->abort = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(&control->tmem_base), kTmemColumns);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&control->tmem_base);
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            uint32_t issued_mask = 0, issued_phase = 0;
+            const GemmProblem* bound = nullptr;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+                const TileWork work = fetch_tile(params, t);
+                const CUtensorMap* tmap_a = &work.problem->tmap_a;
+                const CUtensorMap* tmap_b = &work.problem->tmap_b;
+                if (params.problems != nullptr && work.problem != bound) {
+                    ptx::fence_tensormap_acquire(tmap_a);
+                    ptx::fence_tensormap_acquire(tmap_b);
+                    bound = work.problem;
+                }
+                const uint32_t tile_n = work.tile_n;
+                const uint32_t half = tile_n / 2;
+                const uint32_t tx_bytes = (kTileM + tile_n) * kTileKBytes;
+                const int32_t k_step = work.kind == KIND_F16 ? 64 : 128;   // elements per stage
+                const int32_t row_a = static_cast<int32_t>(work.tile_m * kTileM);
+                const int32_t row_b = static_cast<int32_t>(work.tile_n_index * (work.geglu ? half : tile_n));
+                const int32_t row_gate = static_cast<int32_t>(work.n_out) + row_b;
+                const uint32_t k_blocks = work.k_blocks;
+                for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+                    const uint32_t full_bar = ptx::smem_u32(&control->full[stage]);
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->empty[stage]), phase ^ 1u,
+                                                abort_word, limit)) {
+                        raise_abort(control, params.error_word, DEV_TIMEOUT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_expect_tx(full_bar, tx_bytes);
+                    const uint32_t a_dst = stages_base + stage * stage_bytes;
+                    const uint32_t b_dst = a_dst + b_offset;
+                    const int32_t k0 = static_cast<int32_t>(kb) * k_step;
+                    ptx::tma_load_2d(a_dst, tmap_a, full_bar, k0, row_a);
+                    ptx::tma_load_2d(b_dst, tmap_b, full_bar, k0, row_b);
+                    if (work.geglu) ptx::tma_load_2d(b_dst + half * kTileKBytes, tmap_b, full_bar, k0, row_gate);
+                    issued_mask |= 1u << stage;
+                    issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
+                    if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // Let the copies this thread started land before the CTA retires.
+                for (uint32_t s = 0; s < num_stages; ++s) {
+                    if (issued_mask & (1u << s)) {
+                        (void)ptx::mbar_wait_bounded(ptx::smem_u32(&control->full[s]),
+                                                     (issued_phase >> s) & 1u, abort_word, limit >> 4);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer ---------------------------------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, iteration = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++iteration) {
+                const TileWork work = fetch_tile(params, t);
+                const uint32_t buffer = iteration & 1u;
+                const uint32_t accumulator_phase = (iteration >> 1) & 1u;
+                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->tmem_empty[buffer]),
+                                            accumulator_phase ^ 1u, abort_word, limit)) {
+                    raise_abort(control, params.error_word, DEV_TIMEOUT_MMA);
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t tmem_d = tmem_base + buffer * kMaxTileN;
+                const uint32_t idesc = work.idesc;
+                const uint32_t kind = work.kind;
+                const uint32_t k_blocks = work.k_blocks;
+                for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->full[stage]), phase, abort_word,
+                                                limit)) {
+                        raise_abort(control, params.error_word, DEV_TIMEOUT_MMA + 1);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t a_addr = stages_base + stage * stage_bytes;
+                    const uint64_t desc_a = ptx::umma_smem_desc_sw128(a_addr);
+                    const uint64_t desc_b = ptx::umma_smem_desc_sw128(a_addr + b_offset);
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; ++k) {   // 4 x 32 bytes of K per stage
+                        const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+                        const uint64_t advance = static_cast<uint64_t>(k * 2);   // 32 B >> 4
+                        if (kind == KIND_I8) ptx::umma_i8(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
+                        else if (kind == KIND_F16) ptx::umma_f16(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
+                        else ptx::umma_f8f6f4(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
+                    }
+                    ptx::umma_commit(ptx::smem_u32(&control->empty[stage]));
+                    if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ptx::umma_commit(ptx::smem_u32(&control->tmem_full[buffer]));
+            }
+        }
+    } else {
+        // ------------------------------- epilogue ------------------------------------------
+        // Warp w may touch TMEM lanes 32*(w % 4) .. +31. The two warps of a quadrant take the
+        // even and the odd column chunks of the tile.
+        const uint32_t quadrant = warp & 3u;
+        const uint32_t chunk_first = (warp - 2u) >> 2;
+        const uint32_t epilogue_thread = threadIdx.x - 64u;
+        uint32_t iteration = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++iteration) {
+            const TileWork work = fetch_tile(params, t);
+            const EpilogueParams& ep = params.problems == nullptr ? params.single.ep : work.problem->ep;
+            const uint32_t buffer = iteration & 1u;
+            const uint32_t accumulator_phase = (iteration >> 1) & 1u;
+            // Stage this tile's column operands while the main loop is still running. The slot
+            // was last read two tiles ago; every warp passed the previous tile's barrier since.
+            stage_columns(ep, work.tile_n, work.tile_n_index, control->column_scale[buffer],
+                          control->column_bias[buffer], epilogue_thread);
+            EpilogueTile tile;
+            tile.y = ep.y;
+            tile.acc_out = ep.acc_out;
+            tile.column_scale = control->column_scale[buffer];
+            tile.column_bias = control->column_bias[buffer];
+            tile.n = ep.n;
+            tile.n_out = ep.n_out;
+            tile.tile_n = work.tile_n;
+            tile.n0 = work.tile_n_index * (work.geglu ? work.tile_n / 2 : work.tile_n);
+            tile.row = work.tile_m * kTileM + quadrant * 32u + lane;
+            tile.tmem_row = tmem_base + ((quadrant * 32u) << 16) + buffer * kMaxTileN;
+            tile.chunk_first = chunk_first;
+            const bool row_ok = tile.row < ep.m;
+            tile.flags = (row_ok ? 1u : 0u) | (ep.bias != nullptr ? 2u : 0u) | (ep.vector_store_ok != 0 ? 4u : 0u);
+            const uint32_t kind = ep.kind;
+            const uint32_t activation = ep.activation;
+            tile.a_scale = 1.0f;
+            if (kind == KIND_I8) tile.a_scale = row_ok ? __ldg(ep.a_scales + tile.row) : 0.0f;
+            else if (kind != KIND_F16) tile.a_scale = __ldg(ep.a_scales);
+            epilogue_barrier();
+            if (ok && !ptx::mbar_wait_bounded(ptx::smem_u32(&control->tmem_full[buffer]), accumulator_phase,
+                                              abort_word, limit)) {
+                raise_abort(control, params.error_word, DEV_TIMEOUT_EPILOGUE);
+                ok = false;
+            }
+            // After a timeout the warp keeps walking the tile list (so that the barrier above
+            // stays balanced) but touches neither TMEM nor global memory again.
+            if (!ok) continue;
+            ptx::tc_fence_after();
+            if (kind == KIND_I8) epilogue_dispatch<KIND_I8>(activation, tile);
+            else if (kind == KIND_F16) epilogue_dispatch<KIND_F16>(activation, tile);
+            else epilogue_dispatch<KIND_E4M3>(activation, tile);
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&control->tmem_empty[buffer]));
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+// Failure-detection probe: one thread waits, with a limit, on a barrier that nothing signals;
+// the wait runs out, the timeout code is recorded and the kernel returns normally.
+__global__ void sdxlq_bounded_wait_probe_kernel(uint32_t* error_word, long long limit_cycles) {
+    __shared__ uint64_t barrier;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&barrier), 1);
+        abort_flag = 0;
+        ptx::fence_mbar_init();
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&barrier), 0, &abort_flag, limit_cycles)) {
+            atomicCAS(error_word, 0u, static_cast<uint32_t>(DEV_TIMEOUT_EPILOGUE) + 0x80u);
+        }
+    }
+}
+
+cudaError_t launch_bounded_wait_probe(uint32_t* error_word, long long limit_cycles, cudaStream_t stream) {
+    sdxlq_bounded_wait_probe_kernel<<<1, 32, 0, stream>>>(error_word, limit_cycles);
+    return cudaGetLastError();
+}
+
+// Host-side launcher (called from the dispatch code). `attribute_bytes` remembers, per context,
+// the dynamic shared memory size the kernel has been opted into.
+cudaError_t launch_umma_gemm(const GemmLaunchParams& params, uint32_t grid, size_t dynamic_smem,
+                             cudaStream_t stream, size_t* attribute_bytes) {
+    if (dynamic_smem > *attribute_bytes) {
+        const cudaError_t status = cudaFuncSetAttribute(sdxlq_umma_gemm_kernel,
+                                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                        static_cast<int>(dynamic_smem));
+        if (status != cudaSuccess) return status;
+        *attribute_bytes = dynamic_smem;
+    }
+    sdxlq_umma_gemm_kernel<<<grid, kThreads, dynamic_smem, stream>>>(params);
+    return cudaGetLastError();
+}
+
+}  // namespace sdxlq

@@ -1,0 +1,123 @@
+// Structures shared by the host dispatch code and the kernels, and the epilogue arithmetic
+// shared by the tensor-core GEMM and the small-shape kernel.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace sdxlq {
+
+// Operand kind of a GEMM problem (both operands have the same kind).
+enum GemmKind : uint32_t { KIND_I8 = 0, KIND_E4M3 = 1, KIND_E5M2 = 2, KIND_F16 = 3 };
+
+enum Activation : uint32_t { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU = 2, ACT_QUICK_GELU = 3, ACT_GEGLU = 4 };
+
+// Error word values written by a kernel whose bounded wait ran out.
+enum DeviceError : uint32_t {
+    DEV_OK = 0,
+    DEV_TIMEOUT_PRODUCER = 0x100,
+    DEV_TIMEOUT_MMA = 0x200,
+    DEV_TIMEOUT_EPILOGUE = 0x300,
+};
+
+constexpr uint32_t kTileM = 128;          // rows of one output tile (UMMA M)
+constexpr uint32_t kTileKBytes = 128;     // bytes of K per pipeline stage row (one swizzle span)
+constexpr uint32_t kMaxTileN = 256;       // UMMA N limit
+constexpr uint32_t kTmemColumns = 512;    // two accumulator buffers of up to 256 columns
+
+// Everything the epilogue needs for one problem.
+struct EpilogueParams {
+    __half* y;                   // [M, n_out]
+    int32_t* acc_out;            // optional raw INT32 accumulators [M, N]
+    const float* a_scales;       // INT8: [M]; FP8: [1]; FP16: unused
+    const float* w_scales;       // [N] or [1]; FP16: unused
+    const __half* bias;          // [N] or null
+    uint32_t m, n, k;
+    uint32_t n_out;              // n, or n / 2 for GEGLU
+    uint32_t kind;               // GemmKind
+    uint32_t activation;         // Activation
+    uint32_t w_scale_per_channel;
+    uint32_t vector_store_ok;    // y rows are 16-byte aligned and n_out % 8 == 0
+    uint32_t vector_meta_ok;     // w_scales / bias (and their GEGLU gate halves) are 16-byte aligned
+};
+
+// One GEMM problem of a grouped launch. Tensor maps first (64-byte alignment required).
+struct alignas(64) GemmProblem {
+    CUtensorMap tmap_a;          // [M, K] activations (quantised), box {128 B, 128 rows}
+    CUtensorMap tmap_b;          // [N, K] weights, box {128 B, tile_n rows} (tile_n / 2 for GEGLU)
+    EpilogueParams ep;
+    uint32_t tile_n;             // accumulator columns per tile (multiple of 16, <= 256)
+    uint32_t tiles_m;
+    uint32_t tiles_n;
+    uint32_t k_blocks;           // ceil(K bytes / 128)
+    uint32_t idesc;              // UMMA instruction descriptor
+    uint32_t pad[3];
+};
+
+struct TileRef {
+    uint32_t problem;
+    uint16_t tile_m;
+    uint16_t tile_n;
+};
+
+struct GemmLaunchParams {
+    const GemmProblem* problems; // device table (grouped) or null (single: `single` is used)
+    const TileRef* tiles;        // device tile list (grouped) or null
+    uint32_t num_tiles;
+    uint32_t num_stages;
+    uint32_t stage_bytes;        // bytes of one pipeline stage (A tile + B tile), multiple of 1024
+    uint32_t b_offset;           // offset of the B tile inside a stage (= 128 rows * 128 B)
+    uint32_t* error_word;        // device word set on a bounded-wait timeout
+    long long wait_limit_cycles;
+    GemmProblem single;
+};
+
+// ------------------------------------------------------------------------------------------
+// Epilogue arithmetic. `acc_bits` is the raw 32-bit accumulator (INT32 for KIND_I8, FP32
+// otherwise). Returns the FP16 projection before bias/activation:
+//   INT8: half_rn((float(acc) * a_scale[row]) * w_scale[col])   (dequantize_gemm_f16_kernel)
+//   FP8 : half_rn((acc * x_scale) * w_scale[col or 0])          (native FP8 Linear contract)
+//   FP16: half_rn(acc)
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ __half project_to_half(uint32_t acc_bits, uint32_t kind, float a_scale,
+                                                  float w_scale) {
+    float value;
+    if (kind == KIND_I8) {
+        value = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(acc_bits)), a_scale), w_scale);
+    } else if (kind == KIND_F16) {
+        value = __uint_as_float(acc_bits);
+    } else {
+        value = __fmul_rn(__fmul_rn(__uint_as_float(acc_bits), a_scale), w_scale);
+    }
+    return __float2half_rn(value);
+}
+
+__device__ __forceinline__ float gelu_erf(float x) {
+    return 0.5f * x * (1.0f + erff(x * 0.7071067811865475f));
+}
+
+// Bias + activation on an FP16 projection, as the reference runs them after the GEMM:
+//   none     : __hadd(y, b)                                  (add_last_dim_bias_kernel)
+//   SiLU/GELU/QuickGELU : half_rn(act(float(y) + float(b)))  (bias_activation_in_place_kernel)
+__device__ __forceinline__ __half finish_scalar(__half y, bool has_bias, __half bias, uint32_t activation) {
+    if (!has_bias) return y;
+    if (activation == ACT_NONE) return __hadd(y, bias);
+    const float x = __half2float(y) + __half2float(bias);
+    float result;
+    if (activation == ACT_SILU) result = x / (1.0f + expf(-x));
+    else if (activation == ACT_GELU) result = gelu_erf(x);
+    else result = x / (1.0f + expf(-1.702f * x));
+    return __float2half_rn(result);
+}
+
+// bias_geglu_kernel: out = half_rn((float(yv) + float(bv)) * gelu(float(yg) + float(bg))).
+__device__ __forceinline__ __half finish_geglu(__half y_value, __half bias_value, __half y_gate,
+                                               __half bias_gate) {
+    const float value = __half2float(y_value) + __half2float(bias_value);
+    const float gate = __half2float(y_gate) + __half2float(bias_gate);
+    return __float2half_rn(value * gelu_erf(gate));
+}
+
+}  // namespace sdxlq

@@ -1,0 +1,62 @@
+// Job tables of the quantiser kernels (host <-> device).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace sdxlq {
+
+// One [m, k] matrix to rotate + quantise row-wise to INT8.
+struct QuantInt8Job {
+    const void* x;               // FP16 or FP32 [m, k]
+    int8_t* xq;                  // [m, k]
+    float* scales;               // [m]
+    uint32_t m, k;
+    uint32_t stages;             // log4(group size): 0 = no rotation, 1..4 = groups of 4..256
+    uint32_t threads_per_row;    // 4 * ceil(k / 256)
+    uint32_t rows_per_block;     // block threads / threads_per_row
+    uint32_t x_is_f32;
+    uint32_t vector_ok;          // rows 16-byte aligned: 16-byte loads, 8-byte stores
+    uint32_t first_block;        // first block of this job inside a grouped launch
+    uint32_t num_blocks;
+    uint32_t pad;
+};
+
+struct QuantInt8Launch {
+    const QuantInt8Job* jobs;    // device table (grouped) or null (`single` is used)
+    uint32_t num_jobs;
+    uint32_t pad;
+    QuantInt8Job single;
+};
+
+// One tensor to quantise to FP8 with a tensor-wide dynamic scale.
+struct QuantFp8Job {
+    const void* x;               // FP16, `count` elements
+    uint8_t* q;                  // `count` bytes
+    float* scale_out;            // 1 float: the dequantisation scale
+    uint64_t count;
+    uint32_t fmt;                // 0 = E4M3, 1 = E5M2
+    uint32_t vector_ok;
+    uint32_t first_block;
+    uint32_t num_blocks;
+};
+
+struct QuantFp8Launch {
+    const QuantFp8Job* jobs;     // device table (grouped) or null
+    uint32_t num_jobs;
+    uint32_t clear_count;        // amax words of the other parity to clear for the call after next
+    uint32_t* clear_bits;
+    uint32_t* amax_bits;         // one scratch word per job, all zero on entry of the amax kernel
+    QuantFp8Job single;
+};
+
+cudaError_t launch_rotate_quantize_int8(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
+                                        cudaStream_t stream);
+cudaError_t launch_fp8_quantize(const QuantFp8Launch& launch, uint32_t blocks, cudaStream_t stream);
+cudaError_t launch_fp8_weight_pack(const void* source, int32_t dtype, uint32_t n, uint32_t k, uint32_t fmt,
+                                   uint32_t per_channel, uint32_t k_major, uint8_t* destination,
+                                   float* scales, cudaStream_t stream);
+cudaError_t launch_fill_f32(float* values, uint32_t count, float value, cudaStream_t stream);
+
+}  // namespace sdxlq
