@@ -129,10 +129,10 @@ def load_library() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    path = library_path()
+    path = os.environ.get("SDXLQ_LIBRARY") or library_path()
     if not os.path.exists(path):
-        raise CudaError(f"{path} is missing: build it with `python -m` build step "
-                        "(__graft_entry__.build()); there is no CPU fallback", STATUS_CUDA)
+        raise CudaError(f"{path} is missing: build it first (build() of this package, or "
+                        "__graft_entry__.build()); there is no CPU fallback", STATUS_CUDA)
     lib = ctypes.CDLL(path)
     vp, i32, u32, u64, sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_size_t
     lib.sdxlq_context_create.argtypes = [ctypes.c_int, vp, sz, ctypes.POINTER(vp)]

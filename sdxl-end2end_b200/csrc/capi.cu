@@ -25,9 +25,14 @@
 namespace sdxlq {
 cudaError_t launch_umma_gemm(const GemmLaunchParams& params, uint32_t grid, size_t dynamic_smem,
                              cudaStream_t stream, size_t* attribute_bytes);
+size_t umma_gemm_control_bytes();
 cudaError_t launch_small_linear(const void* a, const void* b, const EpilogueParams& ep, uint32_t k_major,
                                 cudaStream_t stream);
 cudaError_t launch_bounded_wait_probe(uint32_t* error_word, long long limit_cycles, cudaStream_t stream);
+cudaError_t launch_int8_plain_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t max_vectors,
+                                   cudaStream_t stream);
+cudaError_t launch_int8_rotated_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
+                                     uint32_t stages, cudaStream_t stream);
 }  // namespace sdxlq
 
 using namespace sdxlq;
@@ -37,7 +42,6 @@ namespace {
 constexpr size_t kDefaultWorkspace = size_t(256) << 20;
 constexpr uint32_t kMaxFp8Jobs = 4096;
 constexpr size_t kSmemLimit = 232448;      // 227 KiB opt-in shared memory per CTA on sm_100
-constexpr size_t kControlBytes = 5120;     // barriers, staged column operands, alignment slack
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -229,14 +233,23 @@ struct SmallCall {
     uint32_t k_major;
 };
 
+// INT8 quantiser jobs of one kernel flavour (one launch each).
+struct Int8JobSet {
+    std::vector<QuantInt8Job> jobs;
+    uint32_t blocks = 0;
+    uint32_t threads = 256;
+    uint32_t max_vectors = 0;      // plain rows: most 16-byte vectors a lane holds
+    uint32_t stage_mask = 0;       // rotated rows: bit s set when a job has `s` butterfly stages
+};
+
+enum Int8Flavour { INT8_GENERIC = 0, INT8_PLAIN = 1, INT8_ROTATED = 2, INT8_FLAVOURS = 3 };
+
 struct Prepared {
-    std::vector<QuantInt8Job> int8_jobs;
+    Int8JobSet int8[INT8_FLAVOURS];
     std::vector<QuantFp8Job> fp8_jobs;
     std::vector<GemmProblem> problems;
     std::vector<TileRef> tiles;
     std::vector<SmallCall> small;
-    uint32_t int8_blocks = 0;
-    uint32_t int8_threads = 256;
     uint32_t fp8_blocks = 0;
     uint32_t max_tile_n = 0;
     uint32_t int8_linears = 0;
@@ -269,18 +282,70 @@ int add_int8_job(sdxlq_context* ctx, Prepared& prep, const void* x, bool x_is_f3
     job.stages = group_stages(group);
     job.threads_per_row = 4 * static_cast<uint32_t>((k + 255) / 256);
     if (job.threads_per_row > 256) return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE, "INT8 activation rows longer than 16384 are not supported");
-    const uint32_t threads = grouped ? 256 : best_int8_block(job.threads_per_row);
-    if (!grouped) prep.int8_threads = threads;
-    job.rows_per_block = threads / job.threads_per_row;
     job.x_is_f32 = x_is_f32 ? 1 : 0;
     const size_t element = x_is_f32 ? 4 : 2;
     job.vector_ok = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && ((k * element) % 16 == 0) &&
                     (reinterpret_cast<uintptr_t>(xq) % 8 == 0) && (k % 8 == 0);
-    job.first_block = prep.int8_blocks;
+    // FP16 rows with a 16-byte pitch take the throughput kernels; everything else the general one.
+    const bool fast = !x_is_f32 && job.vector_ok;
+    Int8Flavour flavour = INT8_GENERIC;
+    if (fast && job.stages == 0 && k <= 5120) flavour = INT8_PLAIN;
+    else if (fast && job.stages != 0) flavour = INT8_ROTATED;
+    Int8JobSet& set = prep.int8[flavour];
+    if (flavour == INT8_PLAIN) {
+        job.rows_per_block = 8;                     // one warp per row, 256 threads
+        set.max_vectors = std::max<uint32_t>(set.max_vectors, static_cast<uint32_t>((k / 8 + 31) / 32));
+    } else {
+        const uint32_t threads = grouped ? 256 : best_int8_block(job.threads_per_row);
+        if (!grouped) set.threads = threads;
+        job.rows_per_block = threads / job.threads_per_row;
+        if (flavour == INT8_ROTATED) set.stage_mask |= 1u << job.stages;
+    }
+    job.first_block = set.blocks;
     job.num_blocks = static_cast<uint32_t>((m + job.rows_per_block - 1) / job.rows_per_block);
-    prep.int8_blocks += job.num_blocks;
-    prep.int8_jobs.push_back(job);
+    set.blocks += job.num_blocks;
+    set.jobs.push_back(job);
     return SDXLQ_OK;
+}
+
+// Launches the INT8 activation quantisers of a prepared set: one launch per kernel flavour (and
+// per rotation group size). `tables` holds the device copies of the job tables, or nulls.
+int run_int8_quantisers(sdxlq_context* ctx, const Prepared& prep, QuantInt8Job* const tables[INT8_FLAVOURS]) {
+    for (int flavour = 0; flavour < INT8_FLAVOURS; ++flavour) {
+        const Int8JobSet& set = prep.int8[flavour];
+        if (set.jobs.empty()) continue;
+        QuantInt8Launch launch{};
+        launch.jobs = tables != nullptr ? tables[flavour] : nullptr;
+        launch.num_jobs = static_cast<uint32_t>(set.jobs.size());
+        launch.single = set.jobs[0];
+        if (launch.jobs == nullptr && set.jobs.size() != 1) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "internal: job table missing");
+        cudaError_t error = cudaSuccess;
+        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_INT8);
+        if (flavour == INT8_GENERIC) {
+            error = launch_rotate_quantize_int8(launch, set.blocks, set.threads, ctx->stream);
+        } else if (flavour == INT8_PLAIN) {
+            error = launch_int8_plain_rows(launch, set.blocks, set.max_vectors, ctx->stream);
+        } else {
+            for (uint32_t stages = 1; stages <= 4 && error == cudaSuccess; ++stages) {
+                if (set.stage_mask & (1u << stages)) {
+                    error = launch_int8_rotated_rows(launch, set.blocks, set.threads, stages, ctx->stream);
+                }
+            }
+        }
+        if (error != cudaSuccess) return fail_cuda(ctx, error, "INT8 activation quantise launch");
+    }
+    return SDXLQ_OK;
+}
+
+int int8_quantiser_launches(const Prepared& prep) {
+    int launches = 0;
+    for (int flavour = 0; flavour < INT8_FLAVOURS; ++flavour) {
+        const Int8JobSet& set = prep.int8[flavour];
+        if (set.jobs.empty()) continue;
+        if (flavour != INT8_ROTATED) { ++launches; continue; }
+        for (uint32_t stages = 1; stages <= 4; ++stages) launches += (set.stage_mask >> stages) & 1u;
+    }
+    return launches;
 }
 
 void add_fp8_job(Prepared& prep, const void* x, uint64_t count, uint32_t fmt, uint8_t* q, float* scale_out) {
@@ -426,8 +491,9 @@ struct GemmGeometry {
 GemmGeometry gemm_geometry(uint32_t max_tile_n) {
     GemmGeometry g{};
     g.stage_bytes = (kTileM + max_tile_n) * kTileKBytes;
-    g.num_stages = static_cast<uint32_t>(std::min<size_t>(8, (kSmemLimit - kControlBytes) / g.stage_bytes));
-    g.dynamic_smem = kControlBytes + static_cast<size_t>(g.num_stages) * g.stage_bytes;
+    const size_t control_bytes = umma_gemm_control_bytes();   // barriers, staged column operands, alignment slack
+    g.num_stages = static_cast<uint32_t>(std::min<size_t>(8, (kSmemLimit - control_bytes) / g.stage_bytes));
+    g.dynamic_smem = control_bytes + static_cast<size_t>(g.num_stages) * g.stage_bytes;
     return g;
 }
 
@@ -470,7 +536,7 @@ struct sdxlq_group_plan {
     Prepared prep;
     GemmProblem* device_problems = nullptr;
     TileRef* device_tiles = nullptr;
-    QuantInt8Job* device_int8_jobs = nullptr;
+    QuantInt8Job* device_int8_jobs[INT8_FLAVOURS] = {nullptr, nullptr, nullptr};
     QuantFp8Job* device_fp8_jobs = nullptr;
     int device = 0;
 };
@@ -601,15 +667,8 @@ int sdxlq_linear(sdxlq_context* ctx, const sdxlq_linear_desc* desc) {
     Prepared prep;
     int status = prepare(ctx, desc, 1, false, prep);
     if (status != SDXLQ_OK) return status;
-    if (!prep.int8_jobs.empty()) {
-        QuantInt8Launch launch{};
-        launch.jobs = nullptr;
-        launch.num_jobs = 1;
-        launch.single = prep.int8_jobs[0];
-        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_INT8);
-        const cudaError_t error = launch_rotate_quantize_int8(launch, prep.int8_blocks, prep.int8_threads, ctx->stream);
-        if (error != cudaSuccess) return fail_cuda(ctx, error, "INT8 activation quantise launch");
-    }
+    status = run_int8_quantisers(ctx, prep, nullptr);
+    if (status != SDXLQ_OK) return status;
     if (!prep.fp8_jobs.empty()) {
         const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, nullptr);
         LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8);
@@ -658,7 +717,8 @@ int sdxlq_group_plan_create(sdxlq_context* ctx, const sdxlq_linear_desc* descs, 
         return cudaMemcpy(*destination, host.data(), host.size() * sizeof(T), cudaMemcpyHostToDevice) == cudaSuccess;
     };
     if (!upload(&plan->device_problems, prep.problems) || !upload(&plan->device_tiles, prep.tiles) ||
-        !upload(&plan->device_int8_jobs, prep.int8_jobs) || !upload(&plan->device_fp8_jobs, prep.fp8_jobs)) {
+        !upload(&plan->device_int8_jobs[0], prep.int8[0].jobs) || !upload(&plan->device_int8_jobs[1], prep.int8[1].jobs) ||
+        !upload(&plan->device_int8_jobs[2], prep.int8[2].jobs) || !upload(&plan->device_fp8_jobs, prep.fp8_jobs)) {
         sdxlq_group_plan_destroy(plan);
         return fail(ctx, SDXLQ_ERR_CUDA, "grouped plan: device table allocation failed");
     }
@@ -669,14 +729,9 @@ int sdxlq_group_plan_create(sdxlq_context* ctx, const sdxlq_linear_desc* descs, 
 int sdxlq_group_plan_run(sdxlq_context* ctx, sdxlq_group_plan* plan) {
     if (ctx == nullptr || plan == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
     Prepared& prep = plan->prep;
-    if (!prep.int8_jobs.empty()) {
-        QuantInt8Launch launch{};
-        launch.jobs = plan->device_int8_jobs;
-        launch.num_jobs = static_cast<uint32_t>(prep.int8_jobs.size());
-        launch.single = prep.int8_jobs[0];
-        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_INT8);
-        const cudaError_t error = launch_rotate_quantize_int8(launch, prep.int8_blocks, 256, ctx->stream);
-        if (error != cudaSuccess) return fail_cuda(ctx, error, "grouped INT8 activation quantise launch");
+    {
+        const int quantise_status = run_int8_quantisers(ctx, prep, plan->device_int8_jobs);
+        if (quantise_status != SDXLQ_OK) return quantise_status;
     }
     if (!prep.fp8_jobs.empty()) {
         const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, plan->device_fp8_jobs);
@@ -711,7 +766,7 @@ int sdxlq_group_plan_run(sdxlq_context* ctx, sdxlq_group_plan* plan) {
 int sdxlq_group_plan_launches(const sdxlq_group_plan* plan) {
     if (plan == nullptr) return 0;
     const Prepared& prep = plan->prep;
-    return (prep.int8_jobs.empty() ? 0 : 1) + (prep.fp8_jobs.empty() ? 0 : 2) + (prep.problems.empty() ? 0 : 1) +
+    return int8_quantiser_launches(prep) + (prep.fp8_jobs.empty() ? 0 : 2) + (prep.problems.empty() ? 0 : 1) +
            static_cast<int>(prep.small.size());
 }
 
@@ -720,7 +775,7 @@ void sdxlq_group_plan_destroy(sdxlq_group_plan* plan) {
     cudaSetDevice(plan->device);
     cudaFree(plan->device_problems);
     cudaFree(plan->device_tiles);
-    cudaFree(plan->device_int8_jobs);
+    for (QuantInt8Job* table : plan->device_int8_jobs) cudaFree(table);
     cudaFree(plan->device_fp8_jobs);
     delete plan;
 }
@@ -753,13 +808,7 @@ int sdxlq_quantize_act_int8(sdxlq_context* ctx, const void* x, int32_t x_dtype, 
     Prepared prep;
     const int status = add_int8_job(ctx, prep, x, x_dtype == SDXLQ_FP32, m, k, convrot_group_size, xq, scales, false);
     if (status != SDXLQ_OK) return status;
-    QuantInt8Launch launch{};
-    launch.num_jobs = 1;
-    launch.single = prep.int8_jobs[0];
-    LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_INT8);
-    const cudaError_t error = launch_rotate_quantize_int8(launch, prep.int8_blocks, prep.int8_threads, ctx->stream);
-    if (error != cudaSuccess) return fail_cuda(ctx, error, "INT8 activation quantise launch");
-    return SDXLQ_OK;
+    return run_int8_quantisers(ctx, prep, nullptr);
 }
 
 int sdxlq_quantize_act_fp8(sdxlq_context* ctx, const void* x_f16, uint64_t count, int32_t fmt, uint8_t* q,

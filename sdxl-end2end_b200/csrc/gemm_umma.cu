@@ -24,7 +24,11 @@ namespace sdxlq {
 namespace {
 
 constexpr uint32_t kMaxStages = 8;
-constexpr uint32_t kEpilogueWarps = 8;                       // two per TMEM lane quadrant
+#ifndef SDXLQ_EPILOGUE_WARPS
+#define SDXLQ_EPILOGUE_WARPS 8
+#endif
+constexpr uint32_t kEpilogueWarps = SDXLQ_EPILOGUE_WARPS;    // a multiple of 4: warps per TMEM lane quadrant x 4
+constexpr uint32_t kWarpsPerQuadrant = kEpilogueWarps / 4;
 constexpr uint32_t kThreads = 64 + 32 * kEpilogueWarps;      // producer warp + MMA warp + epilogue
 
 struct alignas(16) Control {
@@ -38,7 +42,8 @@ struct alignas(16) Control {
     // Per-tile epilogue operands staged by the epilogue warps, one slot per accumulator buffer:
     // the weight scale and the bias of every accumulator column of the tile.
     alignas(16) float column_scale[2][kMaxTileN];
-    alignas(16) __half column_bias[2][kMaxTileN];
+    alignas(16) float column_bias[2][kMaxTileN];         // the FP16 bias widened to FP32 (exact)
+    alignas(16) __half column_bias_half[2][kMaxTileN];
 };
 
 // What the producer and the MMA issuer need to know about a tile, held in registers.
@@ -97,7 +102,8 @@ __device__ __forceinline__ void epilogue_barrier() {
 // Column j of a GEGLU tile is value column n0 + j for j < tile_n / 2 and gate column
 // n_out + n0 + (j - tile_n / 2) otherwise. Columns past the matrix edge get scale 0, bias 0.
 __device__ __forceinline__ void stage_columns(const EpilogueParams& ep, uint32_t tile_n, uint32_t tile_n_index,
-                                              float* column_scale, __half* column_bias, uint32_t thread) {
+                                              float* column_scale, float* column_bias, __half* column_bias_half,
+                                              uint32_t thread) {
     const bool geglu = ep.activation == ACT_GEGLU;
     const bool scaled = ep.kind != KIND_F16;
     const bool per_channel = scaled && ep.w_scale_per_channel != 0;
@@ -116,7 +122,8 @@ __device__ __forceinline__ void stage_columns(const EpilogueParams& ep, uint32_t
             if (ep.bias != nullptr) bias = ep.bias[column];
         }
         column_scale[j] = scale;
-        column_bias[j] = bias;
+        column_bias[j] = __half2float(bias);
+        column_bias_half[j] = bias;
     }
 }
 
@@ -147,25 +154,42 @@ __device__ __forceinline__ void store_row_chunk(__half* y, uint32_t n_out, bool 
     }
 }
 
-// Reads W staged scales / biases starting at column j0 (a multiple of 8) with 16-byte loads.
+// Reads W consecutive staged FP32 values starting at column j0 (a multiple of 4) with 16-byte loads.
 template <int W>
-__device__ __forceinline__ void read_staged(const float* column_scale, const __half* column_bias, uint32_t j0,
-                                            float (&scale)[W], uint32_t (&bias_words)[W / 2]) {
+__device__ __forceinline__ void read_staged(const float* values, uint32_t j0, float (&out)[W]) {
 #pragma unroll
     for (int i = 0; i < W / 4; ++i) {
-        const float4 v = *reinterpret_cast<const float4*>(column_scale + j0 + 4 * i);
-        scale[4 * i] = v.x; scale[4 * i + 1] = v.y; scale[4 * i + 2] = v.z; scale[4 * i + 3] = v.w;
-    }
-#pragma unroll
-    for (int i = 0; i < W / 8; ++i) {
-        const uint4 v = *reinterpret_cast<const uint4*>(column_bias + j0 + 8 * i);
-        bias_words[4 * i] = v.x; bias_words[4 * i + 1] = v.y; bias_words[4 * i + 2] = v.z; bias_words[4 * i + 3] = v.w;
+        const float4 v = *reinterpret_cast<const float4*>(values + j0 + 4 * i);
+        out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
     }
 }
 
+// W staged FP16 values, packed two per word.
+template <int W>
+__device__ __forceinline__ void read_staged_half(const __half* values, uint32_t j0, uint32_t (&out)[W / 2]) {
+#pragma unroll
+    for (int i = 0; i < W / 8; ++i) {
+        const uint4 v = *reinterpret_cast<const uint4*>(values + j0 + 8 * i);
+        out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
+    }
+}
+
+// The accumulator scaled to the projection value before its FP16 rounding.
 template <uint32_t Kind>
-__device__ __forceinline__ __half project(uint32_t acc_bits, float a_scale, float w_scale) {
-    return project_to_half(acc_bits, Kind == 1 ? static_cast<uint32_t>(KIND_E4M3) : Kind, a_scale, w_scale);
+__device__ __forceinline__ float dequantise(uint32_t acc_bits, float a_scale, float w_scale) {
+    if (Kind == KIND_I8) return __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(acc_bits)), a_scale), w_scale);
+    if (Kind == KIND_F16) return __uint_as_float(acc_bits);
+    return __fmul_rn(__fmul_rn(__uint_as_float(acc_bits), a_scale), w_scale);
+}
+
+// Two FP32 values -> two FP16 values in one word (round to nearest even), .x in the low half.
+__device__ __forceinline__ uint32_t to_half2_bits(float lo, float hi) {
+    const __half2 packed = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&packed);
+}
+
+__device__ __forceinline__ float2 from_half2_bits(uint32_t word) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&word));
 }
 
 // Everything one epilogue warp needs for its share of a tile, passed by value to the
@@ -174,16 +198,22 @@ struct EpilogueTile {
     __half* y;
     int32_t* acc_out;
     const float* column_scale;      // shared memory
-    const __half* column_bias;      // shared memory
+    const float* column_bias;       // shared memory, FP32
+    const __half* column_bias_half; // shared memory, FP16
     float a_scale;
     uint32_t n, n_out;
     uint32_t tile_n, n0;            // accumulator columns of the tile; first output column
     uint32_t row, tmem_row;
-    uint32_t chunk_first;           // 0 or 1: which of the two warps of the quadrant
+    uint32_t chunk_first;           // which of the warps of this TMEM lane quadrant
     uint32_t flags;                 // bit 0 row in range, bit 1 has bias, bit 2 vector stores
 };
 
 // Drains this warp's share of one accumulator tile. Kind: 0 INT8, 1 FP8 (either format), 3 FP16.
+// Arithmetic per output, as the reference runs it after the GEMM:
+//   y = half_rn(dequantised accumulator)
+//   no activation : __hadd(y, bias)                           (add_last_dim_bias_kernel)
+//   SiLU/GELU/QuickGELU : half_rn(act(float(y) + float(bias))) (bias_activation_in_place_kernel)
+//   GEGLU : half_rn((float(y_v) + float(b_v)) * gelu(float(y_g) + float(b_g)))   (bias_geglu_kernel)
 template <uint32_t Kind, uint32_t Act>
 __device__ __noinline__ void epilogue_tile(const EpilogueTile t) {
     const bool row_ok = (t.flags & 1u) != 0;
@@ -192,14 +222,13 @@ __device__ __noinline__ void epilogue_tile(const EpilogueTile t) {
     int32_t* const acc_out = Kind == KIND_I8 ? t.acc_out : nullptr;
     if (Act != ACT_GEGLU) {
         constexpr int W = 16;
-        for (uint32_t c0 = t.chunk_first * W; c0 < t.tile_n; c0 += 2 * W) {
+        for (uint32_t c0 = t.chunk_first * W; c0 < t.tile_n; c0 += kWarpsPerQuadrant * W) {
             const uint32_t col0 = t.n0 + c0;
             if (col0 >= t.n) break;
             uint32_t acc[W];
             ptx::tmem_ld_32x32b_x16(t.tmem_row + c0, acc);
             float w_scale[W];
-            uint32_t bias_words[W / 2];
-            read_staged<W>(t.column_scale, t.column_bias, c0, w_scale, bias_words);
+            read_staged<W>(t.column_scale, c0, w_scale);
             ptx::tmem_ld_wait();
             if (acc_out != nullptr && row_ok) {
                 int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n + col0;
@@ -211,27 +240,45 @@ __device__ __noinline__ void epilogue_tile(const EpilogueTile t) {
             uint32_t out_words[W / 2];
 #pragma unroll
             for (int i = 0; i < W; i += 2) {
-                const __half y0 = project<Kind>(acc[i], t.a_scale, w_scale[i]);
-                const __half y1 = project<Kind>(acc[i + 1], t.a_scale, w_scale[i + 1]);
-                const __half r0 = finish_scalar(y0, has_bias, packed_half(bias_words[i >> 1], 0), Act);
-                const __half r1 = finish_scalar(y1, has_bias, packed_half(bias_words[i >> 1], 1), Act);
-                out_words[i >> 1] = pack_halves(r0, r1);
+                out_words[i >> 1] = to_half2_bits(dequantise<Kind>(acc[i], t.a_scale, w_scale[i]),
+                                                  dequantise<Kind>(acc[i + 1], t.a_scale, w_scale[i + 1]));
+            }
+            if (has_bias) {
+                if (Act == ACT_NONE) {
+                    uint32_t bias_words[W / 2];
+                    read_staged_half<W>(t.column_bias_half, c0, bias_words);
+#pragma unroll
+                    for (int i = 0; i < W / 2; ++i) {
+                        const __half2 sum = __hadd2(*reinterpret_cast<const __half2*>(&out_words[i]),
+                                                    *reinterpret_cast<const __half2*>(&bias_words[i]));
+                        out_words[i] = *reinterpret_cast<const uint32_t*>(&sum);
+                    }
+                } else {
+                    float bias[W];
+                    read_staged<W>(t.column_bias, c0, bias);
+#pragma unroll
+                    for (int i = 0; i < W / 2; ++i) {
+                        const float2 y = from_half2_bits(out_words[i]);
+                        out_words[i] = to_half2_bits(activate(y.x + bias[2 * i], Act), activate(y.y + bias[2 * i + 1], Act));
+                    }
+                }
             }
             if (row_ok) store_row_chunk<W>(t.y, t.n_out, store_vector, t.row, col0, out_words);
         }
     } else {
         constexpr int W = 8;
         const uint32_t half = t.tile_n / 2;
-        for (uint32_t c0 = t.chunk_first * W; c0 < half; c0 += 2 * W) {
+        for (uint32_t c0 = t.chunk_first * W; c0 < half; c0 += kWarpsPerQuadrant * W) {
             const uint32_t col0 = t.n0 + c0;
             if (col0 >= t.n_out) break;
             uint32_t acc_value[W], acc_gate[W];
             ptx::tmem_ld_32x32b_x8(t.tmem_row + c0, acc_value);
             ptx::tmem_ld_32x32b_x8(t.tmem_row + half + c0, acc_gate);
-            float w_value[W], w_gate[W];
-            uint32_t b_value[W / 2], b_gate[W / 2];
-            read_staged<W>(t.column_scale, t.column_bias, c0, w_value, b_value);
-            read_staged<W>(t.column_scale, t.column_bias, half + c0, w_gate, b_gate);
+            float w_value[W], w_gate[W], b_value[W], b_gate[W];
+            read_staged<W>(t.column_scale, c0, w_value);
+            read_staged<W>(t.column_scale, half + c0, w_gate);
+            read_staged<W>(t.column_bias, c0, b_value);
+            read_staged<W>(t.column_bias, half + c0, b_gate);
             ptx::tmem_ld_wait();
             if (acc_out != nullptr && row_ok) {
                 int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n;
@@ -246,14 +293,16 @@ __device__ __noinline__ void epilogue_tile(const EpilogueTile t) {
             uint32_t out_words[W / 2];
 #pragma unroll
             for (int i = 0; i < W; i += 2) {
-                __half r[2];
+                float result[2];
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
-                    const __half y_value = project<Kind>(acc_value[i + j], t.a_scale, w_value[i + j]);
-                    const __half y_gate = project<Kind>(acc_gate[i + j], t.a_scale, w_gate[i + j]);
-                    r[j] = finish_geglu(y_value, packed_half(b_value[i >> 1], j), y_gate, packed_half(b_gate[i >> 1], j));
+                    // one packed conversion rounds the value and the gate projection to FP16
+                    const float2 y = from_half2_bits(to_half2_bits(
+                        dequantise<Kind>(acc_value[i + j], t.a_scale, w_value[i + j]),
+                        dequantise<Kind>(acc_gate[i + j], t.a_scale, w_gate[i + j])));
+                    result[j] = (y.x + b_value[i + j]) * gelu_erf(y.y + b_gate[i + j]);
                 }
-                out_words[i >> 1] = pack_halves(r[0], r[1]);
+                out_words[i >> 1] = to_half2_bits(result[0], result[1]);
             }
             if (row_ok) store_row_chunk<W>(t.y, t.n_out, store_vector, t.row, col0, out_words);
         }
@@ -409,10 +458,10 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
         }
     } else {
         // ------------------------------- epilogue ------------------------------------------
-        // Warp w may touch TMEM lanes 32*(w % 4) .. +31. The two warps of a quadrant take the
-        // even and the odd column chunks of the tile.
+        // Warp w may touch TMEM lanes 32*(w % 4) .. +31. The warps of a quadrant take the column
+        // chunks of the tile round-robin.
         const uint32_t quadrant = warp & 3u;
-        const uint32_t chunk_first = (warp - 2u) >> 2;
+        const uint32_t chunk_first = (warp - 2u) >> 2;      // 0 .. kWarpsPerQuadrant - 1
         const uint32_t epilogue_thread = threadIdx.x - 64u;
         uint32_t iteration = 0;
         bool ok = true;
@@ -424,12 +473,13 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             // Stage this tile's column operands while the main loop is still running. The slot
             // was last read two tiles ago; every warp passed the previous tile's barrier since.
             stage_columns(ep, work.tile_n, work.tile_n_index, control->column_scale[buffer],
-                          control->column_bias[buffer], epilogue_thread);
+                          control->column_bias[buffer], control->column_bias_half[buffer], epilogue_thread);
             EpilogueTile tile;
             tile.y = ep.y;
             tile.acc_out = ep.acc_out;
             tile.column_scale = control->column_scale[buffer];
             tile.column_bias = control->column_bias[buffer];
+            tile.column_bias_half = control->column_bias_half[buffer];
             tile.n = ep.n;
             tile.n_out = ep.n_out;
             tile.tile_n = work.tile_n;
@@ -490,6 +540,10 @@ cudaError_t launch_bounded_wait_probe(uint32_t* error_word, long long limit_cycl
     sdxlq_bounded_wait_probe_kernel<<<1, 32, 0, stream>>>(error_word, limit_cycles);
     return cudaGetLastError();
 }
+
+// Shared memory in front of the pipeline stages: the control block plus the slack needed to align
+// the first stage to 1024 bytes.
+size_t umma_gemm_control_bytes() { return (sizeof(Control) + 1023u + 1023u) / 1024u * 1024u; }
 
 // Host-side launcher (called from the dispatch code). `attribute_bytes` remembers, per context,
 // the dynamic shared memory size the kernel has been opted into.

@@ -94,8 +94,42 @@ __device__ __forceinline__ __half project_to_half(uint32_t acc_bits, uint32_t ki
     return __float2half_rn(value);
 }
 
+// 1 + erf(x / sqrt 2) = 2 * Phi(x), from erfc(t) = 2^(t * r(t)) with t = |x| / sqrt 2 clamped to
+// 4.6 and r a degree-9 polynomial (least-squares fit of log2(erfc(t)) / t on Chebyshev nodes of
+// [0, 4.6]): relative error of erfc below 1.5e-6 for t < 3 and absolute error below 6e-7
+// everywhere, evaluated in FP32. For x >= 0 the result 2 - erfc(t) therefore carries an error
+// below 6e-7; for x < 0 it is erfc(t) itself, which keeps its relative accuracy in the tail where
+// the textbook 1 + erf(x) loses it to cancellation.
+__device__ __forceinline__ float one_plus_erf(float x) {
+    const float u = x * 0.7071067811865475f;
+    const float t = fminf(fabsf(u), 4.6f);
+    float r = -2.6164917699134094e-07f;
+    r = fmaf(r, t, 6.632982149312738e-06f);
+    r = fmaf(r, t, -7.087277481332421e-05f);
+    r = fmaf(r, t, 0.0003955792635679245f);
+    r = fmaf(r, t, -0.0009763258858583868f);
+    r = fmaf(r, t, -0.0020724914502352476f);
+    r = fmaf(r, t, 0.029831526800990105f);
+    r = fmaf(r, t, -0.14946085214614868f);
+    r = fmaf(r, t, -0.9181336760520935f);
+    r = fmaf(r, t, -1.6279360055923462f);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(r * t));
+    return u >= 0.0f ? 2.0f - e : e;
+}
+
+// gelu(x) = 0.5 * x * (1 + erf(x / sqrt 2)), the exact-erf GELU of the reference
+// (apply_linear_activation / bias_geglu_kernel, src/cuda/ops_kernels.cu:128-183).
 __device__ __forceinline__ float gelu_erf(float x) {
-    return 0.5f * x * (1.0f + erff(x * 0.7071067811865475f));
+    return (0.5f * x) * one_plus_erf(x);
+}
+
+// SiLU / GELU / QuickGELU on the FP32 value (ACT_NONE returns x).
+__device__ __forceinline__ float activate(float x, uint32_t activation) {
+    if (activation == ACT_SILU) return x / (1.0f + expf(-x));
+    if (activation == ACT_GELU) return gelu_erf(x);
+    if (activation == ACT_QUICK_GELU) return x / (1.0f + expf(-1.702f * x));
+    return x;
 }
 
 // Bias + activation on an FP16 projection, as the reference runs them after the GEMM:
@@ -104,12 +138,7 @@ __device__ __forceinline__ float gelu_erf(float x) {
 __device__ __forceinline__ __half finish_scalar(__half y, bool has_bias, __half bias, uint32_t activation) {
     if (!has_bias) return y;
     if (activation == ACT_NONE) return __hadd(y, bias);
-    const float x = __half2float(y) + __half2float(bias);
-    float result;
-    if (activation == ACT_SILU) result = x / (1.0f + expf(-x));
-    else if (activation == ACT_GELU) result = gelu_erf(x);
-    else result = x / (1.0f + expf(-1.702f * x));
-    return __float2half_rn(result);
+    return __float2half_rn(activate(__half2float(y) + __half2float(bias), activation));
 }
 
 // bias_geglu_kernel: out = half_rn((float(yv) + float(bv)) * gelu(float(yg) + float(bg))).
