@@ -152,6 +152,30 @@ void sdxlq_group_plan_destroy(sdxlq_group_plan* plan);
 /* Number of kernels one run of the plan launches. */
 int sdxlq_group_plan_launches(const sdxlq_group_plan* plan);
 
+/* The same Linear for callers that must not allocate device memory. It has no counterpart in
+ * the reference (whose Ops::linear takes every temporary from the Runtime arena).
+ *
+ * Some hosts of this library cannot call cudaMalloc when they need a projection: an engine that
+ * has handed all of the GPU's memory to its own pool and forbids driver allocations afterwards,
+ * a plugin that runs inside a callback where the allocator's lock is already held, or a service
+ * whose steady state is audited to be allocation-free. sdxlq_context_create allocates its
+ * workspace, so it is off limits for them. This entry point needs no context: the quantised
+ * activations (INT8: M*K bytes + 4*M; FP8: M*K bytes + 4) go to a 16 MiB array that is part of the
+ * library image on every GPU that loads it, and nothing in the call allocates or frees device
+ * memory. Projections that need more scratch than that are rejected with SDXLQ_ERR_WORKSPACE and
+ * an explanatory message (FP16 weights need none and always fit).
+ *
+ *  - `device` must be the calling thread's current CUDA device. The first call on a device looks
+ *    up the array's device address and the device's properties; make that first call outside any
+ *    stream capture.
+ *  - All calls on one GPU share the array, which still holds the previous call's data when the next
+ *    one starts. Each call overwrites what it reads, but two calls whose kernels overlap on the GPU
+ *    (different streams, no ordering between them) race on it: order them.
+ *  - `message` (may be NULL) receives a NUL-terminated explanation when the status is not SDXLQ_OK.
+ *  - A bounded device-side wait that runs out is not reported by this entry point. */
+int sdxlq_linear_static(int device, void* stream, const sdxlq_linear_desc* desc, char* message,
+                        size_t message_capacity);
+
 /* ---- activation quantisers ---------------------------------------------------------------- */
 
 /* activation_amax_kernel + quantize_activation_kernel (int8_convrot.cu:265-353) in one pass:

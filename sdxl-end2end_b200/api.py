@@ -114,7 +114,7 @@ EXPORTED_SYMBOLS = [
     "sdxlq_group_plan_launches", "sdxlq_quantize_act_int8", "sdxlq_quantize_act_fp8",
     "sdxlq_pack_weight_int8", "sdxlq_pack_weight_fp8", "sdxlq_valid_convrot_group_size",
     "sdxlq_workspace_bytes", "sdxlq_build_info", "sdxlq_context_set_tile_n",
-    "sdxlq_selftest_bounded_wait", "sdxlq_profile_enable", "sdxlq_profile_read",
+    "sdxlq_selftest_bounded_wait", "sdxlq_profile_enable", "sdxlq_profile_read", "sdxlq_linear_static",
 ]
 
 _lib: Optional[ctypes.CDLL] = None
@@ -164,6 +164,7 @@ def load_library() -> ctypes.CDLL:
     lib.sdxlq_selftest_bounded_wait.argtypes = [vp, ctypes.c_longlong]
     lib.sdxlq_profile_enable.argtypes = [vp, ctypes.c_int]
     lib.sdxlq_profile_read.argtypes = [vp, ctypes.POINTER(_CKernelTimes)]
+    lib.sdxlq_linear_static.argtypes = [ctypes.c_int, vp, ctypes.POINTER(_CLinearDesc), ctypes.c_char_p, sz]
     _lib = lib
     return lib
 

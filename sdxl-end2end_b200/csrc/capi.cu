@@ -17,6 +17,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <new>
 #include <string>
 #include <tuple>
@@ -183,7 +184,13 @@ int validate(sdxlq_context* ctx, const sdxlq_linear_desc& d) {
 }
 
 // ---- tile shape ------------------------------------------------------------------------------
-uint32_t choose_tile_n(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool geglu) {
+// Accumulator tile width (columns) for one projection.
+//  * A launch that fills the GPU several times over (grouped launches, big single projections) is
+//    bound by operand traffic into shared memory: a 128 x t tile moves (128 + t) bytes per k-byte
+//    for 128 * t MACs, so wider is better; the cost of a projection is ceil(N / t) * (128 + t)
+//    (padding of the last tile included).
+//  * A launch of few tiles is bound by how many SMs get work: minimise waves * (t + 32).
+uint32_t choose_tile_n(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool geglu, bool grouped) {
     const uint32_t step = geglu ? 32 : 16;
     if (ctx->forced_tile_n >= 16) {
         uint32_t forced = std::min<uint32_t>(kMaxTileN, static_cast<uint32_t>(ctx->forced_tile_n));
@@ -191,16 +198,22 @@ uint32_t choose_tile_n(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool ge
     }
     const uint32_t tiles_m = (m + kTileM - 1) / kTileM;
     const uint32_t sms = static_cast<uint32_t>(ctx->sm_count);
+    const uint32_t columns = geglu ? n / 2 : n;            // GEGLU: a tile holds t/2 value + t/2 gate columns
+    const uint64_t tiles_at_widest = static_cast<uint64_t>(tiles_m) * ((columns + (geglu ? 127 : 255)) / (geglu ? 128 : 256));
+    const bool traffic_bound = grouped ? tiles_m >= 2 : tiles_at_widest >= 3ull * sms;
     uint32_t best = step;
     double best_cost = 1e300;
     for (uint32_t tile_n = kMaxTileN; tile_n >= step; tile_n -= step) {
-        // GEGLU: a tile holds tile_n/2 value columns and tile_n/2 gate columns.
-        const uint32_t columns = geglu ? n / 2 : n;
         const uint32_t per_tile = geglu ? tile_n / 2 : tile_n;
         const uint32_t tiles_n = (columns + per_tile - 1) / per_tile;
-        const uint64_t tiles = static_cast<uint64_t>(tiles_m) * tiles_n;
-        const uint64_t waves = (tiles + sms - 1) / sms;
-        const double cost = static_cast<double>(waves) * (tile_n + 32.0);
+        double cost;
+        if (traffic_bound) {
+            cost = static_cast<double>(tiles_n) * (128.0 + tile_n);
+        } else {
+            const uint64_t tiles = static_cast<uint64_t>(tiles_m) * tiles_n;
+            const uint64_t waves = (tiles + sms - 1) / sms;
+            cost = static_cast<double>(waves) * (tile_n + 32.0);
+        }
         if (cost < best_cost) { best_cost = cost; best = tile_n; }
         if (tile_n == step) break;
     }
@@ -445,7 +458,7 @@ int prepare(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count, bo
 
         GemmProblem problem{};
         problem.ep = ep;
-        problem.tile_n = choose_tile_n(ctx, ep.m, ep.n, geglu);
+        problem.tile_n = choose_tile_n(ctx, ep.m, ep.n, geglu, grouped);
         const uint32_t per_tile = geglu ? problem.tile_n / 2 : problem.tile_n;
         problem.tiles_m = (ep.m + kTileM - 1) / kTileM;
         problem.tiles_n = (ep.n_out + per_tile - 1) / per_tile;
@@ -911,3 +924,93 @@ int sdxlq_selftest_bounded_wait(sdxlq_context* ctx, long long limit_cycles) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free Linear
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;     // quantised-activation scratch, per GPU
+constexpr int kStaticMaxDevices = 16;
+
+// Scratch for the quantised activations and the control words (timeout flag, FP8 amax words) of
+// the allocation-free entry point. File-scope device arrays: every GPU that loads this library
+// holds them until the process exits. Zero-initialised when the module is loaded.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ __align__(256) uint32_t g_static_control[64 + 2 * kMaxFp8Jobs];
+
+struct StaticSlot {
+    bool ready = false;
+    sdxlq_context context;
+};
+
+StaticSlot g_static_slots[kStaticMaxDevices];
+std::mutex g_static_mutex;
+
+void copy_message(char* destination, size_t capacity, const std::string& text) {
+    if (destination == nullptr || capacity == 0) return;
+    const size_t length = std::min(capacity - 1, text.size());
+    std::memcpy(destination, text.data(), length);
+    destination[length] = '\0';
+}
+
+}  // namespace
+
+extern "C" int sdxlq_linear_static(int device, void* stream, const sdxlq_linear_desc* desc, char* message,
+                                   size_t message_capacity) {
+    copy_message(message, message_capacity, "");
+    if (desc == nullptr || device < 0 || device >= kStaticMaxDevices) {
+        copy_message(message, message_capacity, "sdxlq_linear_static: null descriptor or device index out of range");
+        return SDXLQ_ERR_INVALID_ARGUMENT;
+    }
+    int current = -1;
+    if (cudaGetDevice(&current) != cudaSuccess || current != device) {
+        copy_message(message, message_capacity, "sdxlq_linear_static: `device` must be the calling thread's current CUDA device");
+        return SDXLQ_ERR_INVALID_ARGUMENT;
+    }
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticSlot& slot = g_static_slots[device];
+    if (!slot.ready) {
+        // Once per device, with that device current: the array names above are host-side handles,
+        // not device addresses; the kernels need the addresses cudaGetSymbolAddress returns.
+        void* scratch = nullptr;
+        void* control = nullptr;
+        cudaError_t status = cudaGetSymbolAddress(&scratch, g_static_scratch);
+        if (status == cudaSuccess) status = cudaGetSymbolAddress(&control, g_static_control);
+        cudaDeviceProp properties{};
+        if (status == cudaSuccess) status = cudaGetDeviceProperties(&properties, device);
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult query{};
+        if (status == cudaSuccess) status = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &query);
+        if (status != cudaSuccess || scratch == nullptr || control == nullptr || entry == nullptr) {
+            copy_message(message, message_capacity,
+                         std::string("sdxlq_linear_static: set-up failed: ") + cudaGetErrorString(status));
+            return SDXLQ_ERR_CUDA;
+        }
+        if (properties.major != 10) {
+            copy_message(message, message_capacity, "sdxlq_linear_static: the kernels are built for sm_100a only");
+            return SDXLQ_ERR_UNSUPPORTED_SHAPE;
+        }
+        slot.context.device = device;
+        slot.context.sm_count = properties.multiProcessorCount;
+        slot.context.workspace = static_cast<uint8_t*>(scratch);
+        slot.context.workspace_bytes = kStaticScratchBytes;
+        slot.context.control = static_cast<uint32_t*>(control);
+        slot.context.encode = reinterpret_cast<EncodeTiledFn>(entry);
+        slot.ready = true;
+    }
+    const size_t needed = sdxlq_workspace_bytes(desc, 1);
+    if (needed > kStaticScratchBytes) {
+        char text[192];
+        std::snprintf(text, sizeof(text),
+                      "sdxlq_linear_static: this projection needs %zu bytes of scratch for its quantised activations, "
+                      "the static array holds %zu; use sdxlq_linear with a context instead",
+                      needed, kStaticScratchBytes);
+        copy_message(message, message_capacity, text);
+        return SDXLQ_ERR_WORKSPACE;
+    }
+    slot.context.stream = static_cast<cudaStream_t>(stream);
+    const int result = sdxlq_linear(&slot.context, desc);
+    if (result != SDXLQ_OK) copy_message(message, message_capacity, slot.context.last_error);
+    return result;
+}
