@@ -371,7 +371,8 @@ def main():
     gemm_ms, gemm_launches = kernel_times["gemm"]
     quant_ms = kernel_times["quant_int8"][0] + kernel_times["quant_fp8"][0]
     quant_launches = kernel_times["quant_int8"][1] + kernel_times["quant_fp8"][1]
-    gemm_ms_per_launch = gemm_ms / max(gemm_launches, 1)
+    gemm_launches_per_step = max(gemm_launches // max(args.steps, 1), 1)
+    gemm_ms_per_launch = gemm_ms / max(args.steps, 1)      # all GEMM launches of one step together
     eight_bit = kind in ("int8", "e4m3", "e5m2")
     tensor_peak = peaks["bf16_tflops"] * (2.0 if eight_bit else 1.0)
     achieved = ops_per_step / (gemm_ms_per_launch * 1e-3) / 1e12 if gemm_ms_per_launch > 0 else 0.0
@@ -383,7 +384,7 @@ def main():
         "frac": achieved / tensor_peak, "traffic": TRAFFIC_BYTES.get(args.workload),
         "peak_source": (f"{peaks['source']} bf16 {peaks['bf16_tflops']} TFLOP/s x2 for 8-bit operands" if eight_bit
                         else f"{peaks['source']} bf16"),
-        "launch_ms": gemm_ms_per_launch, "ops_per_launch": ops_per_step,
+        "launch_ms": gemm_ms_per_launch, "ops_per_launch": ops_per_step, "gemm_launches_per_step": gemm_launches_per_step,
         "quantize_kernel": {"bound": "hbm", "achieved": quant_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                             "bytes_per_step": quant_bytes, "ms_per_step": quant_ms_per_step},
     }

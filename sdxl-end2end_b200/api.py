@@ -115,6 +115,7 @@ EXPORTED_SYMBOLS = [
     "sdxlq_pack_weight_int8", "sdxlq_pack_weight_fp8", "sdxlq_valid_convrot_group_size",
     "sdxlq_workspace_bytes", "sdxlq_build_info", "sdxlq_context_set_tile_n",
     "sdxlq_selftest_bounded_wait", "sdxlq_profile_enable", "sdxlq_profile_read", "sdxlq_linear_static",
+    "sdxlq_context_set_pair_mode",
 ]
 
 _lib: Optional[ctypes.CDLL] = None
@@ -162,6 +163,7 @@ def load_library() -> ctypes.CDLL:
     lib.sdxlq_build_info.restype = ctypes.c_char_p
     lib.sdxlq_context_set_tile_n.argtypes = [vp, ctypes.c_int]
     lib.sdxlq_selftest_bounded_wait.argtypes = [vp, ctypes.c_longlong]
+    lib.sdxlq_context_set_pair_mode.argtypes = [vp, ctypes.c_int]
     lib.sdxlq_profile_enable.argtypes = [vp, ctypes.c_int]
     lib.sdxlq_profile_read.argtypes = [vp, ctypes.POINTER(_CKernelTimes)]
     lib.sdxlq_linear_static.argtypes = [ctypes.c_int, vp, ctypes.POINTER(_CLinearDesc), ctypes.c_char_p, sz]
@@ -310,6 +312,10 @@ class Context:
 
     def set_tile_n(self, tile_n: int) -> None:
         self.raise_for(self._lib.sdxlq_context_set_tile_n(self._handle, tile_n))
+
+    def set_pair_mode(self, mode: int) -> None:
+        """-1 automatic, 0 never use CTA pairs, 1 for every projection with more than 128 rows."""
+        self.raise_for(self._lib.sdxlq_context_set_pair_mode(self._handle, mode))
 
     def int8_execution_stats(self) -> dict:
         stats = _CStats()

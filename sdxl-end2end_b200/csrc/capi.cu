@@ -25,7 +25,7 @@
 
 namespace sdxlq {
 cudaError_t launch_umma_gemm(const GemmLaunchParams& params, uint32_t grid, size_t dynamic_smem,
-                             cudaStream_t stream, size_t* attribute_bytes);
+                             cudaStream_t stream, size_t* attribute_bytes, bool pair);
 size_t umma_gemm_control_bytes();
 cudaError_t launch_small_linear(const void* a, const void* b, const EpilogueParams& ep, uint32_t k_major,
                                 cudaStream_t stream);
@@ -62,7 +62,9 @@ struct sdxlq_context {
     uint32_t fp8_parity = 0;
     uint32_t fp8_dirty[2] = {0, 0};        // amax words of each parity left non-zero
     int sm_count = 148;
-    size_t umma_smem_attribute = 0;
+    size_t umma_smem_attribute[2] = {0, 0};   // per kernel flavour: single CTA, CTA pair
+    int pair_mode = -1;                       // -1 automatic, 0 never use CTA pairs, 1 whenever possible
+    uint32_t diagnostic_skip = 0;             // SDXLQ_DIAGNOSTIC_SKIP: tuning aid, see GemmLaunchParams
     long long wait_limit_cycles = 4000000000LL;
     int forced_tile_n = 0;
     EncodeTiledFn encode = nullptr;
@@ -184,38 +186,51 @@ int validate(sdxlq_context* ctx, const sdxlq_linear_desc& d) {
 }
 
 // ---- tile shape ------------------------------------------------------------------------------
-// Accumulator tile width (columns) for one projection.
+// Tile shape for one projection: accumulator width (columns) and whether a CTA pair
+// (cta_group::2, 256-row tiles) works on it.
 //  * A launch that fills the GPU several times over (grouped launches, big single projections) is
-//    bound by operand traffic into shared memory: a 128 x t tile moves (128 + t) bytes per k-byte
-//    for 128 * t MACs, so wider is better; the cost of a projection is ceil(N / t) * (128 + t)
-//    (padding of the last tile included).
-//  * A launch of few tiles is bound by how many SMs get work: minimise waves * (t + 32).
-uint32_t choose_tile_n(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool geglu, bool grouped) {
+//    bound by operand traffic into shared memory. A single CTA moves (128 + t) bytes per k-byte for
+//    128 * t MACs; a CTA pair moves (256 + t) for 256 * t. Cost of a projection per 128 rows:
+//    ceil(N / t) * (128 + t), or ceil(N / t) * (128 + t / 2) for a pair (last-tile padding included).
+//  * A launch of few tiles is bound by how many SMs get work: single CTAs, minimise waves * (t + 32).
+struct TileChoice {
+    uint32_t tile_n;
+    bool pair;
+};
+
+TileChoice choose_tile(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool geglu, bool grouped) {
     const uint32_t step = geglu ? 32 : 16;
-    if (ctx->forced_tile_n >= 16) {
-        uint32_t forced = std::min<uint32_t>(kMaxTileN, static_cast<uint32_t>(ctx->forced_tile_n));
-        return std::max(step, forced / step * step);
-    }
     const uint32_t tiles_m = (m + kTileM - 1) / kTileM;
     const uint32_t sms = static_cast<uint32_t>(ctx->sm_count);
     const uint32_t columns = geglu ? n / 2 : n;            // GEGLU: a tile holds t/2 value + t/2 gate columns
     const uint64_t tiles_at_widest = static_cast<uint64_t>(tiles_m) * ((columns + (geglu ? 127 : 255)) / (geglu ? 128 : 256));
     const bool traffic_bound = grouped ? tiles_m >= 2 : tiles_at_widest >= 3ull * sms;
-    uint32_t best = step;
+    const bool pair_allowed = ctx->pair_mode != 0 && m > kTileM && (traffic_bound || ctx->pair_mode == 1);
+    if (ctx->forced_tile_n >= 16) {
+        const uint32_t forced = std::min<uint32_t>(kMaxTileN, static_cast<uint32_t>(ctx->forced_tile_n));
+        const uint32_t pair_step = 32;
+        if (pair_allowed) return TileChoice{std::max(pair_step, forced / pair_step * pair_step), true};
+        return TileChoice{std::max(step, forced / step * step), false};
+    }
+    TileChoice best{step, false};
     double best_cost = 1e300;
-    for (uint32_t tile_n = kMaxTileN; tile_n >= step; tile_n -= step) {
-        const uint32_t per_tile = geglu ? tile_n / 2 : tile_n;
-        const uint32_t tiles_n = (columns + per_tile - 1) / per_tile;
-        double cost;
-        if (traffic_bound) {
-            cost = static_cast<double>(tiles_n) * (128.0 + tile_n);
-        } else {
-            const uint64_t tiles = static_cast<uint64_t>(tiles_m) * tiles_n;
-            const uint64_t waves = (tiles + sms - 1) / sms;
-            cost = static_cast<double>(waves) * (tile_n + 32.0);
+    for (int pair = pair_allowed ? 1 : 0; pair >= 0; --pair) {
+        const uint32_t tile_step = pair ? 32 : step;
+        for (uint32_t tile_n = kMaxTileN; tile_n >= tile_step; tile_n -= tile_step) {
+            const uint32_t per_tile = geglu ? tile_n / 2 : tile_n;
+            const uint32_t tiles_n = (columns + per_tile - 1) / per_tile;
+            double cost;
+            if (traffic_bound || pair) {
+                cost = static_cast<double>(tiles_n) * (128.0 + (pair ? tile_n / 2.0 : tile_n));
+            } else {
+                const uint64_t tiles = static_cast<uint64_t>(tiles_m) * tiles_n;
+                const uint64_t waves = (tiles + sms - 1) / sms;
+                cost = static_cast<double>(waves) * (tile_n + 32.0);
+            }
+            if (cost < best_cost) { best_cost = cost; best = TileChoice{tile_n, pair != 0}; }
+            if (tile_n == tile_step) break;
         }
-        if (cost < best_cost) { best_cost = cost; best = tile_n; }
-        if (tile_n == step) break;
+        if (pair) break;      // a pair is allowed only where it wins: traffic-bound launches
     }
     return best;
 }
@@ -260,11 +275,12 @@ enum Int8Flavour { INT8_GENERIC = 0, INT8_PLAIN = 1, INT8_ROTATED = 2, INT8_FLAV
 struct Prepared {
     Int8JobSet int8[INT8_FLAVOURS];
     std::vector<QuantFp8Job> fp8_jobs;
-    std::vector<GemmProblem> problems;
-    std::vector<TileRef> tiles;
+    // GEMM problems by kernel flavour: [0] single CTA (128-row tiles), [1] CTA pair (256-row tiles)
+    std::vector<GemmProblem> problems[2];
+    std::vector<TileRef> tiles[2];
+    uint32_t max_cta_b_rows[2] = {0, 0};     // most B rows one CTA stages (tile_n, or tile_n / 2 in a pair)
     std::vector<SmallCall> small;
     uint32_t fp8_blocks = 0;
-    uint32_t max_tile_n = 0;
     uint32_t int8_linears = 0;
     uint32_t int8_small = 0;
     size_t scratch_bytes = 0;
@@ -376,6 +392,9 @@ void add_fp8_job(Prepared& prep, const void* x, uint64_t count, uint32_t fmt, ui
     prep.fp8_jobs.push_back(job);
 }
 
+void order_tiles(const sdxlq_context* ctx, const std::vector<GemmProblem>& problems, std::vector<TileRef>& tiles,
+                 bool pair);
+
 int prepare(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count, bool grouped, Prepared& prep) {
     std::map<QuantKey, std::pair<const void*, const float*>> shared_inputs;
     size_t scratch = 0;
@@ -458,41 +477,83 @@ int prepare(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count, bo
 
         GemmProblem problem{};
         problem.ep = ep;
-        problem.tile_n = choose_tile_n(ctx, ep.m, ep.n, geglu, grouped);
+        const TileChoice choice = choose_tile(ctx, ep.m, ep.n, geglu, grouped);
+        const int flavour = choice.pair ? 1 : 0;
+        const uint32_t rows_per_tile = choice.pair ? 2 * kTileM : kTileM;
+        problem.tile_n = choice.tile_n;
         const uint32_t per_tile = geglu ? problem.tile_n / 2 : problem.tile_n;
-        problem.tiles_m = (ep.m + kTileM - 1) / kTileM;
+        problem.tiles_m = (ep.m + rows_per_tile - 1) / rows_per_tile;
         problem.tiles_n = (ep.n_out + per_tile - 1) / per_tile;
         problem.k_blocks = static_cast<uint32_t>((w.k * element + kTileKBytes - 1) / kTileKBytes);
         const uint32_t format = kind == KIND_I8 ? 1u : (kind == KIND_E5M2 ? 1u : 0u);
-        // c_format: 2 = S32 for kind::i8, 1 = F32 otherwise; operands K-major; M = 128.
+        // c_format: 2 = S32 for kind::i8, 1 = F32 otherwise; operands K-major; M = 128 (256 for a pair).
         problem.idesc = ((kind == KIND_I8 ? 2u : 1u) << 4) | (format << 7) | (format << 10) |
-                        ((problem.tile_n >> 3) << 17) | ((kTileM >> 4) << 24);
+                        ((problem.tile_n >> 3) << 17) | ((rows_per_tile >> 4) << 24);
+        // B box: the rows one TMA load brings in. A single CTA loads the whole tile (two boxes of
+        // half the tile for GEGLU); each CTA of a pair loads half of the tile's rows.
+        const uint32_t b_box_rows = choice.pair ? problem.tile_n / 2 : per_tile;
         if (!encode_operand(ctx, &problem.tmap_a, kind, a, ep.m, w.k, kTileM) ||
-            !encode_operand(ctx, &problem.tmap_b, kind, w.data, w.n, w.k, per_tile)) {
+            !encode_operand(ctx, &problem.tmap_b, kind, w.data, w.n, w.k, b_box_rows)) {
             return fail(ctx, SDXLQ_ERR_CUDA, "cuTensorMapEncodeTiled rejected an operand");
         }
-        prep.max_tile_n = std::max(prep.max_tile_n, problem.tile_n);
-        const uint32_t problem_index = static_cast<uint32_t>(prep.problems.size());
-        prep.problems.push_back(problem);
+        prep.max_cta_b_rows[flavour] = std::max(prep.max_cta_b_rows[flavour], choice.pair ? problem.tile_n / 2 : problem.tile_n);
+        const uint32_t problem_index = static_cast<uint32_t>(prep.problems[flavour].size());
+        prep.problems[flavour].push_back(problem);
         if (grouped) {
             // n-major inside an m-tile keeps the CTAs of one wave on the same weight rows.
             for (uint32_t tn = 0; tn < problem.tiles_n; ++tn) {
                 for (uint32_t tm = 0; tm < problem.tiles_m; ++tm) {
-                    prep.tiles.push_back(TileRef{problem_index, static_cast<uint16_t>(tm), static_cast<uint16_t>(tn)});
+                    prep.tiles[flavour].push_back(TileRef{problem_index, static_cast<uint16_t>(tm), static_cast<uint16_t>(tn)});
                 }
             }
         }
     }
-    if (grouped && prep.problems.size() > 1) {
-        // Longest tiles first so that the round-robin walk of the persistent CTAs ends evenly.
-        std::stable_sort(prep.tiles.begin(), prep.tiles.end(), [&](const TileRef& l, const TileRef& r) {
-            const GemmProblem& pl = prep.problems[l.problem];
-            const GemmProblem& pr = prep.problems[r.problem];
-            return static_cast<uint64_t>(pl.k_blocks) * (pl.tile_n + 128) > static_cast<uint64_t>(pr.k_blocks) * (pr.tile_n + 128);
-        });
+    for (int flavour = 0; flavour < 2; ++flavour) {
+        if (!grouped || prep.problems[flavour].size() <= 1) continue;
+        order_tiles(ctx, prep.problems[flavour], prep.tiles[flavour], flavour == 1);
     }
     prep.scratch_bytes = scratch;
     return SDXLQ_OK;
+}
+
+// Orders the tile list of a grouped launch. The persistent CTAs (or CTA pairs) walk it with a
+// stride equal to their count, and a CTA overlaps the epilogue of tile i with the main loop of tile
+// i + 1 (two accumulator buffers). Tiles whose epilogue outlasts their main loop (GEGLU with short
+// K) are therefore alternated, one CTA-count block at a time, with tiles whose main loop dominates
+// (long K); inside each class the longest tiles come first so that the walk ends evenly.
+// Time model, fitted on B200: main loop ~ k_blocks * tile_n * 2.07e-3 us; epilogue ~ tile_n *
+// 8.3e-3 us, or tile_n * 28.8e-3 us with the GEGLU epilogue.
+void order_tiles(const sdxlq_context* ctx, const std::vector<GemmProblem>& problems, std::vector<TileRef>& tiles,
+                 bool pair) {
+    auto mainloop_time = [&](const TileRef& t) {
+        const GemmProblem& p = problems[t.problem];
+        return 2.07e-3 * p.k_blocks * p.tile_n;
+    };
+    auto epilogue_time = [&](const TileRef& t) {
+        const GemmProblem& p = problems[t.problem];
+        return (p.ep.activation == ACT_GEGLU ? 28.8e-3 : 8.3e-3) * p.tile_n;
+    };
+    std::vector<TileRef> epilogue_heavy, mainloop_heavy;
+    for (const TileRef& t : tiles) (epilogue_time(t) > mainloop_time(t) ? epilogue_heavy : mainloop_heavy).push_back(t);
+    auto longest_first = [&](const TileRef& l, const TileRef& r) {
+        return std::max(mainloop_time(l), epilogue_time(l)) > std::max(mainloop_time(r), epilogue_time(r));
+    };
+    std::stable_sort(epilogue_heavy.begin(), epilogue_heavy.end(), longest_first);
+    std::stable_sort(mainloop_heavy.begin(), mainloop_heavy.end(), longest_first);
+    const size_t block = std::max<size_t>(1, pair ? ctx->sm_count / 2 : ctx->sm_count);
+    const size_t total_e = epilogue_heavy.size(), total_m = mainloop_heavy.size();
+    size_t taken_e = 0, taken_m = 0;
+    tiles.clear();
+    while (taken_e < total_e || taken_m < total_m) {
+        // take the next block from the class that is behind its share of the list
+        const bool take_e = taken_m >= total_m ||
+                            (taken_e < total_e && taken_e * (total_e + total_m) <= (taken_e + taken_m) * total_e);
+        std::vector<TileRef>& source = take_e ? epilogue_heavy : mainloop_heavy;
+        size_t& taken = take_e ? taken_e : taken_m;
+        const size_t count = std::min(block, source.size() - taken);
+        tiles.insert(tiles.end(), source.begin() + taken, source.begin() + taken + count);
+        taken += count;
+    }
 }
 
 struct GemmGeometry {
@@ -501,9 +562,9 @@ struct GemmGeometry {
     size_t dynamic_smem;
 };
 
-GemmGeometry gemm_geometry(uint32_t max_tile_n) {
+GemmGeometry gemm_geometry(uint32_t max_cta_b_rows) {
     GemmGeometry g{};
-    g.stage_bytes = (kTileM + max_tile_n) * kTileKBytes;
+    g.stage_bytes = (kTileM + max_cta_b_rows) * kTileKBytes;
     const size_t control_bytes = umma_gemm_control_bytes();   // barriers, staged column operands, alignment slack
     g.num_stages = static_cast<uint32_t>(std::min<size_t>(8, (kSmemLimit - control_bytes) / g.stage_bytes));
     g.dynamic_smem = control_bytes + static_cast<size_t>(g.num_stages) * g.stage_bytes;
@@ -528,6 +589,34 @@ QuantFp8Launch bind_fp8(sdxlq_context* ctx, const std::vector<QuantFp8Job>& jobs
     return launch;
 }
 
+// Launches the tensor-core GEMM of one kernel flavour: `problems` / `tiles` are the device tables
+// of a grouped plan, or null for a single problem passed in the kernel parameters.
+int run_gemm_flavour(sdxlq_context* ctx, const Prepared& prep, int flavour, const GemmProblem* problems,
+                     const TileRef* tiles) {
+    if (prep.problems[flavour].empty()) return SDXLQ_OK;
+    const bool pair = flavour == 1;
+    const GemmGeometry geometry = gemm_geometry(prep.max_cta_b_rows[flavour]);
+    GemmLaunchParams params{};
+    params.problems = problems;
+    params.tiles = tiles;
+    params.single = prep.problems[flavour][0];
+    params.num_tiles = problems != nullptr ? static_cast<uint32_t>(prep.tiles[flavour].size())
+                                           : params.single.tiles_m * params.single.tiles_n;
+    params.num_stages = geometry.num_stages;
+    params.stage_bytes = geometry.stage_bytes;
+    params.b_offset = kTileM * kTileKBytes;
+    params.error_word = ctx->control;
+    params.wait_limit_cycles = ctx->wait_limit_cycles;
+    params.diagnostic_skip = ctx->diagnostic_skip;
+    const uint32_t sms = static_cast<uint32_t>(ctx->sm_count);
+    const uint32_t grid = pair ? 2 * std::min<uint32_t>(params.num_tiles, sms / 2) : std::min<uint32_t>(params.num_tiles, sms);
+    LaunchTimer timer(ctx, SDXLQ_KERNEL_GEMM);
+    const cudaError_t error = launch_umma_gemm(params, grid, geometry.dynamic_smem, ctx->stream,
+                                               ctx->umma_smem_attribute, pair);
+    if (error != cudaSuccess) return fail_cuda(ctx, error, "tensor-core GEMM launch");
+    return SDXLQ_OK;
+}
+
 int run_small(sdxlq_context* ctx, const Prepared& prep) {
     for (const SmallCall& call : prep.small) {
         LaunchTimer timer(ctx, SDXLQ_KERNEL_SMALL);
@@ -547,8 +636,8 @@ void count_stats(sdxlq_context* ctx, const Prepared& prep) {
 
 struct sdxlq_group_plan {
     Prepared prep;
-    GemmProblem* device_problems = nullptr;
-    TileRef* device_tiles = nullptr;
+    GemmProblem* device_problems[2] = {nullptr, nullptr};
+    TileRef* device_tiles[2] = {nullptr, nullptr};
     QuantInt8Job* device_int8_jobs[INT8_FLAVOURS] = {nullptr, nullptr, nullptr};
     QuantFp8Job* device_fp8_jobs = nullptr;
     int device = 0;
@@ -590,6 +679,8 @@ int sdxlq_context_create(int device, void* stream, size_t workspace_bytes, sdxlq
         if (parsed > 0) ctx->wait_limit_cycles = parsed;
     }
     if (const char* text = std::getenv("SDXLQ_TILE_N")) ctx->forced_tile_n = std::atoi(text);
+    if (const char* text = std::getenv("SDXLQ_PAIR")) ctx->pair_mode = std::atoi(text);
+    if (const char* text = std::getenv("SDXLQ_DIAGNOSTIC_SKIP")) ctx->diagnostic_skip = static_cast<uint32_t>(std::atoi(text));
     *out = ctx;
     return SDXLQ_OK;
 }
@@ -614,6 +705,12 @@ int sdxlq_context_set_stream(sdxlq_context* ctx, void* stream) {
 int sdxlq_context_set_tile_n(sdxlq_context* ctx, int tile_n) {
     if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
     ctx->forced_tile_n = tile_n;
+    return SDXLQ_OK;
+}
+
+int sdxlq_context_set_pair_mode(sdxlq_context* ctx, int mode) {
+    if (ctx == nullptr || mode < -1 || mode > 1) return SDXLQ_ERR_INVALID_ARGUMENT;
+    ctx->pair_mode = mode;
     return SDXLQ_OK;
 }
 
@@ -655,7 +752,7 @@ int sdxlq_get_stats(const sdxlq_context* ctx, sdxlq_int8_stats* out) {
 
 int sdxlq_valid_convrot_group_size(size_t group_size) { return valid_group(group_size) ? 1 : 0; }
 
-const char* sdxlq_build_info(void) { return "sdxlq sm_100a tcgen05/TMA cta_group::1 128xN"; }
+const char* sdxlq_build_info(void) { return "sdxlq sm_100a tcgen05/TMA cta_group::1 128xN + cta_group::2 256xN"; }
 
 size_t sdxlq_workspace_bytes(const sdxlq_linear_desc* descs, size_t count) {
     if (descs == nullptr) return 0;
@@ -688,24 +785,9 @@ int sdxlq_linear(sdxlq_context* ctx, const sdxlq_linear_desc* desc) {
         const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream);
         if (error != cudaSuccess) return fail_cuda(ctx, error, "FP8 activation quantise launch");
     }
-    if (!prep.problems.empty()) {
-        const GemmProblem& problem = prep.problems[0];
-        const GemmGeometry geometry = gemm_geometry(problem.tile_n);
-        GemmLaunchParams params{};
-        params.problems = nullptr;
-        params.tiles = nullptr;
-        params.num_tiles = problem.tiles_m * problem.tiles_n;
-        params.num_stages = geometry.num_stages;
-        params.stage_bytes = geometry.stage_bytes;
-        params.b_offset = kTileM * kTileKBytes;
-        params.error_word = ctx->control;
-        params.wait_limit_cycles = ctx->wait_limit_cycles;
-        params.single = problem;
-        const uint32_t grid = std::min<uint32_t>(params.num_tiles, static_cast<uint32_t>(ctx->sm_count));
-        LaunchTimer timer(ctx, SDXLQ_KERNEL_GEMM);
-        const cudaError_t error = launch_umma_gemm(params, grid, geometry.dynamic_smem, ctx->stream,
-                                                   &ctx->umma_smem_attribute);
-        if (error != cudaSuccess) return fail_cuda(ctx, error, "tensor-core GEMM launch");
+    for (int flavour = 0; flavour < 2; ++flavour) {
+        status = run_gemm_flavour(ctx, prep, flavour, nullptr, nullptr);
+        if (status != SDXLQ_OK) return status;
     }
     status = run_small(ctx, prep);
     if (status != SDXLQ_OK) return status;
@@ -729,7 +811,8 @@ int sdxlq_group_plan_create(sdxlq_context* ctx, const sdxlq_linear_desc* descs, 
         if (cudaMalloc(reinterpret_cast<void**>(destination), host.size() * sizeof(T)) != cudaSuccess) return false;
         return cudaMemcpy(*destination, host.data(), host.size() * sizeof(T), cudaMemcpyHostToDevice) == cudaSuccess;
     };
-    if (!upload(&plan->device_problems, prep.problems) || !upload(&plan->device_tiles, prep.tiles) ||
+    if (!upload(&plan->device_problems[0], prep.problems[0]) || !upload(&plan->device_tiles[0], prep.tiles[0]) ||
+        !upload(&plan->device_problems[1], prep.problems[1]) || !upload(&plan->device_tiles[1], prep.tiles[1]) ||
         !upload(&plan->device_int8_jobs[0], prep.int8[0].jobs) || !upload(&plan->device_int8_jobs[1], prep.int8[1].jobs) ||
         !upload(&plan->device_int8_jobs[2], prep.int8[2].jobs) || !upload(&plan->device_fp8_jobs, prep.fp8_jobs)) {
         sdxlq_group_plan_destroy(plan);
@@ -752,23 +835,9 @@ int sdxlq_group_plan_run(sdxlq_context* ctx, sdxlq_group_plan* plan) {
         const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream);
         if (error != cudaSuccess) return fail_cuda(ctx, error, "grouped FP8 activation quantise launch");
     }
-    if (!prep.problems.empty()) {
-        const GemmGeometry geometry = gemm_geometry(prep.max_tile_n);
-        GemmLaunchParams params{};
-        params.problems = plan->device_problems;
-        params.tiles = plan->device_tiles;
-        params.num_tiles = static_cast<uint32_t>(prep.tiles.size());
-        params.num_stages = geometry.num_stages;
-        params.stage_bytes = geometry.stage_bytes;
-        params.b_offset = kTileM * kTileKBytes;
-        params.error_word = ctx->control;
-        params.wait_limit_cycles = ctx->wait_limit_cycles;
-        params.single = prep.problems[0];
-        const uint32_t grid = std::min<uint32_t>(params.num_tiles, static_cast<uint32_t>(ctx->sm_count));
-        LaunchTimer timer(ctx, SDXLQ_KERNEL_GEMM);
-        const cudaError_t error = launch_umma_gemm(params, grid, geometry.dynamic_smem, ctx->stream,
-                                                   &ctx->umma_smem_attribute);
-        if (error != cudaSuccess) return fail_cuda(ctx, error, "grouped tensor-core GEMM launch");
+    for (int flavour = 0; flavour < 2; ++flavour) {
+        const int gemm_status = run_gemm_flavour(ctx, prep, flavour, plan->device_problems[flavour], plan->device_tiles[flavour]);
+        if (gemm_status != SDXLQ_OK) return gemm_status;
     }
     const int status = run_small(ctx, prep);
     if (status != SDXLQ_OK) return status;
@@ -779,15 +848,15 @@ int sdxlq_group_plan_run(sdxlq_context* ctx, sdxlq_group_plan* plan) {
 int sdxlq_group_plan_launches(const sdxlq_group_plan* plan) {
     if (plan == nullptr) return 0;
     const Prepared& prep = plan->prep;
-    return int8_quantiser_launches(prep) + (prep.fp8_jobs.empty() ? 0 : 2) + (prep.problems.empty() ? 0 : 1) +
+    return int8_quantiser_launches(prep) + (prep.fp8_jobs.empty() ? 0 : 2) + (prep.problems[0].empty() ? 0 : 1) + (prep.problems[1].empty() ? 0 : 1) +
            static_cast<int>(prep.small.size());
 }
 
 void sdxlq_group_plan_destroy(sdxlq_group_plan* plan) {
     if (plan == nullptr) return;
     cudaSetDevice(plan->device);
-    cudaFree(plan->device_problems);
-    cudaFree(plan->device_tiles);
+    for (GemmProblem* table : plan->device_problems) cudaFree(table);
+    for (TileRef* table : plan->device_tiles) cudaFree(table);
     for (QuantInt8Job* table : plan->device_int8_jobs) cudaFree(table);
     cudaFree(plan->device_fp8_jobs);
     delete plan;

@@ -8,6 +8,7 @@
 // bias_activation_in_place / bias_geglu (src/cuda/ops_kernels.cu:76-82, 142-183).
 //
 // One CTA per SM walks a tile list (all tiles of all problems of a grouped launch):
+// (or one cluster of two CTAs per SM pair, see the kernel template)
 //   warp 0    TMA producer  : cp.async.bulk.tensor 2D loads into a ring of 128B-swizzled stages
 //   warp 1    MMA issuer    : tcgen05.mma (kind::i8 / kind::f8f6f4 / kind::f16), accumulators
 //                             in TMEM, two accumulator buffers so the next tile's main loop
@@ -322,6 +323,14 @@ __device__ __forceinline__ void epilogue_dispatch(uint32_t activation, const Epi
 
 }  // namespace
 
+// kPair = false: one CTA per 128-row tile (cta_group::1).
+// kPair = true : a cluster of two CTAs per 256-row tile (cta_group::2). Each CTA loads its own 128
+//   rows of A and half of the tile's B rows (for GEGLU: the leader the value rows, its peer the
+//   gate rows); the leader's elected thread issues M=256 MMAs that read both CTAs' shared memory
+//   and write 128 accumulator rows into each CTA's tensor memory. Every TMA load of the pair counts
+//   on the leader's full barrier; the MMA completion is committed to both CTAs' empty / tmem_full
+//   barriers; both CTAs' epilogue warps arrive on the leader's tmem_empty barrier.
+template <bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
     extern __shared__ __align__(16) uint8_t dynamic_smem[];
@@ -336,6 +345,13 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
     const uint32_t num_tiles = params.num_tiles;
     volatile uint32_t* abort_word = &control->abort;
     const long long limit = params.wait_limit_cycles;
+    const bool skip_epilogue = (params.diagnostic_skip & 1u) != 0;
+    const bool skip_mainloop = (params.diagnostic_skip & 2u) != 0;
+    const uint32_t cta_rank = kPair ? ptx::cluster_cta_rank() : 0u;
+    const bool leader = cta_rank == 0;
+    const uint32_t first_tile = kPair ? blockIdx.x >> 1 : blockIdx.x;
+    const uint32_t tile_stride = kPair ? gridDim.x >> 1 : gridDim.x;
+    constexpr uint32_t kRowsPerTile = kPair ? 2 * kTileM : kTileM;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < num_stages; ++s) {
@@ -344,17 +360,23 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
         }
         for (uint32_t b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_u32(&control->tmem_full[b]), 1);
-            ptx::mbar_init(ptx::smem_u32(&control->tmem_empty[b]), kEpilogueWarps);
+            ptx::mbar_init(ptx::smem_u32(&control->tmem_empty[b]), kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
         }
         control->abort = 0;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_u32(&control->tmem_base), kTmemColumns);
-        ptx::tmem_relinquish();
+        if (kPair) {
+            ptx::tmem_alloc_pair(ptx::smem_u32(&control->tmem_base), kTmemColumns);
+            ptx::tmem_relinquish_pair();
+        } else {
+            ptx::tmem_alloc(ptx::smem_u32(&control->tmem_base), kTmemColumns);
+            ptx::tmem_relinquish();
+        }
     }
     ptx::tc_fence_before();
     __syncthreads();
+    if (kPair) ptx::cluster_sync();          // the peer's barriers exist before anything signals them
     ptx::tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&control->tmem_base);
 
@@ -365,7 +387,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             uint32_t issued_mask = 0, issued_phase = 0;
             const GemmProblem* bound = nullptr;
             bool ok = true;
-            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+            for (uint32_t t = first_tile; ok && t < num_tiles; t += tile_stride) {
                 const TileWork work = fetch_tile(params, t);
                 const CUtensorMap* tmap_a = &work.problem->tmap_a;
                 const CUtensorMap* tmap_b = &work.problem->tmap_b;
@@ -376,11 +398,15 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                 }
                 const uint32_t tile_n = work.tile_n;
                 const uint32_t half = tile_n / 2;
-                const uint32_t tx_bytes = (kTileM + tile_n) * kTileKBytes;
+                // bytes that land per stage, over both CTAs of a pair
+                const uint32_t tx_bytes = (kPair ? 2 * kTileM + tile_n : kTileM + tile_n) * kTileKBytes;
                 const int32_t k_step = work.kind == KIND_F16 ? 64 : 128;   // elements per stage
-                const int32_t row_a = static_cast<int32_t>(work.tile_m * kTileM);
+                const int32_t row_a = static_cast<int32_t>(work.tile_m * kRowsPerTile + cta_rank * kTileM);
                 const int32_t row_b = static_cast<int32_t>(work.tile_n_index * (work.geglu ? half : tile_n));
                 const int32_t row_gate = static_cast<int32_t>(work.n_out) + row_b;
+                // pair: this CTA's half of the B rows (GEGLU: value rows in the leader, gate rows in the peer)
+                const int32_t row_b_pair = work.geglu ? (leader ? row_b : row_gate)
+                                                      : row_b + static_cast<int32_t>(cta_rank * half);
                 const uint32_t k_blocks = work.k_blocks;
                 for (uint32_t kb = 0; kb < k_blocks; ++kb) {
                     const uint32_t full_bar = ptx::smem_u32(&control->full[stage]);
@@ -390,19 +416,27 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                         ok = false;
                         break;
                     }
-                    ptx::mbar_expect_tx(full_bar, tx_bytes);
                     const uint32_t a_dst = stages_base + stage * stage_bytes;
                     const uint32_t b_dst = a_dst + b_offset;
                     const int32_t k0 = static_cast<int32_t>(kb) * k_step;
-                    ptx::tma_load_2d(a_dst, tmap_a, full_bar, k0, row_a);
-                    ptx::tma_load_2d(b_dst, tmap_b, full_bar, k0, row_b);
-                    if (work.geglu) ptx::tma_load_2d(b_dst + half * kTileKBytes, tmap_b, full_bar, k0, row_gate);
+                    if (skip_mainloop) {
+                        if (leader) ptx::mbar_arrive(full_bar);
+                    } else if (kPair) {
+                        if (leader) ptx::mbar_expect_tx(full_bar, tx_bytes);
+                        ptx::tma_load_2d_pair(a_dst, tmap_a, full_bar, k0, row_a);
+                        ptx::tma_load_2d_pair(b_dst, tmap_b, full_bar, k0, row_b_pair);
+                    } else {
+                        ptx::mbar_expect_tx(full_bar, tx_bytes);
+                        ptx::tma_load_2d(a_dst, tmap_a, full_bar, k0, row_a);
+                        ptx::tma_load_2d(b_dst, tmap_b, full_bar, k0, row_b);
+                        if (work.geglu) ptx::tma_load_2d(b_dst + half * kTileKBytes, tmap_b, full_bar, k0, row_gate);
+                    }
                     issued_mask |= 1u << stage;
                     issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
                     if (++stage == num_stages) { stage = 0; phase ^= 1u; }
                 }
             }
-            if (!ok) {
+            if (!ok && (!kPair || leader)) {
                 // Let the copies this thread started land before the CTA retires.
                 for (uint32_t s = 0; s < num_stages; ++s) {
                     if (issued_mask & (1u << s)) {
@@ -414,10 +448,10 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
         }
     } else if (warp == 1) {
         // ------------------------------- MMA issuer ---------------------------------------
-        if (lane == 0) {
+        if (lane == 0 && leader) {
             uint32_t stage = 0, phase = 0, iteration = 0;
             bool ok = true;
-            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++iteration) {
+            for (uint32_t t = first_tile; ok && t < num_tiles; t += tile_stride, ++iteration) {
                 const TileWork work = fetch_tile(params, t);
                 const uint32_t buffer = iteration & 1u;
                 const uint32_t accumulator_phase = (iteration >> 1) & 1u;
@@ -444,16 +478,37 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                     const uint64_t desc_b = ptx::umma_smem_desc_sw128(a_addr + b_offset);
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k) {   // 4 x 32 bytes of K per stage
+                        if (skip_mainloop) break;
                         const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
                         const uint64_t advance = static_cast<uint64_t>(k * 2);   // 32 B >> 4
-                        if (kind == KIND_I8) ptx::umma_i8(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
-                        else if (kind == KIND_F16) ptx::umma_f16(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
-                        else ptx::umma_f8f6f4(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
+                        if (kPair) {
+                            if (kind == KIND_I8) ptx::umma_i8_pair(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
+                            else if (kind == KIND_F16) ptx::umma_f16_pair(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
+                            else ptx::umma_f8f6f4_pair(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
+                        } else {
+                            if (kind == KIND_I8) ptx::umma_i8(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
+                            else if (kind == KIND_F16) ptx::umma_f16(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
+                            else ptx::umma_f8f6f4(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
+                        }
                     }
-                    ptx::umma_commit(ptx::smem_u32(&control->empty[stage]));
+                    const uint32_t empty_bar = ptx::smem_u32(&control->empty[stage]);
+                    if (kPair) {
+                        ptx::umma_commit_pair(empty_bar);                        // frees the leader's stage
+                        ptx::umma_commit_pair(ptx::map_to_cta(empty_bar, 1));    // and the peer's
+                    } else {
+                        ptx::umma_commit(empty_bar);
+                    }
                     if (++stage == num_stages) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) ptx::umma_commit(ptx::smem_u32(&control->tmem_full[buffer]));
+                if (ok) {
+                    const uint32_t full_bar = ptx::smem_u32(&control->tmem_full[buffer]);
+                    if (kPair) {
+                        ptx::umma_commit_pair(full_bar);
+                        ptx::umma_commit_pair(ptx::map_to_cta(full_bar, 1));
+                    } else {
+                        ptx::umma_commit(full_bar);
+                    }
+                }
             }
         }
     } else {
@@ -465,7 +520,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
         const uint32_t epilogue_thread = threadIdx.x - 64u;
         uint32_t iteration = 0;
         bool ok = true;
-        for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++iteration) {
+        for (uint32_t t = first_tile; t < num_tiles; t += tile_stride, ++iteration) {
             const TileWork work = fetch_tile(params, t);
             const EpilogueParams& ep = params.problems == nullptr ? params.single.ep : work.problem->ep;
             const uint32_t buffer = iteration & 1u;
@@ -484,7 +539,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             tile.n_out = ep.n_out;
             tile.tile_n = work.tile_n;
             tile.n0 = work.tile_n_index * (work.geglu ? work.tile_n / 2 : work.tile_n);
-            tile.row = work.tile_m * kTileM + quadrant * 32u + lane;
+            tile.row = work.tile_m * kRowsPerTile + cta_rank * kTileM + quadrant * 32u + lane;
             tile.tmem_row = tmem_base + ((quadrant * 32u) << 16) + buffer * kMaxTileN;
             tile.chunk_first = chunk_first;
             const bool row_ok = tile.row < ep.m;
@@ -504,20 +559,27 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             // stays balanced) but touches neither TMEM nor global memory again.
             if (!ok) continue;
             ptx::tc_fence_after();
-            if (kind == KIND_I8) epilogue_dispatch<KIND_I8>(activation, tile);
+            if (skip_epilogue) { /* diagnostic: accumulators are dropped */ }
+            else if (kind == KIND_I8) epilogue_dispatch<KIND_I8>(activation, tile);
             else if (kind == KIND_F16) epilogue_dispatch<KIND_F16>(activation, tile);
             else epilogue_dispatch<KIND_E4M3>(activation, tile);
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&control->tmem_empty[buffer]));
+            if (lane == 0) {
+                const uint32_t empty_bar = ptx::smem_u32(&control->tmem_empty[buffer]);
+                if (kPair) ptx::mbar_arrive_cluster(empty_bar & ptx::kPeerBitMask);   // the leader's barrier
+                else ptx::mbar_arrive(empty_bar);
+            }
         }
     }
 
     ptx::tc_fence_before();
     __syncthreads();
+    if (kPair) ptx::cluster_sync();          // neither CTA retires while its peer may still touch it
     if (warp == 1) {
         ptx::tc_fence_after();
-        ptx::tmem_dealloc(tmem_base, kTmemColumns);
+        if (kPair) ptx::tmem_dealloc_pair(tmem_base, kTmemColumns);
+        else ptx::tmem_dealloc(tmem_base, kTmemColumns);
     }
 }
 
@@ -545,19 +607,33 @@ cudaError_t launch_bounded_wait_probe(uint32_t* error_word, long long limit_cycl
 // the first stage to 1024 bytes.
 size_t umma_gemm_control_bytes() { return (sizeof(Control) + 1023u + 1023u) / 1024u * 1024u; }
 
-// Host-side launcher (called from the dispatch code). `attribute_bytes` remembers, per context,
-// the dynamic shared memory size the kernel has been opted into.
+// Host-side launcher (called from the dispatch code). `attribute_bytes[pair]` remembers, per
+// context, the dynamic shared memory size each kernel flavour has been opted into. `grid` counts
+// CTAs (even for the CTA-pair flavour, which is launched as clusters of two).
 cudaError_t launch_umma_gemm(const GemmLaunchParams& params, uint32_t grid, size_t dynamic_smem,
-                             cudaStream_t stream, size_t* attribute_bytes) {
-    if (dynamic_smem > *attribute_bytes) {
-        const cudaError_t status = cudaFuncSetAttribute(sdxlq_umma_gemm_kernel,
-                                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             cudaStream_t stream, size_t* attribute_bytes, bool pair) {
+    auto kernel = pair ? sdxlq_umma_gemm_kernel<true> : sdxlq_umma_gemm_kernel<false>;
+    if (dynamic_smem > attribute_bytes[pair ? 1 : 0]) {
+        const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                         static_cast<int>(dynamic_smem));
         if (status != cudaSuccess) return status;
-        *attribute_bytes = dynamic_smem;
+        attribute_bytes[pair ? 1 : 0] = dynamic_smem;
     }
-    sdxlq_umma_gemm_kernel<<<grid, kThreads, dynamic_smem, stream>>>(params);
-    return cudaGetLastError();
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(grid, 1, 1);
+    config.blockDim = dim3(kThreads, 1, 1);
+    config.dynamicSmemBytes = dynamic_smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    if (pair) {
+        attribute.id = cudaLaunchAttributeClusterDimension;
+        attribute.val.clusterDim.x = 2;
+        attribute.val.clusterDim.y = 1;
+        attribute.val.clusterDim.z = 1;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&config, kernel, params);
 }
 
 }  // namespace sdxlq

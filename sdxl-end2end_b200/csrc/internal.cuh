@@ -71,6 +71,10 @@ struct GemmLaunchParams {
     uint32_t b_offset;           // offset of the B tile inside a stage (= 128 rows * 128 B)
     uint32_t* error_word;        // device word set on a bounded-wait timeout
     long long wait_limit_cycles;
+    uint32_t diagnostic_skip;    // tuning aid: bit 0 skips the epilogue arithmetic and stores, bit 1 skips
+                                 // the operand loads and MMAs (barriers are still signalled); results are
+                                 // meaningless when set
+    uint32_t pad0;
     GemmProblem single;
 };
 

