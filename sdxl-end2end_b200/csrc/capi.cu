@@ -63,7 +63,8 @@ struct sdxlq_context {
     uint32_t fp8_dirty[2] = {0, 0};        // amax words of each parity left non-zero
     int sm_count = 148;
     size_t umma_smem_attribute[2] = {0, 0};   // per kernel flavour: single CTA, CTA pair
-    int pair_mode = -1;                       // -1 automatic, 0 never use CTA pairs, 1 whenever possible
+    int pair_mode = 0;                        // 0 never use CTA pairs (default: they measured no faster), 1 whenever
+                                              // possible, -1 for traffic-bound launches only
     uint32_t diagnostic_skip = 0;             // SDXLQ_DIAGNOSTIC_SKIP: tuning aid, see GemmLaunchParams
     long long wait_limit_cycles = 4000000000LL;
     int forced_tile_n = 0;
@@ -137,10 +138,12 @@ uint32_t group_stages(uint32_t group_size) {
 // ---- validation: the checks of Ops::linear, int8_convrot_linear, fp8_weight_only_linear ----
 int validate(sdxlq_context* ctx, const sdxlq_linear_desc& d) {
     const sdxlq_weight& w = d.weight;
-    if (w.data == nullptr || d.y == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: null weight or output pointer");
-    if (d.x == nullptr && d.xq == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: null input pointer");
+    // An empty input (m == 0) is a no-op whose input and output buffers may be null.
+    if (w.data == nullptr || (d.y == nullptr && d.m != 0)) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: null weight or output pointer");
+    if (d.x == nullptr && d.xq == nullptr && d.m != 0) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: null input pointer");
     if (w.n == 0 || w.k == 0) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: empty weight");
-    if (d.m > 0x7FFFFFFFull || w.n > 0x7FFFFFFFull || w.k > 0x7FFFFFFFull) {
+    // Tile coordinates and the K-block count travel as 16-bit fields of a tile record.
+    if (d.m > 0xFFFFull * kTileM || w.n > 0xFFFFull * 16 || w.k > 0xFFFFull * 64) {
         return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE, "linear dimensions exceed kernel integer range");
     }
     if (d.activation < SDXLQ_ACT_NONE || d.activation > SDXLQ_ACT_GEGLU) {
@@ -205,7 +208,9 @@ TileChoice choose_tile(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool ge
     const uint32_t columns = geglu ? n / 2 : n;            // GEGLU: a tile holds t/2 value + t/2 gate columns
     const uint64_t tiles_at_widest = static_cast<uint64_t>(tiles_m) * ((columns + (geglu ? 127 : 255)) / (geglu ? 128 : 256));
     const bool traffic_bound = grouped ? tiles_m >= 2 : tiles_at_widest >= 3ull * sms;
-    const bool pair_allowed = ctx->pair_mode != 0 && m > kTileM && (traffic_bound || ctx->pair_mode == 1);
+    // The diagnostic skip modes drop the loads that keep the two CTAs of a pair in step.
+    const bool pair_allowed = ctx->pair_mode != 0 && ctx->diagnostic_skip == 0 && m > kTileM &&
+                              (traffic_bound || ctx->pair_mode == 1);
     if (ctx->forced_tile_n >= 16) {
         const uint32_t forced = std::min<uint32_t>(kMaxTileN, static_cast<uint32_t>(ctx->forced_tile_n));
         const uint32_t pair_step = 32;
@@ -503,7 +508,7 @@ int prepare(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count, bo
             // n-major inside an m-tile keeps the CTAs of one wave on the same weight rows.
             for (uint32_t tn = 0; tn < problem.tiles_n; ++tn) {
                 for (uint32_t tm = 0; tm < problem.tiles_m; ++tm) {
-                    prep.tiles[flavour].push_back(TileRef{problem_index, static_cast<uint16_t>(tm), static_cast<uint16_t>(tn)});
+                    prep.tiles[flavour].push_back(make_tile_ref(problem, problem_index, tm, tn));
                 }
             }
         }

@@ -47,47 +47,26 @@ struct alignas(16) Control {
     alignas(16) __half column_bias_half[2][kMaxTileN];
 };
 
-// What the producer and the MMA issuer need to know about a tile, held in registers.
-struct TileWork {
-    const GemmProblem* problem;
-    uint32_t tile_m;
-    uint32_t tile_n_index;
-    uint32_t tile_n;
-    uint32_t k_blocks;
-    uint32_t idesc;
-    uint32_t kind;
-    uint32_t geglu;
-    uint32_t n_out;
-};
-
-// Single-problem launches read the problem from the kernel parameters (constant bank);
-// grouped launches read the tile list and the problem table from global memory.
-__device__ __forceinline__ TileWork fetch_tile(const GemmLaunchParams& params, uint32_t index) {
-    TileWork work;
+// The record of tile `index` of the launch. Single-problem launches build it from the kernel
+// parameters (constant bank); grouped launches read it from the tile list in global memory.
+// Indices past the end read the last record, so a role may always fetch one tile ahead.
+__device__ __forceinline__ TileRef load_tile(const GemmLaunchParams& params, uint32_t index) {
+    index = min(index, params.num_tiles - 1u);
     if (params.problems == nullptr) {
-        work.problem = &params.single;
-        work.tile_m = index % params.single.tiles_m;
-        work.tile_n_index = index / params.single.tiles_m;
-        work.tile_n = params.single.tile_n;
-        work.k_blocks = params.single.k_blocks;
-        work.idesc = params.single.idesc;
-        work.kind = params.single.ep.kind;
-        work.geglu = params.single.ep.activation == ACT_GEGLU ? 1u : 0u;
-        work.n_out = params.single.ep.n_out;
-    } else {
-        const TileRef ref = params.tiles[index];
-        const GemmProblem* problem = params.problems + ref.problem;
-        work.problem = problem;
-        work.tile_m = ref.tile_m;
-        work.tile_n_index = ref.tile_n;
-        work.tile_n = problem->tile_n;
-        work.k_blocks = problem->k_blocks;
-        work.idesc = problem->idesc;
-        work.kind = problem->ep.kind;
-        work.geglu = problem->ep.activation == ACT_GEGLU ? 1u : 0u;
-        work.n_out = problem->ep.n_out;
+        return make_tile_ref(params.single, 0u, index % params.single.tiles_m, index / params.single.tiles_m);
     }
-    return work;
+    const uint4* source = reinterpret_cast<const uint4*>(params.tiles + index);
+    union {
+        TileRef record;
+        uint4 words[4];
+    } u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) u.words[i] = __ldg(source + i);
+    return u.record;
+}
+
+__device__ __forceinline__ const GemmProblem* tile_problem(const GemmLaunchParams& params, const TileRef& tile) {
+    return params.problems == nullptr ? &params.single : params.problems + tile.problem;
 }
 
 __device__ __forceinline__ void raise_abort(Control* control, uint32_t* error_word, uint32_t code) {
@@ -99,32 +78,59 @@ __device__ __forceinline__ void epilogue_barrier() {
     asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
 }
 
-// Stages the weight scale and bias of each accumulator column of a tile into shared memory.
+// The weight scale and the bias of the accumulator columns one epilogue thread stages for a tile,
+// plus the activation scale of the thread's output row. Loaded into registers one tile ahead and
+// written to shared memory once the previous user of the slot is done.
 // Column j of a GEGLU tile is value column n0 + j for j < tile_n / 2 and gate column
 // n_out + n0 + (j - tile_n / 2) otherwise. Columns past the matrix edge get scale 0, bias 0.
-__device__ __forceinline__ void stage_columns(const EpilogueParams& ep, uint32_t tile_n, uint32_t tile_n_index,
-                                              float* column_scale, float* column_bias, __half* column_bias_half,
-                                              uint32_t thread) {
-    const bool geglu = ep.activation == ACT_GEGLU;
-    const bool scaled = ep.kind != KIND_F16;
-    const bool per_channel = scaled && ep.w_scale_per_channel != 0;
+constexpr uint32_t kColumnsPerThread = (kMaxTileN + 32 * kEpilogueWarps - 1) / (32 * kEpilogueWarps);
+
+struct ColumnOperands {
+    float scale[kColumnsPerThread];
+    __half bias[kColumnsPerThread];
+    float a_scale;
+};
+
+__device__ __forceinline__ ColumnOperands load_column_operands(const TileRef& tile, uint32_t thread, uint32_t row) {
+    ColumnOperands values;
+    const bool geglu = tile.activation == ACT_GEGLU;
+    const bool scaled = tile.kind != KIND_F16;
+    const bool per_channel = (tile.flags & TILE_SCALE_PER_CHANNEL) != 0;
+    const uint32_t tile_n = tile.tile_n;
     const uint32_t half = tile_n / 2;
-    const uint32_t per_tile = geglu ? half : tile_n;
-    const uint32_t n0 = tile_n_index * per_tile;
-    const float shared_scale = (scaled && !per_channel) ? __ldg(ep.w_scales) : 1.0f;
-    for (uint32_t j = thread; j < tile_n; j += 32 * kEpilogueWarps) {
+    const uint32_t n0 = tile.tile_n_index * (geglu ? half : tile_n);
+#pragma unroll
+    for (uint32_t i = 0; i < kColumnsPerThread; ++i) {
+        const uint32_t j = thread + i * 32 * kEpilogueWarps;
         const uint32_t local = (geglu && j >= half) ? j - half : j;
-        const bool valid = n0 + local < ep.n_out;
-        const uint32_t column = (geglu && j >= half) ? ep.n_out + n0 + local : n0 + local;
+        const bool valid = j < tile_n && n0 + local < tile.n_out;
+        const uint32_t column = (geglu && j >= half) ? tile.n_out + n0 + local : n0 + local;
         float scale = 0.0f;
         __half bias = __half(0);
         if (valid) {
-            scale = per_channel ? __ldg(ep.w_scales + column) : shared_scale;
-            if (ep.bias != nullptr) bias = ep.bias[column];
+            scale = scaled ? __ldg(tile.w_scales + (per_channel ? column : 0u)) : 1.0f;
+            if ((tile.flags & TILE_HAS_BIAS) != 0) bias = tile.bias[column];
         }
-        column_scale[j] = scale;
-        column_bias[j] = __half2float(bias);
-        column_bias_half[j] = bias;
+        values.scale[i] = scale;
+        values.bias[i] = bias;
+    }
+    values.a_scale = 1.0f;
+    if (tile.kind == KIND_I8) values.a_scale = row < tile.m ? __ldg(tile.a_scales + row) : 0.0f;
+    else if (tile.kind != KIND_F16) values.a_scale = __ldg(tile.a_scales);
+    return values;
+}
+
+__device__ __forceinline__ void store_column_operands(const ColumnOperands& values, uint32_t tile_n, uint32_t thread,
+                                                      float* column_scale, float* column_bias,
+                                                      __half* column_bias_half) {
+#pragma unroll
+    for (uint32_t i = 0; i < kColumnsPerThread; ++i) {
+        const uint32_t j = thread + i * 32 * kEpilogueWarps;
+        if (j < tile_n) {
+            column_scale[j] = values.scale[i];
+            column_bias[j] = __half2float(values.bias[i]);
+            column_bias_half[j] = values.bias[i];
+        }
     }
 }
 
@@ -136,32 +142,37 @@ __device__ __forceinline__ __half packed_half(const uint32_t word, int index) {
     return __ushort_as_half(static_cast<unsigned short>(index == 0 ? (word & 0xFFFFu) : (word >> 16)));
 }
 
-// W FP16 results of one output row, packed two per word -> global memory.
-template <int W>
-__device__ __forceinline__ void store_row_chunk(__half* y, uint32_t n_out, bool vector_ok, uint32_t row,
-                                                uint32_t col0, const uint32_t (&words)[W / 2]) {
+// 16 FP16 results of one output row, packed two per word -> global memory. `wide` (row pitch and
+// base 32-byte aligned) writes the 32 bytes with one 256-bit store so that each lane fills a
+// whole memory sector; `vector_ok` (16-byte aligned) uses two 128-bit stores.
+__device__ __forceinline__ void store_row_16(__half* y, uint32_t n_out, bool vector_ok, bool wide, uint32_t row,
+                                             uint32_t col0, const uint32_t (&words)[8]) {
     __half* destination = y + static_cast<size_t>(row) * n_out + col0;
-    if (vector_ok && col0 + W <= n_out) {
-#pragma unroll
-        for (int i = 0; i < W / 8; ++i) {
-            reinterpret_cast<uint4*>(destination)[i] =
-                make_uint4(words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
-        }
+    if (col0 + 16 <= n_out && wide) {
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(destination), "r"(words[0]),
+                     "r"(words[1]), "r"(words[2]), "r"(words[3]), "r"(words[4]), "r"(words[5]), "r"(words[6]),
+                     "r"(words[7])
+                     : "memory");
+    } else if (col0 + 16 <= n_out && vector_ok) {
+        reinterpret_cast<uint4*>(destination)[0] = make_uint4(words[0], words[1], words[2], words[3]);
+        reinterpret_cast<uint4*>(destination)[1] = make_uint4(words[4], words[5], words[6], words[7]);
     } else {
 #pragma unroll
-        for (int i = 0; i < W; ++i) {
+        for (int i = 0; i < 16; ++i) {
             if (col0 + i < n_out) destination[i] = packed_half(words[i >> 1], i & 1);
         }
     }
 }
 
-// Reads W consecutive staged FP32 values starting at column j0 (a multiple of 4) with 16-byte loads.
+// Reads W consecutive staged FP32 values starting at column j0 (a multiple of 4) with 16-byte
+// loads, as W / 2 pairs.
 template <int W>
-__device__ __forceinline__ void read_staged(const float* values, uint32_t j0, float (&out)[W]) {
+__device__ __forceinline__ void read_staged(const float* values, uint32_t j0, float2 (&out)[W / 2]) {
 #pragma unroll
     for (int i = 0; i < W / 4; ++i) {
         const float4 v = *reinterpret_cast<const float4*>(values + j0 + 4 * i);
-        out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
+        out[2 * i] = make_float2(v.x, v.y);
+        out[2 * i + 1] = make_float2(v.z, v.w);
     }
 }
 
@@ -175,17 +186,21 @@ __device__ __forceinline__ void read_staged_half(const __half* values, uint32_t 
     }
 }
 
-// The accumulator scaled to the projection value before its FP16 rounding.
+// Two accumulators scaled to the projection values before their FP16 rounding:
+// (acc * a_scale) * w_scale with both products rounded to FP32, as the reference's dequantisation
+// computes them, here on the packed FP32 pipe (each half rounds like the scalar multiply).
 template <uint32_t Kind>
-__device__ __forceinline__ float dequantise(uint32_t acc_bits, float a_scale, float w_scale) {
-    if (Kind == KIND_I8) return __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(acc_bits)), a_scale), w_scale);
-    if (Kind == KIND_F16) return __uint_as_float(acc_bits);
-    return __fmul_rn(__fmul_rn(__uint_as_float(acc_bits), a_scale), w_scale);
+__device__ __forceinline__ float2 dequantise2(uint32_t acc0, uint32_t acc1, float2 a_scale, float2 w_scale) {
+    if (Kind == KIND_F16) return make_float2(__uint_as_float(acc0), __uint_as_float(acc1));
+    const float2 raw = Kind == KIND_I8
+                           ? make_float2(static_cast<float>(static_cast<int32_t>(acc0)), static_cast<float>(static_cast<int32_t>(acc1)))
+                           : make_float2(__uint_as_float(acc0), __uint_as_float(acc1));
+    return __fmul2_rn(__fmul2_rn(raw, a_scale), w_scale);
 }
 
 // Two FP32 values -> two FP16 values in one word (round to nearest even), .x in the low half.
-__device__ __forceinline__ uint32_t to_half2_bits(float lo, float hi) {
-    const __half2 packed = __floats2half2_rn(lo, hi);
+__device__ __forceinline__ uint32_t to_half2_bits(float2 v) {
+    const __half2 packed = __float22half2_rn(v);
     return *reinterpret_cast<const uint32_t*>(&packed);
 }
 
@@ -206,10 +221,18 @@ struct EpilogueTile {
     uint32_t tile_n, n0;            // accumulator columns of the tile; first output column
     uint32_t row, tmem_row;
     uint32_t chunk_first;           // which of the warps of this TMEM lane quadrant
-    uint32_t flags;                 // bit 0 row in range, bit 1 has bias, bit 2 vector stores
+    uint32_t flags;                 // bit 0 row in range, bit 1 has bias, bit 2 16-byte stores, bit 3 32-byte stores
 };
 
-// Drains this warp's share of one accumulator tile. Kind: 0 INT8, 1 FP8 (either format), 3 FP16.
+// Tuning aid (flag bit 4): the results are computed but, except for one bit pattern that real data
+// all but never produces, not stored.
+__device__ __forceinline__ bool keep(uint32_t flags, const uint32_t (&words)[8]) {
+    return (flags & 16u) == 0 ||
+           (words[0] ^ words[1] ^ words[2] ^ words[3] ^ words[4] ^ words[5] ^ words[6] ^ words[7]) == 0x7FFF7FFEu;
+}
+
+// Drains this warp's share of one accumulator tile in chunks of 16 output columns.
+// Kind: 0 INT8, 1 FP8 (either format), 3 FP16.
 // Arithmetic per output, as the reference runs it after the GEMM:
 //   y = half_rn(dequantised accumulator)
 //   no activation : __hadd(y, bias)                           (add_last_dim_bias_kernel)
@@ -220,15 +243,17 @@ __device__ __noinline__ void epilogue_tile(const EpilogueTile t) {
     const bool row_ok = (t.flags & 1u) != 0;
     const bool has_bias = (t.flags & 2u) != 0;
     const bool store_vector = (t.flags & 4u) != 0;
+    const bool store_wide = (t.flags & 8u) != 0;
+    const float2 a_scale = make_float2(t.a_scale, t.a_scale);
     int32_t* const acc_out = Kind == KIND_I8 ? t.acc_out : nullptr;
+    constexpr int W = 16;
     if (Act != ACT_GEGLU) {
-        constexpr int W = 16;
         for (uint32_t c0 = t.chunk_first * W; c0 < t.tile_n; c0 += kWarpsPerQuadrant * W) {
             const uint32_t col0 = t.n0 + c0;
             if (col0 >= t.n) break;
             uint32_t acc[W];
             ptx::tmem_ld_32x32b_x16(t.tmem_row + c0, acc);
-            float w_scale[W];
+            float2 w_scale[W / 2];
             read_staged<W>(t.column_scale, c0, w_scale);
             ptx::tmem_ld_wait();
             if (acc_out != nullptr && row_ok) {
@@ -240,9 +265,8 @@ __device__ __noinline__ void epilogue_tile(const EpilogueTile t) {
             }
             uint32_t out_words[W / 2];
 #pragma unroll
-            for (int i = 0; i < W; i += 2) {
-                out_words[i >> 1] = to_half2_bits(dequantise<Kind>(acc[i], t.a_scale, w_scale[i]),
-                                                  dequantise<Kind>(acc[i + 1], t.a_scale, w_scale[i + 1]));
+            for (int i = 0; i < W / 2; ++i) {
+                out_words[i] = to_half2_bits(dequantise2<Kind>(acc[2 * i], acc[2 * i + 1], a_scale, w_scale[i]));
             }
             if (has_bias) {
                 if (Act == ACT_NONE) {
@@ -255,57 +279,60 @@ __device__ __noinline__ void epilogue_tile(const EpilogueTile t) {
                         out_words[i] = *reinterpret_cast<const uint32_t*>(&sum);
                     }
                 } else {
-                    float bias[W];
+                    float2 bias[W / 2];
                     read_staged<W>(t.column_bias, c0, bias);
 #pragma unroll
                     for (int i = 0; i < W / 2; ++i) {
-                        const float2 y = from_half2_bits(out_words[i]);
-                        out_words[i] = to_half2_bits(activate(y.x + bias[2 * i], Act), activate(y.y + bias[2 * i + 1], Act));
+                        const float2 x = __fadd2_rn(from_half2_bits(out_words[i]), bias[i]);
+                        out_words[i] = to_half2_bits(Act == ACT_GELU ? gelu_erf2(x)
+                                                                     : make_float2(activate(x.x, Act), activate(x.y, Act)));
                     }
                 }
             }
-            if (row_ok) store_row_chunk<W>(t.y, t.n_out, store_vector, t.row, col0, out_words);
+            if (row_ok && keep(t.flags, out_words)) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
         }
     } else {
-        constexpr int W = 8;
         const uint32_t half = t.tile_n / 2;
         for (uint32_t c0 = t.chunk_first * W; c0 < half; c0 += kWarpsPerQuadrant * W) {
             const uint32_t col0 = t.n0 + c0;
             if (col0 >= t.n_out) break;
-            uint32_t acc_value[W], acc_gate[W];
-            ptx::tmem_ld_32x32b_x8(t.tmem_row + c0, acc_value);
-            ptx::tmem_ld_32x32b_x8(t.tmem_row + half + c0, acc_gate);
-            float w_value[W], w_gate[W], b_value[W], b_gate[W];
-            read_staged<W>(t.column_scale, c0, w_value);
-            read_staged<W>(t.column_scale, half + c0, w_gate);
-            read_staged<W>(t.column_bias, c0, b_value);
-            read_staged<W>(t.column_bias, half + c0, b_gate);
-            ptx::tmem_ld_wait();
-            if (acc_out != nullptr && row_ok) {
-                int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n;
+            uint32_t out_words[W / 2];
+            // two steps of 8 columns keep the live accumulators and column operands at 8 + 8
 #pragma unroll
-                for (int i = 0; i < W; ++i) {
-                    if (col0 + i < t.n_out) {
-                        raw[col0 + i] = static_cast<int32_t>(acc_value[i]);
-                        raw[t.n_out + col0 + i] = static_cast<int32_t>(acc_gate[i]);
+            for (int step = 0; step < 2; ++step) {
+                const uint32_t c = c0 + 8u * step;
+                uint32_t acc_value[8], acc_gate[8];
+                ptx::tmem_ld_32x32b_x8(t.tmem_row + c, acc_value);
+                ptx::tmem_ld_32x32b_x8(t.tmem_row + half + c, acc_gate);
+                float2 w_value[4], w_gate[4], b_value[4], b_gate[4];
+                read_staged<8>(t.column_scale, c, w_value);
+                read_staged<8>(t.column_scale, half + c, w_gate);
+                read_staged<8>(t.column_bias, c, b_value);
+                read_staged<8>(t.column_bias, half + c, b_gate);
+                ptx::tmem_ld_wait();
+                if (acc_out != nullptr && row_ok) {
+                    int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        if (col0 + 8u * step + i < t.n_out) {
+                            raw[col0 + 8u * step + i] = static_cast<int32_t>(acc_value[i]);
+                            raw[t.n_out + col0 + 8u * step + i] = static_cast<int32_t>(acc_gate[i]);
+                        }
                     }
                 }
-            }
-            uint32_t out_words[W / 2];
 #pragma unroll
-            for (int i = 0; i < W; i += 2) {
-                float result[2];
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    // one packed conversion rounds the value and the gate projection to FP16
-                    const float2 y = from_half2_bits(to_half2_bits(
-                        dequantise<Kind>(acc_value[i + j], t.a_scale, w_value[i + j]),
-                        dequantise<Kind>(acc_gate[i + j], t.a_scale, w_gate[i + j])));
-                    result[j] = (y.x + b_value[i + j]) * gelu_erf(y.y + b_gate[i + j]);
+                for (int i = 0; i < 4; ++i) {
+                    // both projections are rounded to FP16 before the bias is added in FP32
+                    const float2 value = __fadd2_rn(
+                        from_half2_bits(to_half2_bits(dequantise2<Kind>(acc_value[2 * i], acc_value[2 * i + 1], a_scale, w_value[i]))),
+                        b_value[i]);
+                    const float2 gate = __fadd2_rn(
+                        from_half2_bits(to_half2_bits(dequantise2<Kind>(acc_gate[2 * i], acc_gate[2 * i + 1], a_scale, w_gate[i]))),
+                        b_gate[i]);
+                    out_words[4 * step + i] = to_half2_bits(__fmul2_rn(value, gelu_erf2(gate)));
                 }
-                out_words[i >> 1] = to_half2_bits(result[0], result[1]);
             }
-            if (row_ok) store_row_chunk<W>(t.y, t.n_out, store_vector, t.row, col0, out_words);
+            if (row_ok && keep(t.flags, out_words)) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
         }
     }
 }
@@ -346,7 +373,9 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
     volatile uint32_t* abort_word = &control->abort;
     const long long limit = params.wait_limit_cycles;
     const bool skip_epilogue = (params.diagnostic_skip & 1u) != 0;
-    const bool skip_mainloop = (params.diagnostic_skip & 2u) != 0;
+    const bool skip_loads = (params.diagnostic_skip & (2u | 4u)) != 0;
+    const bool skip_mma = (params.diagnostic_skip & (2u | 8u)) != 0;
+    const bool skip_stores = (params.diagnostic_skip & 16u) != 0;
     const uint32_t cta_rank = kPair ? ptx::cluster_cta_rank() : 0u;
     const bool leader = cta_rank == 0;
     const uint32_t first_tile = kPair ? blockIdx.x >> 1 : blockIdx.x;
@@ -387,25 +416,29 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             uint32_t issued_mask = 0, issued_phase = 0;
             const GemmProblem* bound = nullptr;
             bool ok = true;
+            TileRef next = load_tile(params, first_tile);
             for (uint32_t t = first_tile; ok && t < num_tiles; t += tile_stride) {
-                const TileWork work = fetch_tile(params, t);
-                const CUtensorMap* tmap_a = &work.problem->tmap_a;
-                const CUtensorMap* tmap_b = &work.problem->tmap_b;
-                if (params.problems != nullptr && work.problem != bound) {
+                const TileRef work = next;
+                next = load_tile(params, t + tile_stride);      // in flight while this tile's loads are issued
+                const GemmProblem* problem = tile_problem(params, work);
+                const CUtensorMap* tmap_a = &problem->tmap_a;
+                const CUtensorMap* tmap_b = &problem->tmap_b;
+                if (params.problems != nullptr && problem != bound) {
                     ptx::fence_tensormap_acquire(tmap_a);
                     ptx::fence_tensormap_acquire(tmap_b);
-                    bound = work.problem;
+                    bound = problem;
                 }
+                const bool geglu = work.activation == ACT_GEGLU;
                 const uint32_t tile_n = work.tile_n;
                 const uint32_t half = tile_n / 2;
                 // bytes that land per stage, over both CTAs of a pair
                 const uint32_t tx_bytes = (kPair ? 2 * kTileM + tile_n : kTileM + tile_n) * kTileKBytes;
                 const int32_t k_step = work.kind == KIND_F16 ? 64 : 128;   // elements per stage
                 const int32_t row_a = static_cast<int32_t>(work.tile_m * kRowsPerTile + cta_rank * kTileM);
-                const int32_t row_b = static_cast<int32_t>(work.tile_n_index * (work.geglu ? half : tile_n));
+                const int32_t row_b = static_cast<int32_t>(work.tile_n_index * (geglu ? half : tile_n));
                 const int32_t row_gate = static_cast<int32_t>(work.n_out) + row_b;
                 // pair: this CTA's half of the B rows (GEGLU: value rows in the leader, gate rows in the peer)
-                const int32_t row_b_pair = work.geglu ? (leader ? row_b : row_gate)
+                const int32_t row_b_pair = geglu ? (leader ? row_b : row_gate)
                                                       : row_b + static_cast<int32_t>(cta_rank * half);
                 const uint32_t k_blocks = work.k_blocks;
                 for (uint32_t kb = 0; kb < k_blocks; ++kb) {
@@ -419,7 +452,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                     const uint32_t a_dst = stages_base + stage * stage_bytes;
                     const uint32_t b_dst = a_dst + b_offset;
                     const int32_t k0 = static_cast<int32_t>(kb) * k_step;
-                    if (skip_mainloop) {
+                    if (skip_loads) {
                         if (leader) ptx::mbar_arrive(full_bar);
                     } else if (kPair) {
                         if (leader) ptx::mbar_expect_tx(full_bar, tx_bytes);
@@ -429,7 +462,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                         ptx::mbar_expect_tx(full_bar, tx_bytes);
                         ptx::tma_load_2d(a_dst, tmap_a, full_bar, k0, row_a);
                         ptx::tma_load_2d(b_dst, tmap_b, full_bar, k0, row_b);
-                        if (work.geglu) ptx::tma_load_2d(b_dst + half * kTileKBytes, tmap_b, full_bar, k0, row_gate);
+                        if (geglu) ptx::tma_load_2d(b_dst + half * kTileKBytes, tmap_b, full_bar, k0, row_gate);
                     }
                     issued_mask |= 1u << stage;
                     issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
@@ -451,8 +484,10 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
         if (lane == 0 && leader) {
             uint32_t stage = 0, phase = 0, iteration = 0;
             bool ok = true;
+            TileRef next = load_tile(params, first_tile);
             for (uint32_t t = first_tile; ok && t < num_tiles; t += tile_stride, ++iteration) {
-                const TileWork work = fetch_tile(params, t);
+                const TileRef work = next;
+                next = load_tile(params, t + tile_stride);      // in flight while this tile's MMAs are issued
                 const uint32_t buffer = iteration & 1u;
                 const uint32_t accumulator_phase = (iteration >> 1) & 1u;
                 if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->tmem_empty[buffer]),
@@ -478,7 +513,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                     const uint64_t desc_b = ptx::umma_smem_desc_sw128(a_addr + b_offset);
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k) {   // 4 x 32 bytes of K per stage
-                        if (skip_mainloop) break;
+                        if (skip_mma) break;
                         const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
                         const uint64_t advance = static_cast<uint64_t>(k * 2);   // 32 B >> 4
                         if (kPair) {
@@ -518,37 +553,46 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
         const uint32_t quadrant = warp & 3u;
         const uint32_t chunk_first = (warp - 2u) >> 2;      // 0 .. kWarpsPerQuadrant - 1
         const uint32_t epilogue_thread = threadIdx.x - 64u;
+        const uint32_t row_in_tile = cta_rank * kTileM + quadrant * 32u + lane;
         uint32_t iteration = 0;
         bool ok = true;
+        // Software pipeline over this CTA's tiles: the record of tile i + 2 and the column operands
+        // of tile i + 1 are loaded into registers while tile i is drained, so that no global-memory
+        // latency sits between two tiles.
+        TileRef work = load_tile(params, first_tile);
+        TileRef next = load_tile(params, first_tile + tile_stride);
+        ColumnOperands operands = load_column_operands(work, epilogue_thread, work.tile_m * kRowsPerTile + row_in_tile);
+        store_column_operands(operands, work.tile_n, epilogue_thread, control->column_scale[0], control->column_bias[0],
+                              control->column_bias_half[0]);
         for (uint32_t t = first_tile; t < num_tiles; t += tile_stride, ++iteration) {
-            const TileWork work = fetch_tile(params, t);
-            const EpilogueParams& ep = params.problems == nullptr ? params.single.ep : work.problem->ep;
             const uint32_t buffer = iteration & 1u;
             const uint32_t accumulator_phase = (iteration >> 1) & 1u;
-            // Stage this tile's column operands while the main loop is still running. The slot
-            // was last read two tiles ago; every warp passed the previous tile's barrier since.
-            stage_columns(ep, work.tile_n, work.tile_n_index, control->column_scale[buffer],
-                          control->column_bias[buffer], control->column_bias_half[buffer], epilogue_thread);
+            const float a_scale = operands.a_scale;
+            const TileRef after_next = load_tile(params, t + 2u * tile_stride);
+            operands = load_column_operands(next, epilogue_thread, next.tile_m * kRowsPerTile + row_in_tile);
+            const bool geglu = work.activation == ACT_GEGLU;
             EpilogueTile tile;
-            tile.y = ep.y;
-            tile.acc_out = ep.acc_out;
+            tile.y = work.y;
+            tile.acc_out = nullptr;
+            if ((work.flags & TILE_RAW_ACCUMULATORS) != 0) tile.acc_out = tile_problem(params, work)->ep.acc_out;
             tile.column_scale = control->column_scale[buffer];
             tile.column_bias = control->column_bias[buffer];
             tile.column_bias_half = control->column_bias_half[buffer];
-            tile.n = ep.n;
-            tile.n_out = ep.n_out;
+            tile.n = work.n;
+            tile.n_out = work.n_out;
             tile.tile_n = work.tile_n;
-            tile.n0 = work.tile_n_index * (work.geglu ? work.tile_n / 2 : work.tile_n);
-            tile.row = work.tile_m * kRowsPerTile + cta_rank * kTileM + quadrant * 32u + lane;
+            tile.n0 = work.tile_n_index * (geglu ? work.tile_n / 2u : work.tile_n);
+            tile.row = work.tile_m * kRowsPerTile + row_in_tile;
             tile.tmem_row = tmem_base + ((quadrant * 32u) << 16) + buffer * kMaxTileN;
             tile.chunk_first = chunk_first;
-            const bool row_ok = tile.row < ep.m;
-            tile.flags = (row_ok ? 1u : 0u) | (ep.bias != nullptr ? 2u : 0u) | (ep.vector_store_ok != 0 ? 4u : 0u);
-            const uint32_t kind = ep.kind;
-            const uint32_t activation = ep.activation;
-            tile.a_scale = 1.0f;
-            if (kind == KIND_I8) tile.a_scale = row_ok ? __ldg(ep.a_scales + tile.row) : 0.0f;
-            else if (kind != KIND_F16) tile.a_scale = __ldg(ep.a_scales);
+            tile.flags = (tile.row < work.m ? 1u : 0u) | ((work.flags & TILE_HAS_BIAS) != 0 ? 2u : 0u) |
+                         ((work.flags & TILE_STORE_16) != 0 ? 4u : 0u) | ((work.flags & TILE_STORE_32) != 0 ? 8u : 0u) |
+                         (skip_stores ? 16u : 0u);
+            const uint32_t kind = work.kind;
+            const uint32_t activation = work.activation;
+            tile.a_scale = a_scale;
+            // Every warp is done with tile i - 1 here, so the other slot may be rewritten below;
+            // this tile's slot was written before the barrier.
             epilogue_barrier();
             if (ok && !ptx::mbar_wait_bounded(ptx::smem_u32(&control->tmem_full[buffer]), accumulator_phase,
                                               abort_word, limit)) {
@@ -557,19 +601,25 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             }
             // After a timeout the warp keeps walking the tile list (so that the barrier above
             // stays balanced) but touches neither TMEM nor global memory again.
-            if (!ok) continue;
-            ptx::tc_fence_after();
-            if (skip_epilogue) { /* diagnostic: accumulators are dropped */ }
-            else if (kind == KIND_I8) epilogue_dispatch<KIND_I8>(activation, tile);
-            else if (kind == KIND_F16) epilogue_dispatch<KIND_F16>(activation, tile);
-            else epilogue_dispatch<KIND_E4M3>(activation, tile);
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                const uint32_t empty_bar = ptx::smem_u32(&control->tmem_empty[buffer]);
-                if (kPair) ptx::mbar_arrive_cluster(empty_bar & ptx::kPeerBitMask);   // the leader's barrier
-                else ptx::mbar_arrive(empty_bar);
+            if (ok) {
+                ptx::tc_fence_after();
+                if (skip_epilogue) { /* diagnostic: accumulators are dropped */ }
+                else if (kind == KIND_I8) epilogue_dispatch<KIND_I8>(activation, tile);
+                else if (kind == KIND_F16) epilogue_dispatch<KIND_F16>(activation, tile);
+                else epilogue_dispatch<KIND_E4M3>(activation, tile);
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    const uint32_t empty_bar = ptx::smem_u32(&control->tmem_empty[buffer]);
+                    if (kPair) ptx::mbar_arrive_cluster(empty_bar & ptx::kPeerBitMask);   // the leader's barrier
+                    else ptx::mbar_arrive(empty_bar);
+                }
             }
+            // The next tile's column operands (loaded above) go into the other slot.
+            store_column_operands(operands, next.tile_n, epilogue_thread, control->column_scale[buffer ^ 1u],
+                                  control->column_bias[buffer ^ 1u], control->column_bias_half[buffer ^ 1u]);
+            work = next;
+            next = after_next;
         }
     }
 

@@ -56,11 +56,63 @@ struct alignas(64) GemmProblem {
     uint32_t pad[3];
 };
 
-struct TileRef {
-    uint32_t problem;
-    uint16_t tile_m;
-    uint16_t tile_n;
+// One tile of a launch: everything the three kernel roles need to start on it, in one 64-byte
+// record, so that a role can fetch the record of its next tile while it works on the current one
+// and never chases a pointer between tiles.
+enum TileFlags : uint16_t {
+    TILE_HAS_BIAS = 1,          // bias != null
+    TILE_SCALE_PER_CHANNEL = 2, // w_scales has one entry per weight row (else one entry)
+    TILE_STORE_16 = 4,          // y rows 16-byte aligned and n_out % 8 == 0
+    TILE_STORE_32 = 8,          // y rows 32-byte aligned and n_out % 16 == 0
+    TILE_RAW_ACCUMULATORS = 16, // the problem also wants its INT32 accumulators (ep.acc_out)
 };
+
+struct alignas(64) TileRef {
+    uint32_t problem;            // index into the problem table (tensor maps, acc_out)
+    uint16_t tile_m;
+    uint16_t tile_n_index;
+    uint32_t idesc;              // UMMA instruction descriptor
+    uint32_t n_out;
+    uint16_t k_blocks;
+    uint16_t tile_n;             // accumulator columns of the tile
+    uint8_t kind;                // GemmKind
+    uint8_t activation;          // Activation
+    uint16_t flags;              // TileFlags
+    uint32_t m, n;
+    const float* w_scales;
+    const __half* bias;
+    __half* y;
+    const float* a_scales;
+};
+static_assert(sizeof(TileRef) == 64, "a tile record is one 64-byte line");
+
+// The record of tile (tile_m, tile_n_index) of `problem` (table index `problem_index`).
+__host__ __device__ inline TileRef make_tile_ref(const GemmProblem& problem, uint32_t problem_index, uint32_t tile_m,
+                                                 uint32_t tile_n_index) {
+    const EpilogueParams& ep = problem.ep;
+    TileRef r;
+    r.problem = problem_index;
+    r.tile_m = static_cast<uint16_t>(tile_m);
+    r.tile_n_index = static_cast<uint16_t>(tile_n_index);
+    r.idesc = problem.idesc;
+    r.n_out = ep.n_out;
+    r.k_blocks = static_cast<uint16_t>(problem.k_blocks);
+    r.tile_n = static_cast<uint16_t>(problem.tile_n);
+    r.kind = static_cast<uint8_t>(ep.kind);
+    r.activation = static_cast<uint8_t>(ep.activation);
+    const bool store_32 = ep.vector_store_ok != 0 && ep.n_out % 16 == 0 && reinterpret_cast<uintptr_t>(ep.y) % 32 == 0;
+    r.flags = static_cast<uint16_t>((ep.bias != nullptr ? TILE_HAS_BIAS : 0) |
+                                    (ep.kind != KIND_F16 && ep.w_scale_per_channel != 0 ? TILE_SCALE_PER_CHANNEL : 0) |
+                                    (ep.vector_store_ok != 0 ? TILE_STORE_16 : 0) | (store_32 ? TILE_STORE_32 : 0) |
+                                    (ep.acc_out != nullptr ? TILE_RAW_ACCUMULATORS : 0));
+    r.m = ep.m;
+    r.n = ep.n;
+    r.w_scales = ep.w_scales;
+    r.bias = ep.bias;
+    r.y = ep.y;
+    r.a_scales = ep.a_scales;
+    return r;
+}
 
 struct GemmLaunchParams {
     const GemmProblem* problems; // device table (grouped) or null (single: `single` is used)
@@ -71,9 +123,9 @@ struct GemmLaunchParams {
     uint32_t b_offset;           // offset of the B tile inside a stage (= 128 rows * 128 B)
     uint32_t* error_word;        // device word set on a bounded-wait timeout
     long long wait_limit_cycles;
-    uint32_t diagnostic_skip;    // tuning aid: bit 0 skips the epilogue arithmetic and stores, bit 1 skips
-                                 // the operand loads and MMAs (barriers are still signalled); results are
-                                 // meaningless when set
+    uint32_t diagnostic_skip;    // tuning aid, results are meaningless when set. bit 0: no epilogue arithmetic or
+                                 // stores; bit 1: no operand loads, no MMAs; bit 2: no operand loads; bit 3: no
+                                 // MMAs; bit 4: epilogue arithmetic without stores. Barriers are still signalled.
     uint32_t pad0;
     GemmProblem single;
 };
@@ -126,6 +178,32 @@ __device__ __forceinline__ float one_plus_erf(float x) {
 // (apply_linear_activation / bias_geglu_kernel, src/cuda/ops_kernels.cu:128-183).
 __device__ __forceinline__ float gelu_erf(float x) {
     return (0.5f * x) * one_plus_erf(x);
+}
+
+// Two evaluations of one_plus_erf at once on the packed FP32 pipe (fma.rn.f32x2 rounds each half
+// like the scalar fma.rn, so both halves equal the scalar function bit for bit).
+__device__ __forceinline__ float2 one_plus_erf2(float2 x) {
+    const float2 u = __fmul2_rn(x, make_float2(0.7071067811865475f, 0.7071067811865475f));
+    const float2 t = make_float2(fminf(fabsf(u.x), 4.6f), fminf(fabsf(u.y), 4.6f));
+    float2 r = make_float2(-2.6164917699134094e-07f, -2.6164917699134094e-07f);
+    r = __ffma2_rn(r, t, make_float2(6.632982149312738e-06f, 6.632982149312738e-06f));
+    r = __ffma2_rn(r, t, make_float2(-7.087277481332421e-05f, -7.087277481332421e-05f));
+    r = __ffma2_rn(r, t, make_float2(0.0003955792635679245f, 0.0003955792635679245f));
+    r = __ffma2_rn(r, t, make_float2(-0.0009763258858583868f, -0.0009763258858583868f));
+    r = __ffma2_rn(r, t, make_float2(-0.0020724914502352476f, -0.0020724914502352476f));
+    r = __ffma2_rn(r, t, make_float2(0.029831526800990105f, 0.029831526800990105f));
+    r = __ffma2_rn(r, t, make_float2(-0.14946085214614868f, -0.14946085214614868f));
+    r = __ffma2_rn(r, t, make_float2(-0.9181336760520935f, -0.9181336760520935f));
+    r = __ffma2_rn(r, t, make_float2(-1.6279360055923462f, -1.6279360055923462f));
+    const float2 exponent = __fmul2_rn(r, t);
+    float2 e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(exponent.x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(exponent.y));
+    return make_float2(u.x >= 0.0f ? 2.0f - e.x : e.x, u.y >= 0.0f ? 2.0f - e.y : e.y);
+}
+
+__device__ __forceinline__ float2 gelu_erf2(float2 x) {
+    return __fmul2_rn(__fmul2_rn(x, make_float2(0.5f, 0.5f)), one_plus_erf2(x));
 }
 
 // SiLU / GELU / QuickGELU on the FP32 value (ACT_NONE returns x).
