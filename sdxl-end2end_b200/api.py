@@ -343,9 +343,12 @@ def _ptr(tensor: Optional[torch.Tensor]):
 class Ops:
     """The projection operators of sdxl::cuda::Ops (include/sdxl/cuda/ops.hpp:17-30)."""
 
-    def __init__(self, context: Context):
+    def __init__(self, context: Context, poison_outputs: bool = False):
         self.ctx = context
         self._lib = context._lib
+        # Tests set this: outputs this class allocates start as NaN, so that an element a kernel
+        # failed to write cannot pass for a result left in recycled memory.
+        self.poison_outputs = poison_outputs
 
     # -- descriptor ---------------------------------------------------------------------------
     def _desc(self, call: LinearCall) -> _CLinearDesc:
@@ -373,6 +376,8 @@ class Ops:
         if call.y is None:
             device = (x if x is not None else call.xq).device
             call.y = torch.empty(lead + (n_out,), dtype=torch.float16, device=device)
+            if self.poison_outputs:
+                call.y.fill_(float("nan"))
         return _CLinearDesc(_ptr(x), m, weight.c_struct(), _ptr(call.bias), int(call.activation), 0,
                             _ptr(call.y), _ptr(call.xq), _ptr(call.xq_scales), _ptr(call.acc_out))
 

@@ -134,10 +134,6 @@ __device__ __forceinline__ void store_column_operands(const ColumnOperands& valu
     }
 }
 
-__device__ __forceinline__ uint32_t pack_halves(__half lo, __half hi) {
-    return static_cast<uint32_t>(__half_as_ushort(lo)) | (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
-}
-
 __device__ __forceinline__ __half packed_half(const uint32_t word, int index) {
     return __ushort_as_half(static_cast<unsigned short>(index == 0 ? (word & 0xFFFFu) : (word >> 16)));
 }
@@ -350,6 +346,51 @@ __device__ __forceinline__ void epilogue_dispatch(uint32_t activation, const Epi
 
 }  // namespace
 
+// Where the MMA issuer stands in the ring of pipeline stages, plus the loop constants.
+struct MmaCursor {
+    uint32_t stage, phase, num_stages;
+    uint32_t full_base, empty_base;     // shared-memory addresses of full[0] / empty[0]
+    uint32_t a_lo_base;                 // descriptor low word of stage 0's A tile
+    uint32_t stage_units, b_units;      // stage size and B offset in descriptor units (16 bytes)
+    volatile uint32_t* abort_word;
+    long long limit;
+    uint32_t mode;                      // diagnostics: bit 0 no MMAs, bit 1 one MMA per stage
+};
+
+// Issues the MMAs of one tile: k_blocks stages of four MMAs each, into the accumulator at tmem_d.
+// Returns false when a wait for a full stage ran out.
+template <int KindTag, bool kPair>
+__device__ __forceinline__ bool issue_tile_mmas(MmaCursor& c, uint32_t tmem_d, uint32_t idesc, uint32_t k_blocks) {
+    uint32_t stage = c.stage, phase = c.phase;
+    uint32_t accumulate = 0;
+    for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        if (!ptx::mbar_wait_bounded(c.full_base + stage * 8u, phase, c.abort_word, c.limit)) return false;
+        ptx::tc_fence_after();
+        const uint32_t a_lo = c.a_lo_base + stage * c.stage_units;
+        if (c.mode == 0) {
+            ptx::umma_stage<KindTag, kPair>(tmem_d, a_lo, a_lo + c.b_units, ptx::kUmmaDescHiSw128, idesc, accumulate);
+        } else if (c.mode == 2 && KindTag != 0) {   // the one-MMA diagnostic exists for INT8 only
+            ptx::umma_stage<KindTag, kPair>(tmem_d, a_lo, a_lo + c.b_units, ptx::kUmmaDescHiSw128, idesc, accumulate);
+        } else if (c.mode == 2) {
+            const uint64_t hi = static_cast<uint64_t>(ptx::kUmmaDescHiSw128) << 32;
+            if (kPair) ptx::umma_i8_pair(tmem_d, hi | a_lo, hi | (a_lo + c.b_units), idesc, accumulate);
+            else ptx::umma_i8(tmem_d, hi | a_lo, hi | (a_lo + c.b_units), idesc, accumulate);
+        }
+        accumulate = 1;
+        const uint32_t empty_bar = c.empty_base + stage * 8u;
+        if (kPair) {
+            ptx::umma_commit_pair(empty_bar);                        // frees the leader's stage
+            ptx::umma_commit_pair(ptx::map_to_cta(empty_bar, 1));    // and the peer's
+        } else {
+            ptx::umma_commit(empty_bar);
+        }
+        if (++stage == c.num_stages) { stage = 0; phase ^= 1u; }
+    }
+    c.stage = stage;
+    c.phase = phase;
+    return true;
+}
+
 // kPair = false: one CTA per 128-row tile (cta_group::1).
 // kPair = true : a cluster of two CTAs per 256-row tile (cta_group::2). Each CTA loads its own 128
 //   rows of A and half of the tile's B rows (for GEGLU: the leader the value rows, its peer the
@@ -376,6 +417,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
     const bool skip_loads = (params.diagnostic_skip & (2u | 4u)) != 0;
     const bool skip_mma = (params.diagnostic_skip & (2u | 8u)) != 0;
     const bool skip_stores = (params.diagnostic_skip & 16u) != 0;
+    const bool one_mma_per_stage = (params.diagnostic_skip & 32u) != 0;
     const uint32_t cta_rank = kPair ? ptx::cluster_cta_rank() : 0u;
     const bool leader = cta_rank == 0;
     const uint32_t first_tile = kPair ? blockIdx.x >> 1 : blockIdx.x;
@@ -413,10 +455,14 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
         // ------------------------------- TMA producer -------------------------------------
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
-            uint32_t issued_mask = 0, issued_phase = 0;
+            uint32_t issued = 0;                     // stages handed to the copy engine so far
+            const uint32_t full_base = ptx::smem_u32(&control->full[0]);
+            const uint32_t empty_base = ptx::smem_u32(&control->empty[0]);
             const GemmProblem* bound = nullptr;
             bool ok = true;
             TileRef next = load_tile(params, first_tile);
+            // diagnostic without loads: only the leader's arrivals count, its peer has nothing to do
+            if (kPair && skip_loads && !leader) ok = false;
             for (uint32_t t = first_tile; ok && t < num_tiles; t += tile_stride) {
                 const TileRef work = next;
                 next = load_tile(params, t + tile_stride);      // in flight while this tile's loads are issued
@@ -441,17 +487,16 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                 const int32_t row_b_pair = geglu ? (leader ? row_b : row_gate)
                                                       : row_b + static_cast<int32_t>(cta_rank * half);
                 const uint32_t k_blocks = work.k_blocks;
-                for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-                    const uint32_t full_bar = ptx::smem_u32(&control->full[stage]);
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->empty[stage]), phase ^ 1u,
-                                                abort_word, limit)) {
+                int32_t k0 = 0;
+                for (uint32_t kb = 0; kb < k_blocks; ++kb, k0 += k_step) {
+                    if (!ptx::mbar_wait_bounded(empty_base + stage * 8u, phase ^ 1u, abort_word, limit)) {
                         raise_abort(control, params.error_word, DEV_TIMEOUT_PRODUCER);
                         ok = false;
                         break;
                     }
+                    const uint32_t full_bar = full_base + stage * 8u;
                     const uint32_t a_dst = stages_base + stage * stage_bytes;
                     const uint32_t b_dst = a_dst + b_offset;
-                    const int32_t k0 = static_cast<int32_t>(kb) * k_step;
                     if (skip_loads) {
                         if (leader) ptx::mbar_arrive(full_bar);
                     } else if (kPair) {
@@ -464,25 +509,39 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                         ptx::tma_load_2d(b_dst, tmap_b, full_bar, k0, row_b);
                         if (geglu) ptx::tma_load_2d(b_dst + half * kTileKBytes, tmap_b, full_bar, k0, row_gate);
                     }
-                    issued_mask |= 1u << stage;
-                    issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
+                    ++issued;
                     if (++stage == num_stages) { stage = 0; phase ^= 1u; }
                 }
             }
-            if (!ok && (!kPair || leader)) {
-                // Let the copies this thread started land before the CTA retires.
-                for (uint32_t s = 0; s < num_stages; ++s) {
-                    if (issued_mask & (1u << s)) {
-                        (void)ptx::mbar_wait_bounded(ptx::smem_u32(&control->full[s]),
-                                                     (issued_phase >> s) & 1u, abort_word, limit >> 4);
-                    }
+            if (!ok && (!kPair || leader) && !skip_loads) {
+                // Let the copies this thread started land before the CTA retires: the last
+                // min(issued, num_stages) stages may still be in flight.
+                const uint32_t pending = min(issued, num_stages);
+                for (uint32_t i = issued - pending; i < issued; ++i) {
+                    (void)ptx::mbar_wait_bounded(full_base + (i % num_stages) * 8u, (i / num_stages) & 1u, abort_word,
+                                                 limit >> 4);
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------- MMA issuer ---------------------------------------
+        // One thread issues every MMA of the CTA (of the pair). Its loop is the critical path of
+        // the kernel: per stage it runs one barrier poll, one fence, one statement with the four
+        // MMAs and one commit, all on 32-bit values kept in registers.
         if (lane == 0 && leader) {
-            uint32_t stage = 0, phase = 0, iteration = 0;
+            MmaCursor cursor;
+            cursor.stage = 0;
+            cursor.phase = 0;
+            cursor.num_stages = num_stages;
+            cursor.full_base = ptx::smem_u32(&control->full[0]);
+            cursor.empty_base = ptx::smem_u32(&control->empty[0]);
+            cursor.a_lo_base = ptx::umma_desc_lo(stages_base);
+            cursor.stage_units = stage_bytes >> 4;
+            cursor.b_units = b_offset >> 4;
+            cursor.abort_word = abort_word;
+            cursor.limit = limit;
+            cursor.mode = (skip_mma ? 1u : 0u) | (one_mma_per_stage ? 2u : 0u);
+            uint32_t iteration = 0;
             bool ok = true;
             TileRef next = load_tile(params, first_tile);
             for (uint32_t t = first_tile; ok && t < num_tiles; t += tile_stride, ++iteration) {
@@ -497,52 +556,19 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                 }
                 ptx::tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buffer * kMaxTileN;
-                const uint32_t idesc = work.idesc;
-                const uint32_t kind = work.kind;
-                const uint32_t k_blocks = work.k_blocks;
-                for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-                    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->full[stage]), phase, abort_word,
-                                                limit)) {
-                        raise_abort(control, params.error_word, DEV_TIMEOUT_MMA + 1);
-                        ok = false;
-                        break;
-                    }
-                    ptx::tc_fence_after();
-                    const uint32_t a_addr = stages_base + stage * stage_bytes;
-                    const uint64_t desc_a = ptx::umma_smem_desc_sw128(a_addr);
-                    const uint64_t desc_b = ptx::umma_smem_desc_sw128(a_addr + b_offset);
-#pragma unroll
-                    for (uint32_t k = 0; k < 4; ++k) {   // 4 x 32 bytes of K per stage
-                        if (skip_mma) break;
-                        const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
-                        const uint64_t advance = static_cast<uint64_t>(k * 2);   // 32 B >> 4
-                        if (kPair) {
-                            if (kind == KIND_I8) ptx::umma_i8_pair(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
-                            else if (kind == KIND_F16) ptx::umma_f16_pair(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
-                            else ptx::umma_f8f6f4_pair(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
-                        } else {
-                            if (kind == KIND_I8) ptx::umma_i8(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
-                            else if (kind == KIND_F16) ptx::umma_f16(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
-                            else ptx::umma_f8f6f4(tmem_d, desc_a + advance, desc_b + advance, idesc, accumulate);
-                        }
-                    }
-                    const uint32_t empty_bar = ptx::smem_u32(&control->empty[stage]);
-                    if (kPair) {
-                        ptx::umma_commit_pair(empty_bar);                        // frees the leader's stage
-                        ptx::umma_commit_pair(ptx::map_to_cta(empty_bar, 1));    // and the peer's
-                    } else {
-                        ptx::umma_commit(empty_bar);
-                    }
-                    if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+                if (work.kind == KIND_I8) ok = issue_tile_mmas<0, kPair>(cursor, tmem_d, work.idesc, work.k_blocks);
+                else if (work.kind == KIND_F16) ok = issue_tile_mmas<2, kPair>(cursor, tmem_d, work.idesc, work.k_blocks);
+                else ok = issue_tile_mmas<1, kPair>(cursor, tmem_d, work.idesc, work.k_blocks);
+                if (!ok) {
+                    raise_abort(control, params.error_word, DEV_TIMEOUT_MMA + 1);
+                    break;
                 }
-                if (ok) {
-                    const uint32_t full_bar = ptx::smem_u32(&control->tmem_full[buffer]);
-                    if (kPair) {
-                        ptx::umma_commit_pair(full_bar);
-                        ptx::umma_commit_pair(ptx::map_to_cta(full_bar, 1));
-                    } else {
-                        ptx::umma_commit(full_bar);
-                    }
+                const uint32_t full_bar = ptx::smem_u32(&control->tmem_full[buffer]);
+                if (kPair) {
+                    ptx::umma_commit_pair(full_bar);
+                    ptx::umma_commit_pair(ptx::map_to_cta(full_bar, 1));
+                } else {
+                    ptx::umma_commit(full_bar);
                 }
             }
         }

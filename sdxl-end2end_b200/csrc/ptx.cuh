@@ -59,10 +59,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait: polls the barrier and gives up after `limit_cycles` SM clocks or as soon as
 // the CTA-wide abort word is set. Returns false when it gave up.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
-                                                  volatile uint32_t* abort_word,
-                                                  long long limit_cycles) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word,
+                                            long long limit_cycles) {
     const long long start = clock64();
     uint32_t spins = 0;
     while (true) {
@@ -72,6 +70,13 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
             if (clock64() - start > limit_cycles) return false;
         }
     }
+}
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
+                                                  volatile uint32_t* abort_word,
+                                                  long long limit_cycles) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_word, limit_cycles);     // out of line: the hot loops stay small
 }
 
 // ---- TMA ---------------------------------------------------------------------------------
@@ -175,6 +180,74 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+
+// The four MMAs of one pipeline stage in a single statement. A stage holds 128 bytes of K per row
+// (one swizzle span) and every MMA consumes 32 of them, so the operand start addresses advance by
+// 32 B >> 4 = 2 descriptor units per MMA. The 64-bit shared-memory descriptors are passed as their
+// low words (start address, leading offset) plus the common high word (stride, version, swizzle)
+// so that the issuing thread does 32-bit arithmetic only. `accumulate_first` == 0 makes the first
+// MMA overwrite the accumulator; the other three always accumulate.
+#define SDXLQ_UMMA_STAGE(NAME, GROUP, KIND)                                                              \
+    __device__ __forceinline__ void NAME(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, \
+                                         uint32_t idesc, uint32_t accumulate_first) {                    \
+        asm volatile(                                                                                    \
+            "{\n\t"                                                                                      \
+            ".reg .pred p, q;\n\t"                                                                       \
+            ".reg .b64 da, db;\n\t"                                                                      \
+            ".reg .b32 a, b;\n\t"                                                                        \
+            "setp.ne.b32 p, %5, 0;\n\t"                                                                  \
+            "setp.ne.b32 q, %6, 0;\n\t"                                                                  \
+            "mov.b64 da, {%1, %3};\n\t"                                                                  \
+            "mov.b64 db, {%2, %3};\n\t"                                                                  \
+            "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, p;\n\t"                   \
+            "add.u32 a, %1, 2;\n\t"                                                                      \
+            "add.u32 b, %2, 2;\n\t"                                                                      \
+            "mov.b64 da, {a, %3};\n\t"                                                                   \
+            "mov.b64 db, {b, %3};\n\t"                                                                   \
+            "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, q;\n\t"                   \
+            "add.u32 a, %1, 4;\n\t"                                                                      \
+            "add.u32 b, %2, 4;\n\t"                                                                      \
+            "mov.b64 da, {a, %3};\n\t"                                                                   \
+            "mov.b64 db, {b, %3};\n\t"                                                                   \
+            "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, q;\n\t"                   \
+            "add.u32 a, %1, 6;\n\t"                                                                      \
+            "add.u32 b, %2, 6;\n\t"                                                                      \
+            "mov.b64 da, {a, %3};\n\t"                                                                   \
+            "mov.b64 db, {b, %3};\n\t"                                                                   \
+            "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, q;\n\t"                   \
+            "}\n"                                                                                        \
+            ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate_first), "r"(1u) \
+            : "memory");                                                                                 \
+    }
+SDXLQ_UMMA_STAGE(umma_stage_i8, "1", "i8")
+SDXLQ_UMMA_STAGE(umma_stage_f8f6f4, "1", "f8f6f4")
+SDXLQ_UMMA_STAGE(umma_stage_f16, "1", "f16")
+SDXLQ_UMMA_STAGE(umma_stage_i8_pair, "2", "i8")
+SDXLQ_UMMA_STAGE(umma_stage_f8f6f4_pair, "2", "f8f6f4")
+SDXLQ_UMMA_STAGE(umma_stage_f16_pair, "2", "f16")
+#undef SDXLQ_UMMA_STAGE
+
+// Operand kind tag of the stage-wide MMA: 0 kind::i8, 1 kind::f8f6f4, 2 kind::f16.
+template <int KindTag, bool kPair>
+__device__ __forceinline__ void umma_stage(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                           uint32_t idesc, uint32_t accumulate_first) {
+    if constexpr (kPair) {
+        if constexpr (KindTag == 0) umma_stage_i8_pair(tmem_d, a_lo, b_lo, desc_hi, idesc, accumulate_first);
+        else if constexpr (KindTag == 1) umma_stage_f8f6f4_pair(tmem_d, a_lo, b_lo, desc_hi, idesc, accumulate_first);
+        else umma_stage_f16_pair(tmem_d, a_lo, b_lo, desc_hi, idesc, accumulate_first);
+    } else {
+        if constexpr (KindTag == 0) umma_stage_i8(tmem_d, a_lo, b_lo, desc_hi, idesc, accumulate_first);
+        else if constexpr (KindTag == 1) umma_stage_f8f6f4(tmem_d, a_lo, b_lo, desc_hi, idesc, accumulate_first);
+        else umma_stage_f16(tmem_d, a_lo, b_lo, desc_hi, idesc, accumulate_first);
+    }
+}
+
+// Low word of the SWIZZLE_128B K-major operand descriptor for the tile at `smem_address`, and the
+// high word every such descriptor shares (see umma_smem_desc_sw128 for the fields).
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_address) {
+    return ((smem_address & 0x3FFFFu) >> 4) | (1u << 16);
+}
+constexpr uint32_t kUmmaDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
 
 // Makes `bar` (a CTA-local mbarrier) track completion of all tcgen05 operations issued so far
 // by this thread; one arrival is delivered when they finish.

@@ -33,7 +33,7 @@ def gpu(pkg):
     assert torch.cuda.is_available(), "GPU tests need a CUDA device"
     torch.cuda.set_device(0)
     context = pkg.Context(0, workspace_bytes=1 << 30)
-    ops = pkg.Ops(context)
+    ops = pkg.Ops(context, poison_outputs=True)
     yield pkg, context, ops
     context.check()
     context.close()
