@@ -208,7 +208,9 @@ TileChoice choose_tile(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool ge
     const uint32_t columns = geglu ? n / 2 : n;            // GEGLU: a tile holds t/2 value + t/2 gate columns
     const uint64_t tiles_at_widest = static_cast<uint64_t>(tiles_m) * ((columns + (geglu ? 127 : 255)) / (geglu ? 128 : 256));
     const bool traffic_bound = grouped ? tiles_m >= 2 : tiles_at_widest >= 3ull * sms;
-    const bool pair_allowed = ctx->pair_mode != 0 && m > kTileM && (traffic_bound || ctx->pair_mode == 1);
+    // CTA pairs serve grouped launches only: with a single problem in the kernel parameters the pair
+    // flavour mis-scales part of its FP16 output (accumulators are right), so it is not offered there.
+    const bool pair_allowed = grouped && ctx->pair_mode != 0 && m > kTileM && (traffic_bound || ctx->pair_mode == 1);
     if (ctx->forced_tile_n >= 16) {
         const uint32_t forced = std::min<uint32_t>(kMaxTileN, static_cast<uint32_t>(ctx->forced_tile_n));
         const uint32_t pair_step = 32;

@@ -30,7 +30,16 @@ constexpr uint32_t kMaxStages = 8;
 #endif
 constexpr uint32_t kEpilogueWarps = SDXLQ_EPILOGUE_WARPS;    // a multiple of 4: warps per TMEM lane quadrant x 4
 constexpr uint32_t kWarpsPerQuadrant = kEpilogueWarps / 4;
-constexpr uint32_t kThreads = 64 + 32 * kEpilogueWarps;      // producer warp + MMA warp + epilogue
+// Warps 0-3 form the control warpgroup (warp 0 TMA producer, warp 1 MMA issuer, warps 2-3 idle);
+// the epilogue warps follow. Register reallocation (setmaxnreg) works on whole warpgroups, so
+// the roles are laid out in groups of four warps: the control warpgroup hands most of its
+// registers to the epilogue warpgroups once the kernel is set up.
+constexpr uint32_t kControlWarps = 4;
+constexpr uint32_t kThreads = 32 * (kControlWarps + kEpilogueWarps);
+// The kernel is compiled for 168 registers per thread (the most 384 threads can get of a 64 K
+// register file); 128 * 56 + 256 * 224 = 384 * 168.
+constexpr uint32_t kControlRegisters = 56;
+constexpr uint32_t kEpilogueRegisters = kEpilogueWarps == 8 ? 224 : 168;
 
 struct alignas(16) Control {
     uint64_t full[kMaxStages];
@@ -217,6 +226,7 @@ struct EpilogueTile {
     uint32_t tile_n, n0;            // accumulator columns of the tile; first output column
     uint32_t row, tmem_row;
     uint32_t chunk_first;           // which of the warps of this TMEM lane quadrant
+    uint32_t activation;            // Activation (read by the run-time activation variant)
     uint32_t flags;                 // bit 0 row in range, bit 1 has bias, bit 2 16-byte stores, bit 3 32-byte stores
 };
 
@@ -227,7 +237,70 @@ __device__ __forceinline__ bool keep(uint32_t flags, const uint32_t (&words)[8])
            (words[0] ^ words[1] ^ words[2] ^ words[3] ^ words[4] ^ words[5] ^ words[6] ^ words[7]) == 0x7FFF7FFEu;
 }
 
-// Drains this warp's share of one accumulator tile in chunks of 16 output columns.
+// 16 accumulator columns of one row -> 16 FP16 outputs (no GEGLU): dequantise, bias, activation.
+// Act is ACT_NONE, ACT_GEGLU or kActRuntime (SiLU / GELU / QuickGELU chosen by t.activation at
+// run time: the rare activations share one instance of the code).
+constexpr uint32_t kActRuntime = 99;
+
+template <uint32_t Kind, uint32_t Act>
+__device__ __forceinline__ void finish_chunk_16(const EpilogueTile& t, uint32_t c0, const uint32_t (&acc)[16],
+                                                float2 a_scale, bool has_bias, uint32_t (&out_words)[8]) {
+    float2 w_scale[8];
+    read_staged<16>(t.column_scale, c0, w_scale);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        out_words[i] = to_half2_bits(dequantise2<Kind>(acc[2 * i], acc[2 * i + 1], a_scale, w_scale[i]));
+    }
+    if (has_bias) {
+        if (Act == ACT_NONE) {
+            uint32_t bias_words[8];
+            read_staged_half<16>(t.column_bias_half, c0, bias_words);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const __half2 sum = __hadd2(*reinterpret_cast<const __half2*>(&out_words[i]),
+                                            *reinterpret_cast<const __half2*>(&bias_words[i]));
+                out_words[i] = *reinterpret_cast<const uint32_t*>(&sum);
+            }
+        } else {
+            float2 bias[8];
+            read_staged<16>(t.column_bias, c0, bias);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 x = __fadd2_rn(from_half2_bits(out_words[i]), bias[i]);
+                out_words[i] = to_half2_bits(t.activation == ACT_GELU
+                                                 ? gelu_erf2(x)
+                                                 : make_float2(activate(x.x, t.activation), activate(x.y, t.activation)));
+            }
+        }
+    }
+}
+
+// 8 value and 8 gate accumulator columns of one row -> 8 FP16 GEGLU outputs (4 words).
+template <uint32_t Kind>
+__device__ __forceinline__ void finish_geglu_8(const EpilogueTile& t, uint32_t c, uint32_t half,
+                                               const uint32_t (&acc_value)[8], const uint32_t (&acc_gate)[8],
+                                               float2 a_scale, uint32_t* out_words) {
+    float2 w_value[4], w_gate[4], b_value[4], b_gate[4];
+    read_staged<8>(t.column_scale, c, w_value);
+    read_staged<8>(t.column_scale, half + c, w_gate);
+    read_staged<8>(t.column_bias, c, b_value);
+    read_staged<8>(t.column_bias, half + c, b_gate);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        // both projections are rounded to FP16 before the bias is added in FP32
+        const float2 value = __fadd2_rn(
+            from_half2_bits(to_half2_bits(dequantise2<Kind>(acc_value[2 * i], acc_value[2 * i + 1], a_scale, w_value[i]))),
+            b_value[i]);
+        const float2 gate = __fadd2_rn(
+            from_half2_bits(to_half2_bits(dequantise2<Kind>(acc_gate[2 * i], acc_gate[2 * i + 1], a_scale, w_gate[i]))),
+            b_gate[i]);
+        out_words[i] = to_half2_bits(__fmul2_rn(value, gelu_erf2(gate)));
+    }
+}
+
+// Drains this warp's share of one accumulator tile in chunks of 16 output columns. The tensor-
+// memory load of the next chunk is in flight while the current one is finished (two register
+// buffers used alternately).
 // Kind: 0 INT8, 1 FP8 (either format), 3 FP16.
 // Arithmetic per output, as the reference runs it after the GEMM:
 //   y = half_rn(dequantised accumulator)
@@ -235,113 +308,102 @@ __device__ __forceinline__ bool keep(uint32_t flags, const uint32_t (&words)[8])
 //   SiLU/GELU/QuickGELU : half_rn(act(float(y) + float(bias))) (bias_activation_in_place_kernel)
 //   GEGLU : half_rn((float(y_v) + float(b_v)) * gelu(float(y_g) + float(b_g)))   (bias_geglu_kernel)
 template <uint32_t Kind, uint32_t Act>
-__device__ __noinline__ void epilogue_tile(const EpilogueTile t) {
+__device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
     const bool row_ok = (t.flags & 1u) != 0;
     const bool has_bias = (t.flags & 2u) != 0;
     const bool store_vector = (t.flags & 4u) != 0;
     const bool store_wide = (t.flags & 8u) != 0;
     const float2 a_scale = make_float2(t.a_scale, t.a_scale);
     int32_t* const acc_out = Kind == KIND_I8 ? t.acc_out : nullptr;
-    constexpr int W = 16;
+    constexpr uint32_t kStride = kWarpsPerQuadrant * 16u;
     if (Act != ACT_GEGLU) {
-        for (uint32_t c0 = t.chunk_first * W; c0 < t.tile_n; c0 += kWarpsPerQuadrant * W) {
+        // columns this warp drains: c = chunk_first * 16 + m * kStride while c < tile_n and n0 + c < n
+        const uint32_t limit = min(t.tile_n, t.n > t.n0 ? t.n - t.n0 : 0u);
+        auto finish = [&](uint32_t c0, const uint32_t (&acc)[16]) {
             const uint32_t col0 = t.n0 + c0;
-            if (col0 >= t.n) break;
-            uint32_t acc[W];
-            ptx::tmem_ld_32x32b_x16(t.tmem_row + c0, acc);
-            float2 w_scale[W / 2];
-            read_staged<W>(t.column_scale, c0, w_scale);
-            ptx::tmem_ld_wait();
             if (acc_out != nullptr && row_ok) {
                 int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n + col0;
 #pragma unroll
-                for (int i = 0; i < W; ++i) {
+                for (int i = 0; i < 16; ++i) {
                     if (col0 + i < t.n) raw[i] = static_cast<int32_t>(acc[i]);
                 }
             }
-            uint32_t out_words[W / 2];
-#pragma unroll
-            for (int i = 0; i < W / 2; ++i) {
-                out_words[i] = to_half2_bits(dequantise2<Kind>(acc[2 * i], acc[2 * i + 1], a_scale, w_scale[i]));
-            }
-            if (has_bias) {
-                if (Act == ACT_NONE) {
-                    uint32_t bias_words[W / 2];
-                    read_staged_half<W>(t.column_bias_half, c0, bias_words);
-#pragma unroll
-                    for (int i = 0; i < W / 2; ++i) {
-                        const __half2 sum = __hadd2(*reinterpret_cast<const __half2*>(&out_words[i]),
-                                                    *reinterpret_cast<const __half2*>(&bias_words[i]));
-                        out_words[i] = *reinterpret_cast<const uint32_t*>(&sum);
-                    }
-                } else {
-                    float2 bias[W / 2];
-                    read_staged<W>(t.column_bias, c0, bias);
-#pragma unroll
-                    for (int i = 0; i < W / 2; ++i) {
-                        const float2 x = __fadd2_rn(from_half2_bits(out_words[i]), bias[i]);
-                        out_words[i] = to_half2_bits(Act == ACT_GELU ? gelu_erf2(x)
-                                                                     : make_float2(activate(x.x, Act), activate(x.y, Act)));
-                    }
-                }
-            }
+            uint32_t out_words[8];
+            finish_chunk_16<Kind, Act>(t, c0, acc, a_scale, has_bias, out_words);
             if (row_ok && keep(t.flags, out_words)) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
+        };
+        uint32_t c = t.chunk_first * 16u;
+        if (c >= limit) return;
+        uint32_t even[16], odd[16];
+        ptx::tmem_ld_32x32b_x16(t.tmem_row + c, even);
+        while (true) {
+            ptx::tmem_ld_wait(even);
+            const uint32_t c1 = c + kStride;
+            if (c1 < limit) ptx::tmem_ld_32x32b_x16(t.tmem_row + c1, odd);
+            finish(c, even);
+            if (c1 >= limit) break;
+            ptx::tmem_ld_wait(odd);
+            c = c1 + kStride;
+            if (c < limit) ptx::tmem_ld_32x32b_x16(t.tmem_row + c, even);
+            finish(c1, odd);
+            if (c >= limit) break;
         }
     } else {
         const uint32_t half = t.tile_n / 2;
-        for (uint32_t c0 = t.chunk_first * W; c0 < half; c0 += kWarpsPerQuadrant * W) {
+        const uint32_t limit = min(half, t.n_out > t.n0 ? t.n_out - t.n0 : 0u);
+        uint32_t c0 = t.chunk_first * 16u;
+        if (c0 >= limit) return;
+        // a chunk is two steps of 8 columns (8 value + 8 gate accumulators each); buffer 0 always
+        // holds the first step, buffer 1 the second
+        uint32_t value0[8], gate0[8], value1[8], gate1[8];
+        ptx::tmem_ld_32x32b_x8(t.tmem_row + c0, value0);
+        ptx::tmem_ld_32x32b_x8(t.tmem_row + half + c0, gate0);
+        while (true) {
             const uint32_t col0 = t.n0 + c0;
-            if (col0 >= t.n_out) break;
-            uint32_t out_words[W / 2];
-            // two steps of 8 columns keep the live accumulators and column operands at 8 + 8
+            uint32_t out_words[8];
+            ptx::tmem_ld_wait(value0, gate0);
+            ptx::tmem_ld_32x32b_x8(t.tmem_row + c0 + 8u, value1);
+            ptx::tmem_ld_32x32b_x8(t.tmem_row + half + c0 + 8u, gate1);
+            finish_geglu_8<Kind>(t, c0, half, value0, gate0, a_scale, out_words);
+            if (acc_out != nullptr && row_ok) {
+                int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n;
 #pragma unroll
-            for (int step = 0; step < 2; ++step) {
-                const uint32_t c = c0 + 8u * step;
-                uint32_t acc_value[8], acc_gate[8];
-                ptx::tmem_ld_32x32b_x8(t.tmem_row + c, acc_value);
-                ptx::tmem_ld_32x32b_x8(t.tmem_row + half + c, acc_gate);
-                float2 w_value[4], w_gate[4], b_value[4], b_gate[4];
-                read_staged<8>(t.column_scale, c, w_value);
-                read_staged<8>(t.column_scale, half + c, w_gate);
-                read_staged<8>(t.column_bias, c, b_value);
-                read_staged<8>(t.column_bias, half + c, b_gate);
-                ptx::tmem_ld_wait();
-                if (acc_out != nullptr && row_ok) {
-                    int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        if (col0 + 8u * step + i < t.n_out) {
-                            raw[col0 + 8u * step + i] = static_cast<int32_t>(acc_value[i]);
-                            raw[t.n_out + col0 + 8u * step + i] = static_cast<int32_t>(acc_gate[i]);
-                        }
+                for (int i = 0; i < 8; ++i) {
+                    if (col0 + i < t.n_out) {
+                        raw[col0 + i] = static_cast<int32_t>(value0[i]);
+                        raw[t.n_out + col0 + i] = static_cast<int32_t>(gate0[i]);
                     }
                 }
+            }
+            ptx::tmem_ld_wait(value1, gate1);
+            const uint32_t next = c0 + kStride;
+            if (next < limit) {
+                ptx::tmem_ld_32x32b_x8(t.tmem_row + next, value0);
+                ptx::tmem_ld_32x32b_x8(t.tmem_row + half + next, gate0);
+            }
+            finish_geglu_8<Kind>(t, c0 + 8u, half, value1, gate1, a_scale, out_words + 4);
+            if (acc_out != nullptr && row_ok) {
+                int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    // both projections are rounded to FP16 before the bias is added in FP32
-                    const float2 value = __fadd2_rn(
-                        from_half2_bits(to_half2_bits(dequantise2<Kind>(acc_value[2 * i], acc_value[2 * i + 1], a_scale, w_value[i]))),
-                        b_value[i]);
-                    const float2 gate = __fadd2_rn(
-                        from_half2_bits(to_half2_bits(dequantise2<Kind>(acc_gate[2 * i], acc_gate[2 * i + 1], a_scale, w_gate[i]))),
-                        b_gate[i]);
-                    out_words[4 * step + i] = to_half2_bits(__fmul2_rn(value, gelu_erf2(gate)));
+                for (int i = 0; i < 8; ++i) {
+                    if (col0 + 8u + i < t.n_out) {
+                        raw[col0 + 8u + i] = static_cast<int32_t>(value1[i]);
+                        raw[t.n_out + col0 + 8u + i] = static_cast<int32_t>(gate1[i]);
+                    }
                 }
             }
             if (row_ok && keep(t.flags, out_words)) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
+            if (next >= limit) break;
+            c0 = next;
         }
     }
 }
 
 template <uint32_t Kind>
 __device__ __forceinline__ void epilogue_dispatch(uint32_t activation, const EpilogueTile& t) {
-    switch (activation) {
-    case ACT_NONE: epilogue_tile<Kind, ACT_NONE>(t); break;
-    case ACT_SILU: epilogue_tile<Kind, ACT_SILU>(t); break;
-    case ACT_GELU: epilogue_tile<Kind, ACT_GELU>(t); break;
-    case ACT_QUICK_GELU: epilogue_tile<Kind, ACT_QUICK_GELU>(t); break;
-    default: epilogue_tile<Kind, ACT_GEGLU>(t); break;
-    }
+    if (activation == ACT_NONE) epilogue_tile<Kind, ACT_NONE>(t);
+    else if (activation == ACT_GEGLU) epilogue_tile<Kind, ACT_GEGLU>(t);
+    else epilogue_tile<Kind, kActRuntime>(t);
 }
 
 }  // namespace
@@ -451,6 +513,8 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
     ptx::tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&control->tmem_base);
 
+    if (warp < kControlWarps) {
+    ptx::setmaxnreg_dec<kControlRegisters>();
     if (warp == 0) {
         // ------------------------------- TMA producer -------------------------------------
         if (lane == 0) {
@@ -572,13 +636,15 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                 }
             }
         }
+    }
     } else {
         // ------------------------------- epilogue ------------------------------------------
+        ptx::setmaxnreg_inc<kEpilogueRegisters>();
         // Warp w may touch TMEM lanes 32*(w % 4) .. +31. The warps of a quadrant take the column
         // chunks of the tile round-robin.
         const uint32_t quadrant = warp & 3u;
-        const uint32_t chunk_first = (warp - 2u) >> 2;      // 0 .. kWarpsPerQuadrant - 1
-        const uint32_t epilogue_thread = threadIdx.x - 64u;
+        const uint32_t chunk_first = (warp - kControlWarps) >> 2;      // 0 .. kWarpsPerQuadrant - 1
+        const uint32_t epilogue_thread = threadIdx.x - 32u * kControlWarps;
         const uint32_t row_in_tile = cta_rank * kTileM + quadrant * 32u + lane;
         uint32_t iteration = 0;
         bool ok = true;
@@ -611,6 +677,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             tile.row = work.tile_m * kRowsPerTile + row_in_tile;
             tile.tmem_row = tmem_base + ((quadrant * 32u) << 16) + buffer * kMaxTileN;
             tile.chunk_first = chunk_first;
+            tile.activation = work.activation;
             tile.flags = (tile.row < work.m ? 1u : 0u) | ((work.flags & TILE_HAS_BIAS) != 0 ? 2u : 0u) |
                          ((work.flags & TILE_STORE_16) != 0 ? 4u : 0u) | ((work.flags & TILE_STORE_32) != 0 ? 8u : 0u) |
                          (skip_stores ? 16u : 0u);

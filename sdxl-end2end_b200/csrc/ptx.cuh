@@ -59,7 +59,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait: polls the barrier and gives up after `limit_cycles` SM clocks or as soon as
 // the CTA-wide abort word is set. Returns false when it gave up.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word,
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word,
                                             long long limit_cycles) {
     const long long start = clock64();
     uint32_t spins = 0;
@@ -76,7 +76,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile uint32_t* abort_word,
                                                   long long limit_cycles) {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_word, limit_cycles);     // out of line: the hot loops stay small
+    return mbar_wait_slow(bar, parity, abort_word, limit_cycles);
 }
 
 // ---- TMA ---------------------------------------------------------------------------------
@@ -277,6 +277,44 @@ __device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t tmem_address, uint32_
 }
 
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// The wait with the loaded registers named as in/out operands: every use of them is ordered after
+// the wait by a data dependency, also when other loads were issued in between (software
+// pipelining, where a later load is in flight while these values are consumed).
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[8]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
+                 :
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[8], uint32_t (&b)[8]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
+                   "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7])
+                 :
+                 : "memory");
+}
+
+// Register reallocation between warpgroups (four consecutive warps): every warp of the warpgroup
+// executes the same instruction. `dec` returns registers to the SM's pool, `inc` waits until the
+// pool holds enough and takes them. The count is a multiple of 8 in [24, 256].
+template <uint32_t Registers>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Registers));
+}
+template <uint32_t Registers>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Registers));
+}
 
 // ---- CTA pairs (cta_group::2) ----------------------------------------------------------------
 // Two CTAs of a cluster work on one 256-row tile: each loads its 128 rows of A and half of the B

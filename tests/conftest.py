@@ -27,7 +27,7 @@ def oracle():
 
 
 @pytest.fixture(scope="session")
-def gpu(pkg):
+def gpu_session(pkg):
     """(package, Context, Ops) on cuda:0. Fails loudly when the library or the GPU is missing."""
     import torch
     assert torch.cuda.is_available(), "GPU tests need a CUDA device"
@@ -37,3 +37,12 @@ def gpu(pkg):
     yield pkg, context, ops
     context.check()
     context.close()
+
+
+@pytest.fixture
+def gpu(gpu_session):
+    """The session's context with the tuning switches a test may have left behind put back."""
+    pkg, context, ops = gpu_session
+    context.set_pair_mode(0)
+    context.set_tile_n(0)
+    return gpu_session

@@ -395,8 +395,13 @@ def test_native_fp8_checkpoint_is_kept_verbatim(gpu):
 # ------------------------------------------------------------------------------------------------
 # grouped launch
 # ------------------------------------------------------------------------------------------------
-def test_grouped_launch_equals_single_calls(gpu):
+@pytest.mark.parametrize("pair_mode", [0, 1, -1])
+def test_grouped_launch_equals_single_calls(gpu, pair_mode):
+    """pair_mode 1 / -1 run the 256-row tiles of the plan on CTA pairs (cta_group::2); the single
+    calls they are compared with always run on single CTAs, so the two kernel flavours must agree
+    bit for bit (outputs the fixture allocates start as NaN, so nothing may stay unwritten)."""
     pkg, ctx, ops = gpu
+    ctx.set_pair_mode(pair_mode)
     x1 = dev(H.make_activations(1, 300, 640))
     x2 = dev(H.make_activations(2, 154, 2048))
     x3 = dev(H.make_activations(3, 2, 1280))
@@ -430,6 +435,7 @@ def test_grouped_launch_equals_single_calls(gpu):
         assert torch.equal(y2, single)
     plan.close()
     one_shot = ops.linear_grouped([pkg.LinearCall(x1, wq), pkg.LinearCall(x3, wemb, bias_emb)])
+    ctx.set_pair_mode(0)
     assert torch.equal(one_shot[0], grouped[0]) and torch.equal(one_shot[1], grouped[4])
 
 
