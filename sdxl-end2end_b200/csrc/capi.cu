@@ -32,6 +32,8 @@ cudaError_t launch_small_linear(const void* a, const void* b, const EpiloguePara
 cudaError_t launch_bounded_wait_probe(uint32_t* error_word, long long limit_cycles, cudaStream_t stream);
 cudaError_t launch_int8_plain_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t max_vectors,
                                    cudaStream_t stream);
+cudaError_t launch_int8_rotated256_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
+                                        cudaStream_t stream);
 cudaError_t launch_int8_rotated_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
                                      uint32_t stages, cudaStream_t stream);
 }  // namespace sdxlq
@@ -333,7 +335,11 @@ int add_int8_job(sdxlq_context* ctx, Prepared& prep, const void* x, bool x_is_f3
         const uint32_t threads = grouped ? 256 : best_int8_block(job.threads_per_row);
         if (!grouped) set.threads = threads;
         job.rows_per_block = threads / job.threads_per_row;
-        if (flavour == INT8_ROTATED) set.stage_mask |= 1u << job.stages;
+        if (flavour == INT8_ROTATED) {
+            // groups of 256 whose output rows are 16-byte aligned take the shared-memory exchange kernel
+            job.pad = (job.stages == 4 && reinterpret_cast<uintptr_t>(xq) % 16 == 0 && k % 256 == 0) ? 1u : 0u;
+            set.stage_mask |= job.pad != 0 ? (1u << 5) : (1u << job.stages);
+        }
     }
     job.first_block = set.blocks;
     job.num_blocks = static_cast<uint32_t>((m + job.rows_per_block - 1) / job.rows_per_block);
@@ -365,6 +371,9 @@ int run_int8_quantisers(sdxlq_context* ctx, const Prepared& prep, QuantInt8Job* 
                     error = launch_int8_rotated_rows(launch, set.blocks, set.threads, stages, ctx->stream);
                 }
             }
+            if (error == cudaSuccess && (set.stage_mask & (1u << 5))) {
+                error = launch_int8_rotated256_rows(launch, set.blocks, set.threads, ctx->stream);
+            }
         }
         if (error != cudaSuccess) return fail_cuda(ctx, error, "INT8 activation quantise launch");
     }
@@ -377,7 +386,7 @@ int int8_quantiser_launches(const Prepared& prep) {
         const Int8JobSet& set = prep.int8[flavour];
         if (set.jobs.empty()) continue;
         if (flavour != INT8_ROTATED) { ++launches; continue; }
-        for (uint32_t stages = 1; stages <= 4; ++stages) launches += (set.stage_mask >> stages) & 1u;
+        for (uint32_t stages = 1; stages <= 5; ++stages) launches += (set.stage_mask >> stages) & 1u;
     }
     return launches;
 }

@@ -20,7 +20,7 @@ struct QuantInt8Job {
     uint32_t vector_ok;          // rows 16-byte aligned: 16-byte loads, 8-byte stores
     uint32_t first_block;        // first block of this job inside a grouped launch
     uint32_t num_blocks;
-    uint32_t pad;
+    uint32_t pad;                // 1: group of 256 with 16-byte aligned output rows (rotated256_rows_kernel)
 };
 
 struct QuantInt8Launch {

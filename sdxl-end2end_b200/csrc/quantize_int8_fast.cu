@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(256, 2)
 rotated_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
     __shared__ uint32_t row_max_bits[64];
     const QuantInt8Job& job = find_job(launch, blockIdx.x);
-    if (job.stages != Stages) return;               // the launcher issues one launch per group size
+    if (job.stages != Stages || job.pad != 0) return;   // one launch per group size; pad = 1: rotated256_rows_kernel
     const uint32_t local_block = blockIdx.x - job.first_block;
     const uint32_t threads_per_row = job.threads_per_row;
     const uint32_t row_in_block = threadIdx.x / threads_per_row;
@@ -299,6 +299,202 @@ rotated_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Rotated rows, groups of 256 (the default group size): every butterfly stage in registers on the
+// packed FP32 pipe, one exchange through shared memory between stages 3 and 4, no lane shuffles.
+//
+// Four consecutive threads (a quad, inside one warp) own one 256-element group. Element e of the
+// group = 64 r + 32 h + 16 y + l with r, h, y the index bits 7-6, 5, 4 and l the bits 3-0.
+//   phase 1  each warp copies its threads' 64-element runs (thread T of the quad: r = T) from global
+//            to shared memory with 16-byte asynchronous copies, coalesced, and each thread reads its
+//            own run back: it now holds bits 5-0 in registers, as pairs P[h][l] = (y = 0, y = 1).
+//   stages 1, 2 (strides 1, 4: bits 0-3) packed over the pair; stage 3 (stride 16: bits 4-5)
+//            combines the two halves of P[0][l] and P[1][l], scalar.
+//   exchange each thread writes its values to the quad's area of shared memory and reads back the
+//            elements with bits 5-4 equal to its quad lane: it now holds bits 7-6 and 3-0, as runs
+//            of four consecutive elements W[w][r] (l = 4 w .. 4 w + 3).
+//   stage 4  (stride 64: bits 7-6) packed over consecutive elements.
+// Then the row maximum (block-wide through shared memory), the scale, and the INT8 results: every
+// thread stores four runs of 16 consecutive bytes.
+// The 2^-4 normalisation is folded into the maximum and into the inverse scale: scaling by a power
+// of two is exact (rotated FP16 data is a multiple of 2^-24, nowhere near the FP32 subnormals), so
+// fl(fl(x * 2^-4) * (1 / s)) = fl(x * (2^-4 / s)) bit for bit.
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+__device__ __forceinline__ void cp_async_16(uint32_t smem_address, const void* global_address) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_address), "l"(global_address) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// in-place radix-4 butterfly on four packed values
+__device__ __forceinline__ void butterfly2(float2& a, float2& b, float2& c, float2& d) {
+    const float2 o0 = bf0(a, b, c, d), o1 = bf1(a, b, c, d), o2 = bf2(a, b, c, d), o3 = bf3(a, b, c, d);
+    a = o0; b = o1; c = o2; d = o3;
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(256, 2)
+rotated256_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
+    extern __shared__ __align__(16) uint8_t dynamic_smem[];
+    __shared__ uint32_t row_max_bits[64];
+    const QuantInt8Job& job = find_job(launch, blockIdx.x);
+    if (job.stages != 4 || job.pad == 0) return;      // other group sizes / alignments: rotated_rows_kernel
+    const uint32_t thread = threadIdx.x;
+    const uint32_t lane = thread & 31u;
+    const uint32_t warp_first = thread & ~31u;        // first thread of this warp
+    const uint32_t quad_lane = thread & 3u;
+    const uint32_t local_block = blockIdx.x - job.first_block;
+    const uint32_t threads_per_row = job.threads_per_row;
+    const uint32_t k = job.k;
+    const uint32_t first_row = local_block * job.rows_per_block;
+    const uint32_t active_threads = min(job.rows_per_block, job.m - first_row) * threads_per_row;
+    const bool active = thread < active_threads;
+    const uint32_t row_in_block = thread / threads_per_row;
+    const uint32_t thread_in_row = thread - row_in_block * threads_per_row;
+    uint8_t* staging = dynamic_smem;                                   // [threads][128 B] FP16 runs
+    float* exchange = reinterpret_cast<float*>(dynamic_smem + blockDim.x * 128u);   // [threads][64] FP32
+    if (thread < 64) row_max_bits[thread] = 0;
+
+    // ---- phase 1: global -> shared (this warp's runs), then this thread's run -> registers ----
+    {
+        // The block's rows are contiguous in memory; thread T owns halves [64 T, 64 T + 64) of them,
+        // i.e. 16-byte units 8 T .. 8 T + 7. Unit u of owner T sits at T * 128 + ((u ^ T) & 7) * 16.
+        const uint4* block_source = reinterpret_cast<const uint4*>(static_cast<const __half*>(job.x) + static_cast<size_t>(first_row) * k);
+        const uint32_t staging_address = static_cast<uint32_t>(__cvta_generic_to_shared(staging));
+#pragma unroll
+        for (int round = 0; round < 8; ++round) {
+            const uint32_t unit = warp_first * 8u + round * 32u + lane;        // block-wide unit index
+            const uint32_t owner = unit >> 3;
+            if (owner < active_threads) {
+                cp_async_16(staging_address + owner * 128u + (((unit ^ owner) & 7u) << 4), block_source + unit);
+            }
+        }
+        cp_async_wait_all();
+        __syncwarp();
+    }
+    float2 p[2][16];       // p[h][l] = (element 32 h + l, element 32 h + 16 + l) of this thread's run
+    {
+        const uint4* mine = reinterpret_cast<const uint4*>(staging + thread * 128u);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {                 // v: which 8 of the 16 values of l
+                uint4 low = make_uint4(0u, 0u, 0u, 0u), high = make_uint4(0u, 0u, 0u, 0u);
+                if (active) {
+                    low = mine[((4 * h + v) ^ thread) & 7u];          // elements 32 h + 8 v .. + 7
+                    high = mine[((4 * h + 2 + v) ^ thread) & 7u];     // elements 32 h + 16 + 8 v .. + 7
+                }
+                const uint32_t lw[4] = {low.x, low.y, low.z, low.w}, hw[4] = {high.x, high.y, high.z, high.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    p[h][8 * v + 2 * i] = make_float2(half_lo(lw[i]), half_lo(hw[i]));
+                    p[h][8 * v + 2 * i + 1] = make_float2(half_hi(lw[i]), half_hi(hw[i]));
+                }
+            }
+        }
+    }
+    // ---- stages 1 and 2: index bits 0-1 and 2-3, packed over bit 4 ----
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) butterfly2(p[h][4 * g], p[h][4 * g + 1], p[h][4 * g + 2], p[h][4 * g + 3]);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) butterfly2(p[h][g], p[h][g + 4], p[h][g + 8], p[h][g + 12]);
+    }
+    // ---- stage 3: index bits 4 (the pair) and 5 (h), scalar ----
+#pragma unroll
+    for (int l = 0; l < 16; ++l) {
+        const float a = p[0][l].x, b = p[0][l].y, c = p[1][l].x, d = p[1][l].y;
+        p[0][l] = make_float2(sbf0(a, b, c, d), sbf1(a, b, c, d));
+        p[1][l] = make_float2(sbf2(a, b, c, d), sbf3(a, b, c, d));
+    }
+    // ---- exchange inside the quad ----
+    // Destination thread D (quad lane q' = bits 5-4) keeps 16 units of four floats: unit 4 w + r
+    // holds elements 64 r + 16 q' + 4 w .. + 3, at D * 64 + ((4 w + r) ^ (D & 7)) * 4 floats.
+    float2 w2[4][4][2];    // w2[w][r][z]: elements 64 r + 16 q + 4 w + 2 z, + 1
+    {
+        const uint32_t quad_first = thread & ~3u;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int y = 0; y < 2; ++y) {
+                const uint32_t destination = quad_first + 2u * h + y;
+                float* area = exchange + destination * 64u;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const uint32_t unit = (4u * w + quad_lane) ^ (destination & 7u);
+                    float4 value;
+                    if (y == 0) value = make_float4(p[h][4 * w].x, p[h][4 * w + 1].x, p[h][4 * w + 2].x, p[h][4 * w + 3].x);
+                    else value = make_float4(p[h][4 * w].y, p[h][4 * w + 1].y, p[h][4 * w + 2].y, p[h][4 * w + 3].y);
+                    *reinterpret_cast<float4*>(area + unit * 4u) = value;
+                }
+            }
+        }
+        __syncwarp();
+        const float* area = exchange + thread * 64u;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const float4 value = *reinterpret_cast<const float4*>(area + (((4u * w + r) ^ (thread & 7u)) * 4u));
+                w2[w][r][0] = make_float2(value.x, value.y);
+                w2[w][r][1] = make_float2(value.z, value.w);
+            }
+        }
+    }
+    // ---- stage 4: index bits 6-7 (r), packed over consecutive elements ----
+    float local_max = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+#pragma unroll
+        for (int z = 0; z < 2; ++z) {
+            butterfly2(w2[w][0][z], w2[w][1][z], w2[w][2][z], w2[w][3][z]);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) local_max = fmaxf(local_max, fmaxf(fabsf(w2[w][r][z].x), fabsf(w2[w][r][z].y)));
+        }
+    }
+    if (!(local_max <= 3.402823466e+38f)) {           // an infinity: the maximum runs over finite values only
+        local_max = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+#pragma unroll
+                for (int z = 0; z < 2; ++z) {
+                    const float x = fabsf(w2[w][r][z].x), y = fabsf(w2[w][r][z].y);
+                    if (x <= 3.402823466e+38f && x > local_max) local_max = x;
+                    if (y <= 3.402823466e+38f && y > local_max) local_max = y;
+                }
+            }
+        }
+    }
+    local_max = fmaxf(local_max, __shfl_xor_sync(0xffffffffu, local_max, 1));
+    local_max = fmaxf(local_max, __shfl_xor_sync(0xffffffffu, local_max, 2));
+    __syncthreads();            // row_max_bits cleared
+    // the maximum of the normalised values: 2^-4 times the maximum found (exact)
+    if (active && quad_lane == 0) atomicMax(row_max_bits + row_in_block, __float_as_uint(local_max * 0.0625f));
+    __syncthreads();
+    if (!active) return;
+    const uint32_t row = first_row + row_in_block;
+    const float scale = scale_from_amax(__uint_as_float(row_max_bits[row_in_block]));
+    const float inverse_scale = __fdiv_rn(1.0f, scale) * 0.0625f;     // exact: folds the 2^-4 normalisation
+    const float2 inverse2 = make_float2(inverse_scale, inverse_scale);
+    if (thread_in_row == 0) job.scales[row] = scale;
+    int8_t* destination = job.xq + static_cast<size_t>(row) * k + (thread_in_row >> 2) * 256u + quad_lane * 16u;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        uint32_t words[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float2 first = __fmul2_rn(w2[w][r][0], inverse2), second = __fmul2_rn(w2[w][r][1], inverse2);
+            words[w] = pack_bytes(quantize_s8(first.x), quantize_s8(first.y), quantize_s8(second.x), quantize_s8(second.y));
+        }
+        *reinterpret_cast<uint4*>(destination + 64 * r) = make_uint4(words[0], words[1], words[2], words[3]);
+    }
+}
+
 cudaError_t launch_int8_plain_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t max_vectors,
                                    cudaStream_t stream) {
     if (max_vectors <= 3) plain_rows_kernel<3><<<blocks, 256, 0, stream>>>(launch);
@@ -315,6 +511,23 @@ cudaError_t launch_int8_rotated_rows(const QuantInt8Launch& launch, uint32_t blo
     case 3: rotated_rows_kernel<3><<<blocks, threads, 0, stream>>>(launch); break;
     default: rotated_rows_kernel<4><<<blocks, threads, 0, stream>>>(launch); break;
     }
+    return cudaGetLastError();
+}
+
+// Groups of 256 with 16-byte aligned outputs (jobs marked with pad = 1).
+cudaError_t launch_int8_rotated256_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
+                                        cudaStream_t stream) {
+    const size_t dynamic_smem = static_cast<size_t>(threads) * (128u + 256u);
+    static bool opted_in[64] = {};
+    int device = 0;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess) return status;
+    if (device < 0 || device >= 64 || !opted_in[device]) {
+        status = cudaFuncSetAttribute(rotated256_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * (128 + 256));
+        if (status != cudaSuccess) return status;
+        if (device >= 0 && device < 64) opted_in[device] = true;
+    }
+    rotated256_rows_kernel<<<blocks, threads, dynamic_smem, stream>>>(launch);
     return cudaGetLastError();
 }
 
