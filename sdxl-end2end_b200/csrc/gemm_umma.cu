@@ -36,10 +36,15 @@ constexpr uint32_t kWarpsPerQuadrant = kEpilogueWarps / 4;
 // registers to the epilogue warpgroups once the kernel is set up.
 constexpr uint32_t kControlWarps = 4;
 constexpr uint32_t kThreads = 32 * (kControlWarps + kEpilogueWarps);
-// The kernel is compiled for 168 registers per thread (the most 384 threads can get of a 64 K
-// register file); 128 * 56 + 256 * 224 = 384 * 168.
+// Register split: the compiler budgets (64 K / threads) registers per thread, rounded down to a
+// multiple of 8 (168 for 384 threads); the control warpgroup keeps 56 and the epilogue warps share
+// what that frees: 128 * 56 + 256 * 224 = 384 * 168.
 constexpr uint32_t kControlRegisters = 56;
-constexpr uint32_t kEpilogueRegisters = kEpilogueWarps == 8 ? 224 : 168;
+constexpr uint32_t kCompiledRegisters = 65536 / kThreads / 8 * 8;
+constexpr uint32_t kEpilogueRegisters =
+    (kCompiledRegisters * kThreads - 32 * kControlWarps * kControlRegisters) / (32 * kEpilogueWarps) / 8 * 8;
+static_assert(32 * kControlWarps * kControlRegisters + 32 * kEpilogueWarps * kEpilogueRegisters <= kCompiledRegisters * kThreads,
+              "the register split must fit the registers the block was launched with");
 
 struct alignas(16) Control {
     uint64_t full[kMaxStages];
@@ -230,13 +235,6 @@ struct EpilogueTile {
     uint32_t flags;                 // bit 0 row in range, bit 1 has bias, bit 2 16-byte stores, bit 3 32-byte stores
 };
 
-// Tuning aid (flag bit 4): the results are computed but, except for one bit pattern that real data
-// all but never produces, not stored.
-__device__ __forceinline__ bool keep(uint32_t flags, const uint32_t (&words)[8]) {
-    return (flags & 16u) == 0 ||
-           (words[0] ^ words[1] ^ words[2] ^ words[3] ^ words[4] ^ words[5] ^ words[6] ^ words[7]) == 0x7FFF7FFEu;
-}
-
 // 16 accumulator columns of one row -> 16 FP16 outputs (no GEGLU): dequantise, bias, activation.
 // Act is ACT_NONE, ACT_GEGLU or kActRuntime (SiLU / GELU / QuickGELU chosen by t.activation at
 // run time: the rare activations share one instance of the code).
@@ -330,7 +328,7 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
             }
             uint32_t out_words[8];
             finish_chunk_16<Kind, Act>(t, c0, acc, a_scale, has_bias, out_words);
-            if (row_ok && keep(t.flags, out_words)) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
+            if (row_ok) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
         };
         uint32_t c = t.chunk_first * 16u;
         if (c >= limit) return;
@@ -392,7 +390,7 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
                     }
                 }
             }
-            if (row_ok && keep(t.flags, out_words)) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
+            if (row_ok) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
             if (next >= limit) break;
             c0 = next;
         }
@@ -478,7 +476,6 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
     const bool skip_epilogue = (params.diagnostic_skip & 1u) != 0;
     const bool skip_loads = (params.diagnostic_skip & (2u | 4u)) != 0;
     const bool skip_mma = (params.diagnostic_skip & (2u | 8u)) != 0;
-    const bool skip_stores = (params.diagnostic_skip & 16u) != 0;
     const bool one_mma_per_stage = (params.diagnostic_skip & 32u) != 0;
     const uint32_t cta_rank = kPair ? ptx::cluster_cta_rank() : 0u;
     const bool leader = cta_rank == 0;
@@ -679,8 +676,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             tile.chunk_first = chunk_first;
             tile.activation = work.activation;
             tile.flags = (tile.row < work.m ? 1u : 0u) | ((work.flags & TILE_HAS_BIAS) != 0 ? 2u : 0u) |
-                         ((work.flags & TILE_STORE_16) != 0 ? 4u : 0u) | ((work.flags & TILE_STORE_32) != 0 ? 8u : 0u) |
-                         (skip_stores ? 16u : 0u);
+                         ((work.flags & TILE_STORE_16) != 0 ? 4u : 0u) | ((work.flags & TILE_STORE_32) != 0 ? 8u : 0u);
             const uint32_t kind = work.kind;
             const uint32_t activation = work.activation;
             tile.a_scale = a_scale;

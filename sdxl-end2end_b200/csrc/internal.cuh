@@ -125,7 +125,7 @@ struct GemmLaunchParams {
     long long wait_limit_cycles;
     uint32_t diagnostic_skip;    // tuning aid, results are meaningless when set. bit 0: no epilogue arithmetic or
                                  // stores; bit 1: no operand loads, no MMAs; bit 2: no operand loads; bit 3: no
-                                 // MMAs; bit 4: epilogue arithmetic without stores; bit 5: one MMA per stage instead
+                                 // MMAs; bit 5: one MMA per stage instead
                                  // of four. Barriers are still signalled.
     uint32_t pad0;
     GemmProblem single;
