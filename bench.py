@@ -44,7 +44,7 @@ UNIT = "TOPS"
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes (read + write) of one grouped GEMM launch of the default workload, from the ncu
 # capture summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum).
-TRAFFIC_BYTES = {"layerset640_int8": None}
+TRAFFIC_BYTES = {"layerset640_int8": 88.75e6}
 
 
 def load_peaks():
