@@ -396,19 +396,33 @@ def main():
                    for s in range(min(sets, 2))]
     host_outputs = [[torch.empty(y.shape, dtype=y.dtype).pin_memory() for y in work.outputs[s]] for s in range(min(sets, 2))]
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    # Per buffer set: inputs uploaded / plan finished / outputs downloaded. The upload of step i + 1
+    # waits only for the plan that last read its input buffers, so it overlaps the download of step
+    # i (PCIe is full duplex); the plan waits for its inputs and for the download that last read
+    # its output buffers.
+    uploaded = [torch.cuda.Event() for _ in host_inputs]
+    computed = [torch.cuda.Event() for _ in host_inputs]
+    downloaded = [torch.cuda.Event() for _ in host_inputs]
+    for s in range(len(host_inputs)):
+        computed[s].record(stream)
+        downloaded[s].record(copy_out)
 
     def e2e_step(step):
         s = step % len(host_inputs)
         with torch.cuda.stream(copy_in):
-            copy_in.wait_stream(copy_out)                       # buffers of this set are free again
+            copy_in.wait_event(computed[s])
             for key, host in host_inputs[s].items():
                 work.inputs[s][key].copy_(host, non_blocking=True)
-        stream.wait_stream(copy_in)
+            uploaded[s].record(copy_in)
+        stream.wait_event(uploaded[s])
+        stream.wait_event(downloaded[s])
         work.plans[s].run()
-        copy_out.wait_stream(stream)
+        computed[s].record(stream)
         with torch.cuda.stream(copy_out):
+            copy_out.wait_event(computed[s])
             for host, y in zip(host_outputs[s], work.outputs[s]):
                 host.copy_(y, non_blocking=True)
+            downloaded[s].record(copy_out)
 
     for step in range(2):
         e2e_step(step)
