@@ -196,6 +196,29 @@ class ClockSampler:
                 "samples_under_load": len(loaded)}
 
 
+def library_int8_rate(torch, steps: int = 20):
+    """INT8 x INT8 -> INT32 rate of the vendor library GEMM (torch._int_mm -> cuBLASLt) on an
+    [8192, 8192] x [8192, 8192] product, device-timed: the rate a plain library GEMM without any
+    epilogue reaches on this GPU, reported beside the roofline for context (it is not the peak the
+    roofline fraction uses)."""
+    try:
+        a = torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device="cuda")
+        b = torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device="cuda")
+        for _ in range(3):
+            torch._int_mm(a, b)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            torch._int_mm(a, b)
+        stop.record()
+        torch.cuda.synchronize()
+        seconds = start.elapsed_time(stop) * 1e-3 / steps
+        return {"value": 2.0 * 8192 ** 3 / seconds / 1e12, "unit": "TOPS", "what": "torch._int_mm (cuBLASLt) 8192^3, no epilogue"}
+    except Exception as error:  # the library call is context only; the bench does not depend on it
+        return {"value": None, "unit": "TOPS", "what": f"torch._int_mm unavailable: {error}"}
+
+
 # ------------------------------------------------------------------------------------------------
 # CPU arms
 # ------------------------------------------------------------------------------------------------
@@ -291,6 +314,9 @@ def main():
     parser.add_argument("--reference-rows", type=int, default=256)
     parser.add_argument("--e2e-steps", type=int, default=None)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--library-rate", action="store_true",
+                        help="also time the vendor library's plain INT8 GEMM (context for the roofline; off by default so "
+                             "that the default run launches this repository's kernels only)")
     args = parser.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -389,6 +415,8 @@ def main():
                             "bytes_per_step": quant_bytes, "ms_per_step": quant_ms_per_step},
     }
     roofline["quantize_kernel"]["frac"] = roofline["quantize_kernel"]["achieved"] / peaks["hbm_gbs"]
+    if rank == 0 and kind == "int8" and args.library_rate:
+        roofline["library_int8_gemm"] = library_int8_rate(torch)
 
     # ---- end to end: pinned host inputs -> device, run, results -> pinned host ----------------------
     e2e_steps = args.e2e_steps or max(3, min(args.steps, 20))
