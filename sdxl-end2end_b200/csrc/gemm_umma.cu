@@ -30,32 +30,37 @@ constexpr uint32_t kMaxStages = 8;
 #endif
 constexpr uint32_t kEpilogueWarps = SDXLQ_EPILOGUE_WARPS;    // a multiple of 4: warps per TMEM lane quadrant x 4
 constexpr uint32_t kWarpsPerQuadrant = kEpilogueWarps / 4;
-// Warps 0-3 form the control warpgroup (warp 0 TMA producer, warp 1 MMA issuer, warps 2-3 idle);
+// Warps 0-3 form the control warpgroup (warp 0 TMA producer, warp 1 MMA issuer, warps 2-3 stagers);
 // the epilogue warps follow. Register reallocation (setmaxnreg) works on whole warpgroups, so
 // the roles are laid out in groups of four warps: the control warpgroup hands most of its
 // registers to the epilogue warpgroups once the kernel is set up.
 constexpr uint32_t kControlWarps = 4;
 constexpr uint32_t kThreads = 32 * (kControlWarps + kEpilogueWarps);
 // Register split: the compiler budgets (64 K / threads) registers per thread, rounded down to a
-// multiple of 8 (168 for 384 threads); the control warpgroup keeps 56 and the epilogue warps share
-// what that frees: 128 * 56 + 256 * 224 = 384 * 168.
-constexpr uint32_t kControlRegisters = 56;
+// multiple of 8 (168 for 384 threads); the control warpgroup keeps 64 and the epilogue warps share
+// what that frees: 128 * 64 + 256 * 216 <= 384 * 168.
+constexpr uint32_t kControlRegisters = 64;
 constexpr uint32_t kCompiledRegisters = 65536 / kThreads / 8 * 8;
 constexpr uint32_t kEpilogueRegisters =
     (kCompiledRegisters * kThreads - 32 * kControlWarps * kControlRegisters) / (32 * kEpilogueWarps) / 8 * 8;
 static_assert(32 * kControlWarps * kControlRegisters + 32 * kEpilogueWarps * kEpilogueRegisters <= kCompiledRegisters * kThreads,
               "the register split must fit the registers the block was launched with");
 
-struct alignas(16) Control {
+struct alignas(64) Control {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
+    uint64_t staged[2];          // stager -> epilogue: the slot of this accumulator buffer is filled
+    uint64_t slot_free[2];       // epilogue -> stager: every epilogue warp of this CTA is done with the slot
     uint32_t tmem_base;
     uint32_t abort;
     uint32_t pad[2];
-    // Per-tile epilogue operands staged by the epilogue warps, one slot per accumulator buffer:
-    // the weight scale and the bias of every accumulator column of the tile.
+    // Per-tile epilogue operands, one slot per accumulator buffer, filled by the stager warp while
+    // the tile's main loop runs: the tile record, the activation scale of each of the CTA's 128
+    // rows, and the weight scale and bias of every accumulator column.
+    TileRef header[2];
+    alignas(16) float row_scale[2][kTileM];
     alignas(16) float column_scale[2][kMaxTileN];
     alignas(16) float column_bias[2][kMaxTileN];         // the FP16 bias widened to FP32 (exact)
     alignas(16) __half column_bias_half[2][kMaxTileN];
@@ -88,64 +93,56 @@ __device__ __forceinline__ void raise_abort(Control* control, uint32_t* error_wo
     atomicCAS(error_word, 0u, code);
 }
 
-__device__ __forceinline__ void epilogue_barrier() {
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
-}
-
-// The weight scale and the bias of the accumulator columns one epilogue thread stages for a tile,
-// plus the activation scale of the thread's output row. Loaded into registers one tile ahead and
-// written to shared memory once the previous user of the slot is done.
+// Fills one slot with a tile's epilogue operands. Run by the two stager warps: `part` 0 takes the
+// lower half of the columns and rows, `part` 1 the upper half. All loads are issued before the
+// first store so that their latencies overlap.
 // Column j of a GEGLU tile is value column n0 + j for j < tile_n / 2 and gate column
-// n_out + n0 + (j - tile_n / 2) otherwise. Columns past the matrix edge get scale 0, bias 0.
-constexpr uint32_t kColumnsPerThread = (kMaxTileN + 32 * kEpilogueWarps - 1) / (32 * kEpilogueWarps);
-
-struct ColumnOperands {
-    float scale[kColumnsPerThread];
-    __half bias[kColumnsPerThread];
-    float a_scale;
-};
-
-__device__ __forceinline__ ColumnOperands load_column_operands(const TileRef& tile, uint32_t thread, uint32_t row) {
-    ColumnOperands values;
+// n_out + n0 + (j - tile_n / 2) otherwise. Columns past the matrix edge get scale 0, bias 0; rows
+// past it get activation scale 0.
+__device__ __forceinline__ void stage_tile(const TileRef& tile, uint32_t first_row, uint32_t lane, uint32_t part,
+                                           Control* control, uint32_t slot) {
     const bool geglu = tile.activation == ACT_GEGLU;
     const bool scaled = tile.kind != KIND_F16;
     const bool per_channel = (tile.flags & TILE_SCALE_PER_CHANNEL) != 0;
+    const bool has_bias = (tile.flags & TILE_HAS_BIAS) != 0;
     const uint32_t tile_n = tile.tile_n;
     const uint32_t half = tile_n / 2;
     const uint32_t n0 = tile.tile_n_index * (geglu ? half : tile_n);
+    constexpr uint32_t kColumns = kMaxTileN / 64u;      // columns per lane and part
+    constexpr uint32_t kRows = kTileM / 64u;            // rows per lane and part
+    float scale[kColumns];
+    __half bias[kColumns];
+    float a_scale[kRows];
 #pragma unroll
-    for (uint32_t i = 0; i < kColumnsPerThread; ++i) {
-        const uint32_t j = thread + i * 32 * kEpilogueWarps;
+    for (uint32_t i = 0; i < kColumns; ++i) {
+        const uint32_t j = part * (kMaxTileN / 2u) + lane + 32u * i;
         const uint32_t local = (geglu && j >= half) ? j - half : j;
         const bool valid = j < tile_n && n0 + local < tile.n_out;
         const uint32_t column = (geglu && j >= half) ? tile.n_out + n0 + local : n0 + local;
-        float scale = 0.0f;
-        __half bias = __half(0);
+        scale[i] = 0.0f;
+        bias[i] = __half(0);
         if (valid) {
-            scale = scaled ? __ldg(tile.w_scales + (per_channel ? column : 0u)) : 1.0f;
-            if ((tile.flags & TILE_HAS_BIAS) != 0) bias = tile.bias[column];
+            scale[i] = scaled ? __ldg(tile.w_scales + (per_channel ? column : 0u)) : 1.0f;
+            if (has_bias) bias[i] = tile.bias[column];
         }
-        values.scale[i] = scale;
-        values.bias[i] = bias;
     }
-    values.a_scale = 1.0f;
-    if (tile.kind == KIND_I8) values.a_scale = row < tile.m ? __ldg(tile.a_scales + row) : 0.0f;
-    else if (tile.kind != KIND_F16) values.a_scale = __ldg(tile.a_scales);
-    return values;
-}
-
-__device__ __forceinline__ void store_column_operands(const ColumnOperands& values, uint32_t tile_n, uint32_t thread,
-                                                      float* column_scale, float* column_bias,
-                                                      __half* column_bias_half) {
 #pragma unroll
-    for (uint32_t i = 0; i < kColumnsPerThread; ++i) {
-        const uint32_t j = thread + i * 32 * kEpilogueWarps;
-        if (j < tile_n) {
-            column_scale[j] = values.scale[i];
-            column_bias[j] = __half2float(values.bias[i]);
-            column_bias_half[j] = values.bias[i];
-        }
+    for (uint32_t i = 0; i < kRows; ++i) {
+        const uint32_t r = part * (kTileM / 2u) + lane + 32u * i;
+        a_scale[i] = 1.0f;
+        if (tile.kind == KIND_I8) a_scale[i] = first_row + r < tile.m ? __ldg(tile.a_scales + first_row + r) : 0.0f;
+        else if (tile.kind != KIND_F16) a_scale[i] = __ldg(tile.a_scales);
     }
+#pragma unroll
+    for (uint32_t i = 0; i < kColumns; ++i) {
+        const uint32_t j = part * (kMaxTileN / 2u) + lane + 32u * i;
+        control->column_scale[slot][j] = scale[i];
+        control->column_bias[slot][j] = __half2float(bias[i]);
+        control->column_bias_half[slot][j] = bias[i];
+    }
+#pragma unroll
+    for (uint32_t i = 0; i < kRows; ++i) control->row_scale[slot][part * (kTileM / 2u) + lane + 32u * i] = a_scale[i];
+    if (part == 0 && lane == 0) control->header[slot] = tile;
 }
 
 __device__ __forceinline__ __half packed_half(const uint32_t word, int index) {
@@ -461,7 +458,7 @@ __device__ __forceinline__ bool issue_tile_mmas(MmaCursor& c, uint32_t tmem_d, u
 template <bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
-    extern __shared__ __align__(16) uint8_t dynamic_smem[];
+    extern __shared__ __align__(128) uint8_t dynamic_smem[];
     Control* control = reinterpret_cast<Control*>(dynamic_smem);
     const uint32_t stages_base = (ptx::smem_u32(dynamic_smem) + sizeof(Control) + 1023u) & ~1023u;
 
@@ -491,6 +488,8 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
         for (uint32_t b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_u32(&control->tmem_full[b]), 1);
             ptx::mbar_init(ptx::smem_u32(&control->tmem_empty[b]), kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
+            ptx::mbar_init(ptx::smem_u32(&control->staged[b]), 2);
+            ptx::mbar_init(ptx::smem_u32(&control->slot_free[b]), kEpilogueWarps);
         }
         control->abort = 0;
         ptx::fence_mbar_init();
@@ -633,6 +632,28 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                 }
             }
         }
+    } else {
+        // ------------------------------- stagers (warps 2 and 3) ---------------------------
+        // Fill the epilogue's operand slot of each tile (tile record, row scales, column scales
+        // and bias) while the tile's main loop runs, up to two tiles ahead of the epilogue.
+        uint32_t iteration = 0;
+        TileRef next = load_tile(params, first_tile);
+        for (uint32_t t = first_tile; t < num_tiles; t += tile_stride, ++iteration) {
+            const TileRef work = next;
+            next = load_tile(params, t + tile_stride);
+            const uint32_t slot = iteration & 1u;
+            uint32_t ok = 1;
+            if (lane == 0) {
+                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&control->slot_free[slot]), ((iteration >> 1) & 1u) ^ 1u,
+                                            abort_word, limit) ? 1u : 0u;
+                if (ok == 0) raise_abort(control, params.error_word, DEV_TIMEOUT_EPILOGUE + 1);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (ok == 0) break;
+            stage_tile(work, work.tile_m * kRowsPerTile + cta_rank * kTileM, lane, warp - 2u, control, slot);
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&control->staged[slot]));
+        }
     }
     } else {
         // ------------------------------- epilogue ------------------------------------------
@@ -641,74 +662,55 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
         // chunks of the tile round-robin.
         const uint32_t quadrant = warp & 3u;
         const uint32_t chunk_first = (warp - kControlWarps) >> 2;      // 0 .. kWarpsPerQuadrant - 1
-        const uint32_t epilogue_thread = threadIdx.x - 32u * kControlWarps;
-        const uint32_t row_in_tile = cta_rank * kTileM + quadrant * 32u + lane;
+        const uint32_t row_in_cta = quadrant * 32u + lane;
         uint32_t iteration = 0;
-        bool ok = true;
-        // Software pipeline over this CTA's tiles: the record of tile i + 2 and the column operands
-        // of tile i + 1 are loaded into registers while tile i is drained, so that no global-memory
-        // latency sits between two tiles.
-        TileRef work = load_tile(params, first_tile);
-        TileRef next = load_tile(params, first_tile + tile_stride);
-        ColumnOperands operands = load_column_operands(work, epilogue_thread, work.tile_m * kRowsPerTile + row_in_tile);
-        store_column_operands(operands, work.tile_n, epilogue_thread, control->column_scale[0], control->column_bias[0],
-                              control->column_bias_half[0]);
         for (uint32_t t = first_tile; t < num_tiles; t += tile_stride, ++iteration) {
             const uint32_t buffer = iteration & 1u;
             const uint32_t accumulator_phase = (iteration >> 1) & 1u;
-            const float a_scale = operands.a_scale;
-            const TileRef after_next = load_tile(params, t + 2u * tile_stride);
-            operands = load_column_operands(next, epilogue_thread, next.tile_m * kRowsPerTile + row_in_tile);
-            const bool geglu = work.activation == ACT_GEGLU;
+            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->staged[buffer]), accumulator_phase, abort_word, limit)) {
+                raise_abort(control, params.error_word, DEV_TIMEOUT_EPILOGUE);
+                break;
+            }
+            const TileRef& work = control->header[buffer];
+            const uint32_t tile_n = work.tile_n;
+            const uint32_t activation = work.activation;
+            const uint32_t kind = work.kind;
+            const uint32_t flags = work.flags;
             EpilogueTile tile;
             tile.y = work.y;
             tile.acc_out = nullptr;
-            if ((work.flags & TILE_RAW_ACCUMULATORS) != 0) tile.acc_out = tile_problem(params, work)->ep.acc_out;
+            if ((flags & TILE_RAW_ACCUMULATORS) != 0) tile.acc_out = tile_problem(params, work)->ep.acc_out;
             tile.column_scale = control->column_scale[buffer];
             tile.column_bias = control->column_bias[buffer];
             tile.column_bias_half = control->column_bias_half[buffer];
             tile.n = work.n;
             tile.n_out = work.n_out;
-            tile.tile_n = work.tile_n;
-            tile.n0 = work.tile_n_index * (geglu ? work.tile_n / 2u : work.tile_n);
-            tile.row = work.tile_m * kRowsPerTile + row_in_tile;
+            tile.tile_n = tile_n;
+            tile.n0 = work.tile_n_index * (activation == ACT_GEGLU ? tile_n / 2u : tile_n);
+            tile.row = work.tile_m * kRowsPerTile + cta_rank * kTileM + row_in_cta;
             tile.tmem_row = tmem_base + ((quadrant * 32u) << 16) + buffer * kMaxTileN;
             tile.chunk_first = chunk_first;
-            tile.activation = work.activation;
-            tile.flags = (tile.row < work.m ? 1u : 0u) | ((work.flags & TILE_HAS_BIAS) != 0 ? 2u : 0u) |
-                         ((work.flags & TILE_STORE_16) != 0 ? 4u : 0u) | ((work.flags & TILE_STORE_32) != 0 ? 8u : 0u);
-            const uint32_t kind = work.kind;
-            const uint32_t activation = work.activation;
-            tile.a_scale = a_scale;
-            // Every warp is done with tile i - 1 here, so the other slot may be rewritten below;
-            // this tile's slot was written before the barrier.
-            epilogue_barrier();
-            if (ok && !ptx::mbar_wait_bounded(ptx::smem_u32(&control->tmem_full[buffer]), accumulator_phase,
-                                              abort_word, limit)) {
+            tile.activation = activation;
+            tile.flags = (tile.row < work.m ? 1u : 0u) | ((flags & TILE_HAS_BIAS) != 0 ? 2u : 0u) |
+                         ((flags & TILE_STORE_16) != 0 ? 4u : 0u) | ((flags & TILE_STORE_32) != 0 ? 8u : 0u);
+            tile.a_scale = control->row_scale[buffer][row_in_cta];
+            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->tmem_full[buffer]), accumulator_phase, abort_word, limit)) {
                 raise_abort(control, params.error_word, DEV_TIMEOUT_EPILOGUE);
-                ok = false;
+                break;
             }
-            // After a timeout the warp keeps walking the tile list (so that the barrier above
-            // stays balanced) but touches neither TMEM nor global memory again.
-            if (ok) {
-                ptx::tc_fence_after();
-                if (skip_epilogue) { /* diagnostic: accumulators are dropped */ }
-                else if (kind == KIND_I8) epilogue_dispatch<KIND_I8>(activation, tile);
-                else if (kind == KIND_F16) epilogue_dispatch<KIND_F16>(activation, tile);
-                else epilogue_dispatch<KIND_E4M3>(activation, tile);
-                ptx::tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    const uint32_t empty_bar = ptx::smem_u32(&control->tmem_empty[buffer]);
-                    if (kPair) ptx::mbar_arrive_cluster(empty_bar & ptx::kPeerBitMask);   // the leader's barrier
-                    else ptx::mbar_arrive(empty_bar);
-                }
+            ptx::tc_fence_after();
+            if (skip_epilogue) { /* diagnostic: accumulators are dropped */ }
+            else if (kind == KIND_I8) epilogue_dispatch<KIND_I8>(activation, tile);
+            else if (kind == KIND_F16) epilogue_dispatch<KIND_F16>(activation, tile);
+            else epilogue_dispatch<KIND_E4M3>(activation, tile);
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t empty_bar = ptx::smem_u32(&control->tmem_empty[buffer]);
+                if (kPair) ptx::mbar_arrive_cluster(empty_bar & ptx::kPeerBitMask);   // the leader's barrier
+                else ptx::mbar_arrive(empty_bar);
+                ptx::mbar_arrive(ptx::smem_u32(&control->slot_free[buffer]));
             }
-            // The next tile's column operands (loaded above) go into the other slot.
-            store_column_operands(operands, next.tile_n, epilogue_thread, control->column_scale[buffer ^ 1u],
-                                  control->column_bias[buffer ^ 1u], control->column_bias_half[buffer ^ 1u]);
-            work = next;
-            next = after_next;
         }
     }
 
