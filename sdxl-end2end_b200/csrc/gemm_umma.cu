@@ -546,7 +546,8 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                 // pair: this CTA's half of the B rows (GEGLU: value rows in the leader, gate rows in the peer)
                 const int32_t row_b_pair = geglu ? (leader ? row_b : row_gate)
                                                       : row_b + static_cast<int32_t>(cta_rank * half);
-                const uint32_t k_blocks = work.k_blocks;
+                // diagnostic without loads and MMAs: no stage hand-shakes either, the epilogue runs alone
+                const uint32_t k_blocks = (skip_loads && skip_mma) ? 0u : work.k_blocks;
                 int32_t k0 = 0;
                 for (uint32_t kb = 0; kb < k_blocks; ++kb, k0 += k_step) {
                     if (!ptx::mbar_wait_bounded(empty_base + stage * 8u, phase ^ 1u, abort_word, limit)) {
@@ -616,9 +617,10 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                 }
                 ptx::tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buffer * kMaxTileN;
-                if (work.kind == KIND_I8) ok = issue_tile_mmas<0, kPair>(cursor, tmem_d, work.idesc, work.k_blocks);
-                else if (work.kind == KIND_F16) ok = issue_tile_mmas<2, kPair>(cursor, tmem_d, work.idesc, work.k_blocks);
-                else ok = issue_tile_mmas<1, kPair>(cursor, tmem_d, work.idesc, work.k_blocks);
+                const uint32_t k_blocks = (skip_loads && skip_mma) ? 0u : work.k_blocks;
+                if (work.kind == KIND_I8) ok = issue_tile_mmas<0, kPair>(cursor, tmem_d, work.idesc, k_blocks);
+                else if (work.kind == KIND_F16) ok = issue_tile_mmas<2, kPair>(cursor, tmem_d, work.idesc, k_blocks);
+                else ok = issue_tile_mmas<1, kPair>(cursor, tmem_d, work.idesc, k_blocks);
                 if (!ok) {
                     raise_abort(control, params.error_word, DEV_TIMEOUT_MMA + 1);
                     break;
