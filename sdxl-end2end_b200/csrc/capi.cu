@@ -65,6 +65,9 @@ struct sdxlq_context {
     uint32_t fp8_dirty[2] = {0, 0};        // amax words of each parity left non-zero
     int sm_count = 148;
     size_t umma_smem_attribute[2] = {0, 0};   // per kernel flavour: single CTA, CTA pair
+    int geglu_tile_n = 0;                     // tuning: accumulator tile width of GEGLU projections in grouped launches
+                                              // (0: cost model). 128 lets the MMA issuer run three tiles ahead of the
+                                              // GEGLU epilogues but measured slower (operand traffic, per-tile costs).
     int pair_mode = 0;                        // 0 never use CTA pairs (default: they measured no faster), 1 whenever
                                               // possible, -1 for traffic-bound launches only
     uint32_t diagnostic_skip = 0;             // SDXLQ_DIAGNOSTIC_SKIP: tuning aid, see GemmLaunchParams
@@ -218,6 +221,10 @@ TileChoice choose_tile(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool ge
         const uint32_t pair_step = 32;
         if (pair_allowed) return TileChoice{std::max(pair_step, forced / pair_step * pair_step), true};
         return TileChoice{std::max(step, forced / step * step), false};
+    }
+    // Tuning override for the epilogue-heavy GEGLU tiles of a grouped launch (see geglu_tile_n).
+    if (geglu && grouped && ctx->geglu_tile_n >= 32 && !pair_allowed) {
+        return TileChoice{std::min<uint32_t>(kMaxTileN, static_cast<uint32_t>(ctx->geglu_tile_n) / 32u * 32u), false};
     }
     TileChoice best{step, false};
     double best_cost = 1e300;
@@ -694,6 +701,7 @@ int sdxlq_context_create(int device, void* stream, size_t workspace_bytes, sdxlq
     }
     if (const char* text = std::getenv("SDXLQ_TILE_N")) ctx->forced_tile_n = std::atoi(text);
     if (const char* text = std::getenv("SDXLQ_PAIR")) ctx->pair_mode = std::atoi(text);
+    if (const char* text = std::getenv("SDXLQ_GEGLU_TILE_N")) ctx->geglu_tile_n = std::atoi(text);
     if (const char* text = std::getenv("SDXLQ_DIAGNOSTIC_SKIP")) ctx->diagnostic_skip = static_cast<uint32_t>(std::atoi(text));
     *out = ctx;
     return SDXLQ_OK;

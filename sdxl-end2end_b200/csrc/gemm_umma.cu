@@ -46,24 +46,46 @@ constexpr uint32_t kEpilogueRegisters =
 static_assert(32 * kControlWarps * kControlRegisters + 32 * kEpilogueWarps * kEpilogueRegisters <= kCompiledRegisters * kThreads,
               "the register split must fit the registers the block was launched with");
 
+// The 512 accumulator columns of tensor memory are handed out in quarters of 128: a tile of up to
+// 128 accumulator columns takes one quarter, a wider one two adjacent quarters (never wrapping
+// around). The MMA issuer and the epilogue warps walk the same tile list and place every tile with
+// the same rule, so no placement is communicated. With narrow tiles up to four tiles are in
+// flight between the two roles, with wide tiles two.
+constexpr uint32_t kAccQuarters = 4;
+constexpr uint32_t kQuarterColumns = kTmemColumns / kAccQuarters;
+constexpr uint32_t kSlots = 4;
+
+struct AccumulatorRing {
+    uint32_t cursor = 0;     // next free quarter
+    uint32_t parity = 0;     // one bit per quarter, toggled at each use of the quarter by this role
+    // Places a tile: returns its first quarter, sets `quarters` to how many it takes.
+    __device__ __forceinline__ uint32_t place(uint32_t tile_n, uint32_t& quarters) {
+        quarters = tile_n > kQuarterColumns ? 2u : 1u;
+        if (cursor + quarters > kAccQuarters) cursor = 0;
+        const uint32_t first = cursor;
+        cursor = (cursor + quarters) & (kAccQuarters - 1u);
+        return first;
+    }
+};
+
 struct alignas(64) Control {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
-    uint64_t tmem_full[2];
-    uint64_t tmem_empty[2];
-    uint64_t staged[2];          // stager -> epilogue: the slot of this accumulator buffer is filled
-    uint64_t slot_free[2];       // epilogue -> stager: every epilogue warp of this CTA is done with the slot
+    uint64_t acc_full[kAccQuarters];    // MMA issuer -> epilogue: the tile whose first quarter this is, is complete
+    uint64_t acc_empty[kAccQuarters];   // epilogue -> MMA issuer: this quarter of the accumulator columns is drained
+    uint64_t staged[kSlots];            // stagers -> epilogue: the operand slot of this tile is filled
+    uint64_t slot_free[kSlots];         // epilogue -> stagers: every epilogue warp of this CTA is done with the slot
     uint32_t tmem_base;
     uint32_t abort;
     uint32_t pad[2];
-    // Per-tile epilogue operands, one slot per accumulator buffer, filled by the stager warp while
-    // the tile's main loop runs: the tile record, the activation scale of each of the CTA's 128
-    // rows, and the weight scale and bias of every accumulator column.
-    TileRef header[2];
-    alignas(16) float row_scale[2][kTileM];
-    alignas(16) float column_scale[2][kMaxTileN];
-    alignas(16) float column_bias[2][kMaxTileN];         // the FP16 bias widened to FP32 (exact)
-    alignas(16) __half column_bias_half[2][kMaxTileN];
+    // Per-tile epilogue operands, a ring of slots (tile i of the CTA uses slot i % kSlots), filled
+    // by the stager warps while the tile's main loop runs: the tile record, the activation scale of
+    // each of the CTA's 128 rows, and the weight scale and bias of every accumulator column.
+    TileRef header[kSlots];
+    alignas(16) float row_scale[kSlots][kTileM];
+    alignas(16) float column_scale[kSlots][kMaxTileN];
+    alignas(16) float column_bias[kSlots][kMaxTileN];         // the FP16 bias widened to FP32 (exact)
+    alignas(16) __half column_bias_half[kSlots][kMaxTileN];
 };
 
 // The record of tile `index` of the launch. Single-problem launches build it from the kernel
@@ -453,8 +475,8 @@ __device__ __forceinline__ bool issue_tile_mmas(MmaCursor& c, uint32_t tmem_d, u
 //   rows of A and half of the tile's B rows (for GEGLU: the leader the value rows, its peer the
 //   gate rows); the leader's elected thread issues M=256 MMAs that read both CTAs' shared memory
 //   and write 128 accumulator rows into each CTA's tensor memory. Every TMA load of the pair counts
-//   on the leader's full barrier; the MMA completion is committed to both CTAs' empty / tmem_full
-//   barriers; both CTAs' epilogue warps arrive on the leader's tmem_empty barrier.
+//   on the leader's full barrier; the MMA completion is committed to both CTAs' empty / acc_full
+//   barriers; both CTAs' epilogue warps arrive on the leader's acc_empty barriers.
 template <bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
@@ -485,9 +507,11 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             ptx::mbar_init(ptx::smem_u32(&control->full[s]), 1);
             ptx::mbar_init(ptx::smem_u32(&control->empty[s]), 1);
         }
-        for (uint32_t b = 0; b < 2; ++b) {
-            ptx::mbar_init(ptx::smem_u32(&control->tmem_full[b]), 1);
-            ptx::mbar_init(ptx::smem_u32(&control->tmem_empty[b]), kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
+        for (uint32_t b = 0; b < kAccQuarters; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&control->acc_full[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&control->acc_empty[b]), kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
+        }
+        for (uint32_t b = 0; b < kSlots; ++b) {
             ptx::mbar_init(ptx::smem_u32(&control->staged[b]), 2);
             ptx::mbar_init(ptx::smem_u32(&control->slot_free[b]), kEpilogueWarps);
         }
@@ -602,21 +626,26 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             cursor.abort_word = abort_word;
             cursor.limit = limit;
             cursor.mode = (skip_mma ? 1u : 0u) | (one_mma_per_stage ? 2u : 0u);
-            uint32_t iteration = 0;
+            AccumulatorRing ring;
             bool ok = true;
             TileRef next = load_tile(params, first_tile);
-            for (uint32_t t = first_tile; ok && t < num_tiles; t += tile_stride, ++iteration) {
+            for (uint32_t t = first_tile; ok && t < num_tiles; t += tile_stride) {
                 const TileRef work = next;
                 next = load_tile(params, t + tile_stride);      // in flight while this tile's MMAs are issued
-                const uint32_t buffer = iteration & 1u;
-                const uint32_t accumulator_phase = (iteration >> 1) & 1u;
-                if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->tmem_empty[buffer]),
-                                            accumulator_phase ^ 1u, abort_word, limit)) {
+                uint32_t quarters;
+                const uint32_t first_quarter = ring.place(work.tile_n, quarters);
+                for (uint32_t q = first_quarter; ok && q < first_quarter + quarters; ++q) {
+                    // the quarter's previous user (if any) has been drained by every epilogue warp
+                    ok = ptx::mbar_wait_bounded(ptx::smem_u32(&control->acc_empty[q]), ((ring.parity >> q) & 1u) ^ 1u,
+                                                abort_word, limit);
+                    ring.parity ^= 1u << q;
+                }
+                if (!ok) {
                     raise_abort(control, params.error_word, DEV_TIMEOUT_MMA);
                     break;
                 }
                 ptx::tc_fence_after();
-                const uint32_t tmem_d = tmem_base + buffer * kMaxTileN;
+                const uint32_t tmem_d = tmem_base + first_quarter * kQuarterColumns;
                 const uint32_t k_blocks = (skip_loads && skip_mma) ? 0u : work.k_blocks;
                 if (work.kind == KIND_I8) ok = issue_tile_mmas<0, kPair>(cursor, tmem_d, work.idesc, k_blocks);
                 else if (work.kind == KIND_F16) ok = issue_tile_mmas<2, kPair>(cursor, tmem_d, work.idesc, k_blocks);
@@ -625,7 +654,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                     raise_abort(control, params.error_word, DEV_TIMEOUT_MMA + 1);
                     break;
                 }
-                const uint32_t full_bar = ptx::smem_u32(&control->tmem_full[buffer]);
+                const uint32_t full_bar = ptx::smem_u32(&control->acc_full[first_quarter]);
                 if (kPair) {
                     ptx::umma_commit_pair(full_bar);
                     ptx::umma_commit_pair(ptx::map_to_cta(full_bar, 1));
@@ -637,16 +666,16 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
     } else {
         // ------------------------------- stagers (warps 2 and 3) ---------------------------
         // Fill the epilogue's operand slot of each tile (tile record, row scales, column scales
-        // and bias) while the tile's main loop runs, up to two tiles ahead of the epilogue.
+        // and bias) while the tile's main loop runs, up to kSlots tiles ahead of the epilogue.
         uint32_t iteration = 0;
         TileRef next = load_tile(params, first_tile);
         for (uint32_t t = first_tile; t < num_tiles; t += tile_stride, ++iteration) {
             const TileRef work = next;
             next = load_tile(params, t + tile_stride);
-            const uint32_t slot = iteration & 1u;
+            const uint32_t slot = iteration % kSlots;
             uint32_t ok = 1;
             if (lane == 0) {
-                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&control->slot_free[slot]), ((iteration >> 1) & 1u) ^ 1u,
+                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&control->slot_free[slot]), ((iteration / kSlots) & 1u) ^ 1u,
                                             abort_word, limit) ? 1u : 0u;
                 if (ok == 0) raise_abort(control, params.error_word, DEV_TIMEOUT_EPILOGUE + 1);
             }
@@ -665,11 +694,11 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
         const uint32_t quadrant = warp & 3u;
         const uint32_t chunk_first = (warp - kControlWarps) >> 2;      // 0 .. kWarpsPerQuadrant - 1
         const uint32_t row_in_cta = quadrant * 32u + lane;
+        AccumulatorRing ring;
         uint32_t iteration = 0;
         for (uint32_t t = first_tile; t < num_tiles; t += tile_stride, ++iteration) {
-            const uint32_t buffer = iteration & 1u;
-            const uint32_t accumulator_phase = (iteration >> 1) & 1u;
-            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->staged[buffer]), accumulator_phase, abort_word, limit)) {
+            const uint32_t buffer = iteration % kSlots;
+            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->staged[buffer]), (iteration / kSlots) & 1u, abort_word, limit)) {
                 raise_abort(control, params.error_word, DEV_TIMEOUT_EPILOGUE);
                 break;
             }
@@ -690,16 +719,20 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             tile.tile_n = tile_n;
             tile.n0 = work.tile_n_index * (activation == ACT_GEGLU ? tile_n / 2u : tile_n);
             tile.row = work.tile_m * kRowsPerTile + cta_rank * kTileM + row_in_cta;
-            tile.tmem_row = tmem_base + ((quadrant * 32u) << 16) + buffer * kMaxTileN;
+            uint32_t quarters;
+            const uint32_t first_quarter = ring.place(tile_n, quarters);
+            tile.tmem_row = tmem_base + ((quadrant * 32u) << 16) + first_quarter * kQuarterColumns;
             tile.chunk_first = chunk_first;
             tile.activation = activation;
             tile.flags = (tile.row < work.m ? 1u : 0u) | ((flags & TILE_HAS_BIAS) != 0 ? 2u : 0u) |
                          ((flags & TILE_STORE_16) != 0 ? 4u : 0u) | ((flags & TILE_STORE_32) != 0 ? 8u : 0u);
             tile.a_scale = control->row_scale[buffer][row_in_cta];
-            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->tmem_full[buffer]), accumulator_phase, abort_word, limit)) {
+            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->acc_full[first_quarter]), (ring.parity >> first_quarter) & 1u,
+                                        abort_word, limit)) {
                 raise_abort(control, params.error_word, DEV_TIMEOUT_EPILOGUE);
                 break;
             }
+            ring.parity ^= 1u << first_quarter;
             ptx::tc_fence_after();
             if (skip_epilogue) { /* diagnostic: accumulators are dropped */ }
             else if (kind == KIND_I8) epilogue_dispatch<KIND_I8>(activation, tile);
@@ -708,9 +741,11 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) {
-                const uint32_t empty_bar = ptx::smem_u32(&control->tmem_empty[buffer]);
-                if (kPair) ptx::mbar_arrive_cluster(empty_bar & ptx::kPeerBitMask);   // the leader's barrier
-                else ptx::mbar_arrive(empty_bar);
+                for (uint32_t q = first_quarter; q < first_quarter + quarters; ++q) {
+                    const uint32_t empty_bar = ptx::smem_u32(&control->acc_empty[q]);
+                    if (kPair) ptx::mbar_arrive_cluster(empty_bar & ptx::kPeerBitMask);   // the leader's barrier
+                    else ptx::mbar_arrive(empty_bar);
+                }
                 ptx::mbar_arrive(ptx::smem_u32(&control->slot_free[buffer]));
             }
         }
