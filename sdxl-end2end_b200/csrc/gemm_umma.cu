@@ -429,6 +429,7 @@ __device__ __forceinline__ void epilogue_dispatch(uint32_t activation, const Epi
 struct MmaCursor {
     uint32_t stage, phase, num_stages;
     uint32_t full_base, empty_base;     // shared-memory addresses of full[0] / empty[0]
+    uint32_t peer_empty_base;           // CTA pairs: empty[0] of the peer CTA as a shared::cluster address
     uint32_t a_lo_base;                 // descriptor low word of stage 0's A tile
     uint32_t stage_units, b_units;      // stage size and B offset in descriptor units (16 bytes)
     volatile uint32_t* abort_word;
@@ -458,8 +459,8 @@ __device__ __forceinline__ bool issue_tile_mmas(MmaCursor& c, uint32_t tmem_d, u
         accumulate = 1;
         const uint32_t empty_bar = c.empty_base + stage * 8u;
         if (kPair) {
-            ptx::umma_commit_pair(empty_bar);                        // frees the leader's stage
-            ptx::umma_commit_pair(ptx::map_to_cta(empty_bar, 1));    // and the peer's
+            ptx::umma_commit_pair(empty_bar);                                 // frees the leader's stage
+            ptx::umma_commit_pair(c.peer_empty_base + stage * 8u);            // and the peer's
         } else {
             ptx::umma_commit(empty_bar);
         }
@@ -496,6 +497,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
     const bool skip_loads = (params.diagnostic_skip & (2u | 4u)) != 0;
     const bool skip_mma = (params.diagnostic_skip & (2u | 8u)) != 0;
     const bool one_mma_per_stage = (params.diagnostic_skip & 32u) != 0;
+    const bool a_loads_only = (params.diagnostic_skip & 64u) != 0;
     const uint32_t cta_rank = kPair ? ptx::cluster_cta_rank() : 0u;
     const bool leader = cta_rank == 0;
     const uint32_t first_tile = kPair ? blockIdx.x >> 1 : blockIdx.x;
@@ -588,6 +590,9 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                         if (leader) ptx::mbar_expect_tx(full_bar, tx_bytes);
                         ptx::tma_load_2d_pair(a_dst, tmap_a, full_bar, k0, row_a);
                         ptx::tma_load_2d_pair(b_dst, tmap_b, full_bar, k0, row_b_pair);
+                    } else if (a_loads_only) {      // diagnostic: half of the copy instructions, a third of the bytes
+                        ptx::mbar_expect_tx(full_bar, kTileM * kTileKBytes);
+                        ptx::tma_load_2d(a_dst, tmap_a, full_bar, k0, row_a);
                     } else {
                         ptx::mbar_expect_tx(full_bar, tx_bytes);
                         ptx::tma_load_2d(a_dst, tmap_a, full_bar, k0, row_a);
@@ -620,6 +625,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             cursor.num_stages = num_stages;
             cursor.full_base = ptx::smem_u32(&control->full[0]);
             cursor.empty_base = ptx::smem_u32(&control->empty[0]);
+            cursor.peer_empty_base = kPair ? ptx::map_to_cta(cursor.empty_base, 1) : 0u;
             cursor.a_lo_base = ptx::umma_desc_lo(stages_base);
             cursor.stage_units = stage_bytes >> 4;
             cursor.b_units = b_offset >> 4;

@@ -126,7 +126,7 @@ struct GemmLaunchParams {
     uint32_t diagnostic_skip;    // tuning aid, results are meaningless when set. bit 0: no epilogue arithmetic or
                                  // stores; bit 1: no operand loads, no MMAs; bit 2: no operand loads; bit 3: no
                                  // MMAs; bit 5: one MMA per stage instead
-                                 // of four. Barriers are still signalled.
+                                 // of four; bit 6: only the A operand is loaded. Barriers are still signalled.
     uint32_t pad0;
     GemmProblem single;
 };
