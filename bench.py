@@ -81,6 +81,13 @@ def workload_rows(name: str):
     if name == "layerset1280_fp8":
         return layer_set(1280, 2048, 154), "e4m3", ("SDXL UNet 1280-dim layer set, FP8 E4M3 per-channel weights, native FP8 activations, "
                                                     "M=2048; plus cross-attention to_k/to_v [154,2048]x[1280,2048]")
+    if name == "crossattn_kv_int8":
+        # what a cross-attention K/V cache takes out of every denoising step
+        shapes = importlib.import_module("sdxl-end2end_b200.unet_shapes")
+        rows = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in shapes.unet_projections(2)
+                if ".attn2.to_k" in p.name or ".attn2.to_v" in p.name]
+        return rows, "int8", (f"the {len(rows)} cross-attention to_k/to_v projections [154,2048]x[640|1280,2048] of one SDXL UNet step, "
+                              "INT8 ConvRot, one grouped launch (HBM-bound: weights are read once)")
     if name in ("unet743_int8", "unet743_e5m2"):
         shapes = importlib.import_module("sdxl-end2end_b200.unet_shapes")
         rows = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in shapes.unet_projections(2)]

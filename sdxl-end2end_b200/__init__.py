@@ -15,7 +15,7 @@ from __future__ import annotations
 
 from .api import (  # noqa: F401
     ACT_GEGLU, ACT_GELU, ACT_NONE, ACT_QUICK_GELU, ACT_SILU,
-    CudaError, Context, FP8WeightLoadOptions, GroupPlan, INT8WeightLoadOptions, LinearActivation,
+    CrossAttentionKVCache, CudaError, Context, FP8WeightLoadOptions, GroupPlan, INT8WeightLoadOptions, LinearActivation,
     LinearCall, Ops, QuantizationMetadata, ScalarType, FP8ScaleMode, FP8StorageLayout, Weight,
     library_path, load_library, valid_convrot_group_size,
 )

@@ -566,3 +566,37 @@ class GroupPlan:
             self.close()
         except Exception:
             pass
+
+
+class CrossAttentionKVCache:
+    """Every cross-attention to_k / to_v projection of the UNet computed once per generation.
+
+    `attn2.to_k` and `attn2.to_v` of every transformer block project the text encoder's hidden
+    states (UNet::transformer_block, src/cuda/unet.cpp:120-127), which do not change between
+    denoising steps; the reference recomputes all 140 of them in each of its steps. This cache runs
+    them as ONE grouped launch (one quantisation of the hidden states shared by every projection
+    with the same rotation, one GEMM launch) and hands the results out by name for all steps.
+    """
+
+    def __init__(self, ops: Ops, encoder_hidden_states: torch.Tensor, projections: Sequence[tuple]):
+        """projections: (name, Weight, bias or None) per to_k / to_v weight."""
+        self.names = [name for name, _, _ in projections]
+        if len(set(self.names)) != len(self.names):
+            raise CudaError("cross-attention cache: duplicate projection name")
+        calls = [LinearCall(encoder_hidden_states, weight, bias) for _, weight, bias in projections]
+        self._plan = ops.plan(calls)
+        self._outputs = dict(zip(self.names, self._plan.run()))
+
+    @property
+    def launches(self) -> int:
+        return self._plan.launches
+
+    def refresh(self) -> None:
+        """Recomputes every projection (new prompt written into the same hidden-state buffer)."""
+        self._plan.run()
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        return self._outputs[name]
+
+    def close(self) -> None:
+        self._plan.close()

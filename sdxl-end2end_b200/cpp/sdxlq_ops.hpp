@@ -157,9 +157,59 @@ public:
     [[nodiscard]] TensorRef quantize_e4m3(const TensorRef& input) const { return quantize_fp8(input, ScalarType::Float8E4M3); }
     [[nodiscard]] TensorRef quantize_e5m2(const TensorRef& input) const { return quantize_fp8(input, ScalarType::Float8E5M2); }
 
+    // A fixed set of projections run as one grouped launch per call (sdxlq_group_plan_*): built
+    // once, run many times. Projections that read the same input with the same quantisation share
+    // one quantised copy of it. Two uses at the reference's call sites (src/cuda/unet.cpp:98-149):
+    //   * to_q / to_k / to_v of a transformer block on the same `normalized` tensor;
+    //   * every cross-attention to_k / to_v of the UNet (140 projections) on the text encoder's
+    //     hidden states, which do not change between denoising steps: run the set once per
+    //     generation and keep its outputs for all steps, which takes the skinny K=2048 GEMMs out of
+    //     the step loop.
+    class ProjectionSet final {
+    public:
+        struct Entry {
+            TensorRef input, weight;
+            const TensorRef* bias = nullptr;
+            LinearActivation activation = LinearActivation::None;
+        };
+
+        ProjectionSet(const Ops& ops, const std::vector<Entry>& entries) : runtime_(ops.runtime_) {
+            std::vector<sdxlq_linear_desc> descs;
+            descs.reserve(entries.size());
+            for (const Entry& entry : entries) {
+                TensorRef output;
+                descs.push_back(ops.describe(entry.input, entry.weight, entry.bias, entry.activation, output));
+                outputs_.push_back(output);
+            }
+            runtime_->check(sdxlq_group_plan_create(runtime_->context(), descs.data(), descs.size(), &plan_));
+        }
+        ProjectionSet(const ProjectionSet&) = delete;
+        ProjectionSet& operator=(const ProjectionSet&) = delete;
+        ~ProjectionSet() { sdxlq_group_plan_destroy(plan_); }
+
+        // Enqueues the whole set on the runtime's stream; outputs()[i] belongs to entries[i].
+        void run() const { runtime_->check(sdxlq_group_plan_run(runtime_->context(), plan_)); }
+        [[nodiscard]] const std::vector<TensorRef>& outputs() const { return outputs_; }
+        [[nodiscard]] int launches() const { return sdxlq_group_plan_launches(plan_); }
+
+    private:
+        const Runtime* runtime_ = nullptr;
+        sdxlq_group_plan* plan_ = nullptr;
+        std::vector<TensorRef> outputs_;
+    };
+
 private:
     [[nodiscard]] TensorRef run(const TensorRef& input, const TensorRef& weight, const TensorRef* bias,
                                 LinearActivation activation) const {
+        TensorRef output;
+        const sdxlq_linear_desc desc = describe(input, weight, bias, activation, output);
+        runtime_->check(sdxlq_linear(runtime_->context(), &desc));
+        return output;
+    }
+
+    // Validates like Ops::linear, allocates the output and fills the C descriptor.
+    [[nodiscard]] sdxlq_linear_desc describe(const TensorRef& input, const TensorRef& weight, const TensorRef* bias,
+                                             LinearActivation activation, TensorRef& output) const {
         // The type / role / rank checks of Ops::linear, with its messages.
         if (weight.type == ScalarType::Int8) {
             if (input.type != ScalarType::Float16 || input.role != TensorRole::Model || input.rank() < 2 ||
@@ -184,7 +234,7 @@ private:
         }
         const std::size_t m = input.elements() / k;
 
-        TensorRef output;
+        output = TensorRef{};
         output.shape = input.shape;
         output.shape.back() = activation == LinearActivation::GEGLU ? n / 2 : n;
         output.type = ScalarType::Float16;
@@ -206,8 +256,7 @@ private:
         desc.bias = bias != nullptr ? bias->data : nullptr;
         desc.activation = static_cast<std::int32_t>(activation);
         desc.y = output.data;
-        runtime_->check(sdxlq_linear(runtime_->context(), &desc));
-        return output;
+        return desc;
     }
 
     const Runtime* runtime_ = nullptr;

@@ -62,7 +62,16 @@ def test_cxx_shim_compiles_against_the_header(tmp_path):
     """The C++20 shim that mirrors Ops::linear / linear_activation is header-only over the C ABI."""
     shim = os.path.join(ROOT, "sdxl-end2end_b200", "cpp")
     source = tmp_path / "shim.cpp"
-    source.write_text('#include "sdxlq_ops.hpp"\nint main() { return sdxlq::valid_convrot_group_size(64) ? 0 : 1; }\n')
+    source.write_text(
+        '#include "sdxlq_ops.hpp"\n'
+        '// instantiates the grouped projection set (no GPU work is launched: no context exists)\n'
+        'static void unused(const sdxlq::Ops& ops, const std::vector<sdxlq::Ops::ProjectionSet::Entry>& entries) {\n'
+        '    sdxlq::Ops::ProjectionSet set(ops, entries);\n'
+        '    set.run();\n'
+        '    (void)set.outputs();\n'
+        '    (void)set.launches();\n'
+        '}\n'
+        'int main() { (void)&unused; return sdxlq::valid_convrot_group_size(64) ? 0 : 1; }\n')
     lib_dir = os.path.join(ROOT, "sdxl-end2end_b200")
     subprocess.run(["g++", "-std=c++20", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"), "-I", shim,
                     str(source), "-L", lib_dir, "-lsdxlq", f"-Wl,-rpath,{lib_dir}", "-o", str(tmp_path / "shim")],

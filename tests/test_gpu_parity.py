@@ -502,3 +502,29 @@ def test_bounded_wait_reports_timeout_and_context_survives(gpu):
     y = ops.linear(dev(x), weight, None)
     ctx.check()
     assert np.array_equal(y.cpu().numpy().view(np.uint16), O.int8_convrot_linear(x, wq, ws, 0)["out"])
+
+
+# ------------------------------------------------------------------------------------------------
+# cross-attention K/V projections computed once per generation
+# ------------------------------------------------------------------------------------------------
+def test_cross_attention_kv_cache_matches_per_call_projections(gpu):
+    """The text-encoder hidden states [2*77, 2048] feed attn2.to_k / to_v of every block; the cache
+    runs all of them as one grouped launch (one shared quantisation per rotation setting) and must
+    return what the per-call operator returns, bit for bit, also after a refresh with a new prompt."""
+    pkg, ctx, ops = gpu
+    hidden = dev(H.make_activations(31, 154, 2048))
+    projections = []
+    for index, (n, group) in enumerate([(640, 256), (640, 256), (1280, 256), (1280, 256), (1280, 0)]):
+        weight, _, _ = int8_weight(pkg, n, 2048, group, 40 + index)
+        projections.append((f"block{index // 2}.attn2.{'to_k' if index % 2 == 0 else 'to_v'}", weight, None))
+    cache = pkg.CrossAttentionKVCache(ops, hidden, projections)
+    # one rotated and one unrotated quantisation of the hidden states, one GEMM launch
+    assert cache.launches == 3
+    for name, weight, bias in projections:
+        assert torch.equal(cache[name], ops.linear(hidden, weight, bias))
+    hidden.copy_(dev(H.make_activations(32, 154, 2048)))
+    cache.refresh()
+    ctx.check()
+    for name, weight, bias in projections:
+        assert torch.equal(cache[name], ops.linear(hidden, weight, bias))
+    cache.close()
