@@ -331,5 +331,21 @@ def ref_linear_threaded(x: np.ndarray, w: np.ndarray, bias: np.ndarray | None = 
     return out
 
 
+def ref_safetensors_probe(path: str, key: str, capacity: int = 64):
+    """(dtype value of the reference's DType enum, shape, byte count, leading bytes) of one tensor
+    as the reference's own safetensors parser sees it; raises when that parser rejects the file."""
+    library = ref_lib()
+    dtype, rank = ctypes.c_int(), ctypes.c_int()
+    shape = (ctypes.c_uint64 * 4)()
+    size = ctypes.c_uint64()
+    data = (ctypes.c_ubyte * capacity)()
+    status = library.ref_safetensors_probe(path.encode(), key.encode(), ctypes.byref(dtype), ctypes.byref(rank), shape,
+                                           ctypes.byref(size), data, ctypes.c_uint64(capacity))
+    if status != 0:
+        raise RuntimeError(f"the reference safetensors parser rejected {path}:{key} (status {status})")
+    count = min(int(size.value), capacity)
+    return int(dtype.value), [int(shape[d]) for d in range(rank.value)], int(size.value), bytes(data[:count])
+
+
 def ref_hardware_threads() -> int:
     return int(ref_lib().ref_hardware_threads())

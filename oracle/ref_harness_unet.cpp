@@ -14,6 +14,7 @@
 
 #include <cstdint>
 #include <cstring>
+#include <filesystem>
 
 namespace {
 
@@ -85,5 +86,27 @@ int ref_geglu(const float* input, std::uint64_t rows, std::uint64_t width2, floa
 }
 
 float ref_gelu(float x) { return sdxl::gelu(x); }
+
+// Opens a safetensors file with the reference's own parser (sdxl::SafeTensorFile,
+// src/safetensors.cpp) and reports one tensor: dtype as the reference's DType value, rank, shape
+// (up to 4 dimensions), byte count, and up to `capacity` leading bytes of its data. Returns 0 on
+// success, 1 when the reference threw (malformed file, missing key), 2 for a rank above 4.
+int ref_safetensors_probe(const char* path, const char* key, int* dtype, int* rank, std::uint64_t* shape,
+                          std::uint64_t* bytes, unsigned char* data, std::uint64_t capacity) {
+    try {
+        const sdxl::SafeTensorFile file{std::filesystem::path(path)};
+        const sdxl::TensorView view = file.tensor(key);
+        if (view.shape.size() > 4) return 2;
+        *dtype = static_cast<int>(view.dtype);
+        *rank = static_cast<int>(view.shape.size());
+        for (std::size_t d = 0; d < view.shape.size(); ++d) shape[d] = view.shape[d];
+        *bytes = view.logical_bytes();
+        const std::uint64_t count = *bytes < capacity ? *bytes : capacity;
+        std::memcpy(data, view.data, static_cast<std::size_t>(count));
+        return 0;
+    } catch (const std::exception&) {
+        return 1;
+    }
+}
 
 } // extern "C"

@@ -20,3 +20,4 @@ from .api import (  # noqa: F401
     library_path, load_library, valid_convrot_group_size,
 )
 from .build import build  # noqa: F401
+from . import packed_formats  # noqa: F401

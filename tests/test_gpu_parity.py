@@ -528,3 +528,30 @@ def test_cross_attention_kv_cache_matches_per_call_projections(gpu):
     for name, weight, bias in projections:
         assert torch.equal(cache[name], ops.linear(hidden, weight, bias))
     cache.close()
+
+
+# ------------------------------------------------------------------------------------------------
+# prequantised checkpoint -> device -> Linear
+# ------------------------------------------------------------------------------------------------
+def test_prequantised_int8_checkpoint_loads_and_runs(gpu, tmp_path):
+    """A checkpoint in the reference's prequantised layout (weight I8 + weight_scale + comfy_quant)
+    written and read by packed_formats goes through the prequantised branch of
+    upload_or_quantize_int8_weight and computes what the oracle computes from the same bytes."""
+    pkg, ctx, ops = gpu
+    pf = pkg.packed_formats
+    n, k, group = 320, 1280, 256
+    wq, ws = O.int8_quantize_rows(H.make_weight(51, n, k).astype(np.float32), group)
+    path = str(tmp_path / "unet_int8.safetensors")
+    pf.write_int8_checkpoint(path, {"unet.mid.attn1.to_out.0": pf.Int8LinearRecord(wq, ws.reshape(n, 1), True, True, group)})
+    record = pf.read_int8_checkpoint(path)["unet.mid.attn1.to_out.0"]
+    metadata = pkg.QuantizationMetadata(weight_scale=dev(record.weight_scale), convrot=record.convrot,
+                                        per_row=record.per_row, convrot_group_size=record.convrot_group_size)
+    weight = ops.upload_or_quantize_int8_weight(dev(record.weight), metadata,
+                                                pkg.INT8WeightLoadOptions(require_prequantized=True))
+    assert weight.convrot_group_size == group
+    x = H.make_activations(51, 77, k)
+    bias = H.make_bias(51, n)
+    y = ops.linear(dev(x), weight, dev(bias))
+    ctx.check()
+    want = O.int8_convrot_linear(x, wq, ws, group, bias.view(np.uint16), 0)["out"]
+    assert np.array_equal(y.cpu().numpy().view(np.uint16), want)
