@@ -148,6 +148,12 @@ INT8_CASES = [
     (300, 640, 640, 0, 2, True, 16),        # GELU
     (300, 640, 640, 0, 3, True, 256),       # QuickGELU
     (129, 72, 48, 16, 0, True, 0),          # ragged everything (N not a multiple of 16)
+    # the text encoders' projections (src/cuda/text_encoder.cpp:71-105): M = 2 x 77 tokens
+    (154, 768, 768, 256, 0, True, 0),       # CLIP-L self_attn q/k/v/out_proj
+    (154, 3072, 768, 256, 3, True, 0),      # CLIP-L mlp.fc1 + QuickGELU
+    (154, 768, 3072, 256, 0, True, 0),      # CLIP-L mlp.fc2
+    (154, 5120, 1280, 256, 2, True, 0),     # OpenCLIP bigG mlp.fc1 + GELU
+    (154, 1280, 5120, 256, 0, True, 0),     # OpenCLIP bigG mlp.fc2
 ]
 
 
