@@ -25,7 +25,7 @@
 
 namespace sdxlq {
 cudaError_t launch_umma_gemm(const GemmLaunchParams& params, uint32_t grid, size_t dynamic_smem,
-                             cudaStream_t stream, size_t* attribute_bytes, bool pair);
+                             cudaStream_t stream, size_t* attribute_bytes, bool pair, bool early_launch);
 size_t umma_gemm_control_bytes();
 cudaError_t launch_small_linear(const void* a, const void* b, const EpilogueParams& ep, uint32_t k_major,
                                 cudaStream_t stream);
@@ -74,11 +74,8 @@ struct sdxlq_context {
     long long wait_limit_cycles = 4000000000LL;
     int forced_tile_n = 0;
     EncodeTiledFn encode = nullptr;
-    // Side stream and events for running independent quantiser launches side by side (grouped
-    // plans with both unrotated and rotated inputs). Null in the static, allocation-free context.
-    cudaStream_t side_stream = nullptr;
-    cudaEvent_t fork_event = nullptr, join_event = nullptr;
-    bool concurrent_quantisers = true;
+    bool early_launch = true;                 // GEMM grids start while the quantiser before them drains (programmatic
+                                              // dependent launch); the kernel waits before reading what it wrote
     sdxlq_int8_stats stats{};
     std::string last_error = "";
     // Optional per-kernel timing: CUDA event pairs recorded around each launch on the stream.
@@ -363,21 +360,10 @@ int add_int8_job(sdxlq_context* ctx, Prepared& prep, const void* x, bool x_is_f3
 // Launches the INT8 activation quantisers of a prepared set: one launch per kernel flavour (and
 // per rotation group size). `tables` holds the device copies of the job tables, or nulls.
 int run_int8_quantisers(sdxlq_context* ctx, const Prepared& prep, QuantInt8Job* const tables[INT8_FLAVOURS]) {
-    // The unrotated and the rotated rows are independent launches with different limits (the first
-    // waits on memory latency at high occupancy, the second issues arithmetic at low occupancy):
-    // when a call has both, the unrotated one runs on the side stream beside the rotated one.
-    const bool fork = ctx->concurrent_quantisers && ctx->side_stream != nullptr && !ctx->profiling &&
-                      !prep.int8[INT8_PLAIN].jobs.empty() && !prep.int8[INT8_ROTATED].jobs.empty();
-    if (fork) {
-        if (cudaEventRecord(ctx->fork_event, ctx->stream) != cudaSuccess ||
-            cudaStreamWaitEvent(ctx->side_stream, ctx->fork_event, 0) != cudaSuccess) {
-            return fail_cuda(ctx, cudaGetLastError(), "side stream fork");
-        }
-    }
     for (int flavour = 0; flavour < INT8_FLAVOURS; ++flavour) {
         const Int8JobSet& set = prep.int8[flavour];
         if (set.jobs.empty()) continue;
-        cudaStream_t stream = (fork && flavour == INT8_PLAIN) ? ctx->side_stream : ctx->stream;
+        cudaStream_t stream = ctx->stream;
         QuantInt8Launch launch{};
         launch.jobs = tables != nullptr ? tables[flavour] : nullptr;
         launch.num_jobs = static_cast<uint32_t>(set.jobs.size());
@@ -400,12 +386,6 @@ int run_int8_quantisers(sdxlq_context* ctx, const Prepared& prep, QuantInt8Job* 
             }
         }
         if (error != cudaSuccess) return fail_cuda(ctx, error, "INT8 activation quantise launch");
-    }
-    if (fork) {
-        if (cudaEventRecord(ctx->join_event, ctx->side_stream) != cudaSuccess ||
-            cudaStreamWaitEvent(ctx->stream, ctx->join_event, 0) != cudaSuccess) {
-            return fail_cuda(ctx, cudaGetLastError(), "side stream join");
-        }
     }
     return SDXLQ_OK;
 }
@@ -657,7 +637,7 @@ int run_gemm_flavour(sdxlq_context* ctx, const Prepared& prep, int flavour, cons
     const uint32_t grid = pair ? 2 * std::min<uint32_t>(params.num_tiles, sms / 2) : std::min<uint32_t>(params.num_tiles, sms);
     LaunchTimer timer(ctx, SDXLQ_KERNEL_GEMM);
     const cudaError_t error = launch_umma_gemm(params, grid, geometry.dynamic_smem, ctx->stream,
-                                               ctx->umma_smem_attribute, pair);
+                                               ctx->umma_smem_attribute, pair, ctx->early_launch && !ctx->profiling);
     if (error != cudaSuccess) return fail_cuda(ctx, error, "tensor-core GEMM launch");
     return SDXLQ_OK;
 }
@@ -727,18 +707,7 @@ int sdxlq_context_create(int device, void* stream, size_t workspace_bytes, sdxlq
     if (const char* text = std::getenv("SDXLQ_PAIR")) ctx->pair_mode = std::atoi(text);
     if (const char* text = std::getenv("SDXLQ_GEGLU_TILE_N")) ctx->geglu_tile_n = std::atoi(text);
     if (const char* text = std::getenv("SDXLQ_DIAGNOSTIC_SKIP")) ctx->diagnostic_skip = static_cast<uint32_t>(std::atoi(text));
-    if (const char* text = std::getenv("SDXLQ_CONCURRENT_QUANTISERS")) ctx->concurrent_quantisers = std::atoi(text) != 0;
-    // Without the side stream the quantiser launches simply run one after the other.
-    if (cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaEventCreateWithFlags(&ctx->fork_event, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&ctx->join_event, cudaEventDisableTiming) != cudaSuccess) {
-        if (ctx->side_stream != nullptr) cudaStreamDestroy(ctx->side_stream);
-        if (ctx->fork_event != nullptr) cudaEventDestroy(ctx->fork_event);
-        if (ctx->join_event != nullptr) cudaEventDestroy(ctx->join_event);
-        ctx->side_stream = nullptr;
-        ctx->fork_event = ctx->join_event = nullptr;
-        (void)cudaGetLastError();
-    }
+    if (const char* text = std::getenv("SDXLQ_EARLY_LAUNCH")) ctx->early_launch = std::atoi(text) != 0;
     *out = ctx;
     return SDXLQ_OK;
 }
@@ -749,12 +718,6 @@ void sdxlq_context_destroy(sdxlq_context* ctx) {
     cudaStreamSynchronize(ctx->stream);
     for (auto& entry : ctx->timed) { cudaEventDestroy(entry.start); cudaEventDestroy(entry.stop); }
     for (auto& events : ctx->event_pool) { cudaEventDestroy(events.first); cudaEventDestroy(events.second); }
-    if (ctx->side_stream != nullptr) {
-        cudaStreamSynchronize(ctx->side_stream);
-        cudaStreamDestroy(ctx->side_stream);
-        cudaEventDestroy(ctx->fork_event);
-        cudaEventDestroy(ctx->join_event);
-    }
     cudaFree(ctx->workspace);
     cudaFree(ctx->control);
     delete ctx;

@@ -535,6 +535,11 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
     ptx::tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&control->tmem_base);
 
+    // Everything above touched only this CTA's own state. From here on the roles read what the
+    // kernels before this one wrote (quantised activations, their scales): wait for them to
+    // complete when this grid was launched early; no effect otherwise.
+    ptx::grid_dependency_wait();
+
     if (warp < kControlWarps) {
     ptx::setmaxnreg_dec<kControlRegisters>();
     if (warp == 0) {
@@ -795,7 +800,7 @@ size_t umma_gemm_control_bytes() { return (sizeof(Control) + 1023u + 1023u) / 10
 // context, the dynamic shared memory size each kernel flavour has been opted into. `grid` counts
 // CTAs (even for the CTA-pair flavour, which is launched as clusters of two).
 cudaError_t launch_umma_gemm(const GemmLaunchParams& params, uint32_t grid, size_t dynamic_smem,
-                             cudaStream_t stream, size_t* attribute_bytes, bool pair) {
+                             cudaStream_t stream, size_t* attribute_bytes, bool pair, bool early_launch) {
     auto kernel = pair ? sdxlq_umma_gemm_kernel<true> : sdxlq_umma_gemm_kernel<false>;
     if (dynamic_smem > attribute_bytes[pair ? 1 : 0]) {
         const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -808,15 +813,25 @@ cudaError_t launch_umma_gemm(const GemmLaunchParams& params, uint32_t grid, size
     config.blockDim = dim3(kThreads, 1, 1);
     config.dynamicSmemBytes = dynamic_smem;
     config.stream = stream;
-    cudaLaunchAttribute attribute{};
+    cudaLaunchAttribute attributes[2] = {};
+    unsigned count = 0;
     if (pair) {
-        attribute.id = cudaLaunchAttributeClusterDimension;
-        attribute.val.clusterDim.x = 2;
-        attribute.val.clusterDim.y = 1;
-        attribute.val.clusterDim.z = 1;
-        config.attrs = &attribute;
-        config.numAttrs = 1;
+        attributes[count].id = cudaLaunchAttributeClusterDimension;
+        attributes[count].val.clusterDim.x = 2;
+        attributes[count].val.clusterDim.y = 1;
+        attributes[count].val.clusterDim.z = 1;
+        ++count;
     }
+    if (early_launch) {
+        // Programmatic dependent launch: the grid may start (barrier set-up, tensor-memory
+        // allocation) while the kernel before it on the stream drains; the kernel itself waits
+        // (griddepcontrol.wait) before it reads anything that kernel wrote.
+        attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+    }
+    config.attrs = count != 0 ? attributes : nullptr;
+    config.numAttrs = count;
     return cudaLaunchKernelEx(&config, kernel, params);
 }
 

@@ -316,6 +316,13 @@ __device__ __forceinline__ void setmaxnreg_inc() {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Registers));
 }
 
+// Programmatic dependent launch. `grid_dependency_wait` blocks until the grids this one depends on
+// have completed and their memory is visible; `grid_launch_dependents` lets a dependent grid that
+// was launched with the programmatic attribute start being scheduled. Both do nothing in a grid
+// launched without such a dependency.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- CTA pairs (cta_group::2) ----------------------------------------------------------------
 // Two CTAs of a cluster work on one 256-row tile: each loads its 128 rows of A and half of the B
 // rows into its own shared memory, the even-ranked CTA (the leader) issues the MMAs, and each

@@ -218,6 +218,9 @@ __device__ __forceinline__ void rotate_quantize_rows(const QuantInt8Job& job, ui
 __global__ void __launch_bounds__(256, 2)
 rotate_quantize_int8_kernel(const __grid_constant__ QuantInt8Launch launch) {
     __shared__ uint32_t row_max_bits[64];
+    // a GEMM launched with the programmatic-dependency attribute may begin its set-up now; it
+    // waits for this kernel to complete before it reads the results
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const QuantInt8Job& job = find_job(launch, blockIdx.x);
     const uint32_t local_block = blockIdx.x - job.first_block;
     if (job.x_is_f32) rotate_quantize_rows<float>(job, local_block, row_max_bits);
@@ -310,6 +313,7 @@ fp8_amax_kernel(const __grid_constant__ QuantFp8Launch launch) {
 
 __global__ void __launch_bounds__(256)
 fp8_cast_kernel(const __grid_constant__ QuantFp8Launch launch) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // see rotate_quantize_int8_kernel
     const uint32_t job_index = find_job_index(launch, blockIdx.x);
     const QuantFp8Job& job = launch.jobs == nullptr ? launch.single : launch.jobs[job_index];
     const uint32_t local_block = blockIdx.x - job.first_block;

@@ -27,6 +27,10 @@ __device__ __forceinline__ const QuantInt8Job& find_job(const QuantInt8Launch& l
     return launch.jobs[lo];
 }
 
+// A GEMM launched with the programmatic-dependency attribute may start its set-up once every block
+// of this kernel has got here; it waits for this kernel's completion before it reads the results.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float scale_from_amax(float maximum) {
     return maximum > 0.0f ? fmaxf(__fdiv_rn(maximum, 127.0f), 1.0e-30f) : 1.0f;
 }
@@ -88,6 +92,7 @@ __device__ __forceinline__ float finite_max(const uint4 raw, float current) {
 template <int MaxVectors>
 __global__ void __launch_bounds__(256)
 plain_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
+    launch_dependents();
     const QuantInt8Job& job = find_job(launch, blockIdx.x);
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t row = (blockIdx.x - job.first_block) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -162,6 +167,7 @@ template <int Stages>
 __global__ void __launch_bounds__(256, 2)
 rotated_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
     __shared__ uint32_t row_max_bits[64];
+    launch_dependents();
     const QuantInt8Job& job = find_job(launch, blockIdx.x);
     if (job.stages != Stages || job.pad != 0) return;   // one launch per group size; pad = 1: rotated256_rows_kernel
     const uint32_t local_block = blockIdx.x - job.first_block;
@@ -339,6 +345,7 @@ __global__ void __launch_bounds__(256, 2)
 rotated256_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
     extern __shared__ __align__(16) uint8_t dynamic_smem[];
     __shared__ uint32_t row_max_bits[64];
+    launch_dependents();
     const QuantInt8Job& job = find_job(launch, blockIdx.x);
     if (job.stages != 4 || job.pad == 0) return;      // other group sizes / alignments: rotated_rows_kernel
     const uint32_t thread = threadIdx.x;
