@@ -9,7 +9,10 @@ the 640-dim transformer-block layer set under W8A8 INT8 ConvRot at 1024^2, CFG b
 ff.net.2 [8192,2560]x[640,2560]); the three attention projections share one quantised input.
 Other workloads: `layerset1280_fp8` (the 1280-dim set under FP8 E4M3 per-channel, plus the
 skinny cross-attention K/V GEMM), `unet743_int8` / `unet743_e5m2` (all 743 rank-2 projections of
-one UNet step as one grouped launch).
+one UNet step as one grouped launch), `crossattn_kv_int8` (the 140 cross-attention K/V projections
+a per-generation cache removes from every step), `unetstep_int8|e4m3|e5m2` (one denoising step's
+projections for this rank's share of 8 images x CFG 2: strong scaling over 1/2/4/8 ranks by
+sharding images, projections only).
 
 Rank 0 prints ONE JSON line. `value` is whole-job throughput (all ranks) with inputs resident in
 HBM, timed on the device with CUDA events, max over ranks. `e2e` is the same metric through the
@@ -88,6 +91,22 @@ def workload_rows(name: str):
                 if ".attn2.to_k" in p.name or ".attn2.to_v" in p.name]
         return rows, "int8", (f"the {len(rows)} cross-attention to_k/to_v projections [154,2048]x[640|1280,2048] of one SDXL UNet step, "
                               "INT8 ConvRot, one grouped launch (HBM-bound: weights are read once)")
+    if name.startswith("unetstep_"):
+        # unetstep_<int8|e4m3|e5m2>: every projection of one denoising step for this rank's share of a
+        # fixed job of 8 images x CFG 2 (UNet batch 16), images sharded over the ranks with replicated
+        # weights (UNet batch 16 / world per rank). Only the projections run: convolutions, norms and
+        # attention are not part of this path, so steps/s here bounds the UNet's from above.
+        kind = name.split("_", 1)[1]
+        if kind not in ("int8", "e4m3", "e5m2"):
+            raise SystemExit(f"unknown workload {name}")
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if 16 % world != 0 or 16 // world < 2:
+            raise SystemExit("unetstep shards 8 CFG pairs: 1, 2, 4 or 8 ranks")
+        local_batch = 16 // world
+        shapes = importlib.import_module("sdxl-end2end_b200.unet_shapes")
+        rows = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in shapes.unet_projections(local_batch)]
+        return rows, kind, (f"all 743 rank-2 projections of one SDXL UNet step at 1024^2 for {local_batch // 2} of 8 images x CFG 2 "
+                            f"(UNet batch {local_batch} of 16 on this rank), one grouped launch, {kind}; projections only")
     if name in ("unet743_int8", "unet743_e5m2"):
         shapes = importlib.import_module("sdxl-end2end_b200.unet_shapes")
         rows = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in shapes.unet_projections(2)]
@@ -344,7 +363,7 @@ def main():
     import torch.distributed as dist
 
     if args.steps is None:
-        args.steps = 2000 if args.workload.startswith("layerset") else 200
+        args.steps = 2000 if args.workload.startswith("layerset") else (20 if args.workload.startswith("unetstep_") else 200)
     if args.warmup is None:
         args.warmup = 20
     args.warmup = max(args.warmup, 3)
@@ -483,7 +502,8 @@ def main():
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if args.workload.startswith("unetstep_") else "weak", "vs_baseline": None,
             "dtype": {"int8": "int8", "e4m3": "fp8_e4m3", "e5m2": "fp8_e5m2"}.get(kind, "f16"), "data": "synthetic",
             "config": {"workload": description, "name": args.workload, "projections": len(rows),
                        "ops_per_step": ops_per_step, "parallelism": f"dp{world} (replicated weights, no collective)",
@@ -492,6 +512,7 @@ def main():
                              f"working set {work.working_set / 1e6:.0f} MB per step (> {L2_BYTES / 1e6:.0f} MB L2)",
                        "timing": "CUDA events on the launching stream, max over ranks"},
             "clocks": clocks,
+            **({"unet_steps_per_s_projections_only": 1e3 / (elapsed_ms / args.steps)} if args.workload.startswith("unetstep_") else {}),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": work.h2d_bytes, "d2h_bytes_per_step": work.d2h_bytes,
                     "steps": e2e_steps, "ms_per_step": e2e_seconds / e2e_steps * 1e3},
             "gpu_launches": work.launches_per_step() * args.steps,

@@ -561,3 +561,30 @@ def test_prequantised_int8_checkpoint_loads_and_runs(gpu, tmp_path):
     ctx.check()
     want = O.int8_convrot_linear(x, wq, ws, group, bias.view(np.uint16), 0)["out"]
     assert np.array_equal(y.cpu().numpy().view(np.uint16), want)
+
+
+# ------------------------------------------------------------------------------------------------
+# sharding images over ranks does not change any image's result
+# ------------------------------------------------------------------------------------------------
+def test_per_image_results_do_not_depend_on_the_shard(gpu):
+    """Ranks take whole images (rows of M). With per-token INT8 activation scales and per-row
+    accumulation, the rows a rank computes for its images are bit-identical to the same rows of the
+    full batch, so an 8-GPU job equals the 1-GPU job image by image. (FP8 activations use one
+    tensor-wide scale, so there the shards agree within the FP8 tolerance only.)"""
+    pkg, ctx, ops = gpu
+    tokens, images = 256, 4
+    x = H.make_activations(77, tokens * images, 1280)
+    weight, _, _ = int8_weight(pkg, 2560, 1280, 256, 77)
+    bias = dev(H.make_bias(77, 2560))
+    full = ops.linear_activation(dev(x), weight, bias, pkg.ACT_GEGLU)
+    for image in range(images):
+        rows = slice(image * tokens, (image + 1) * tokens)
+        shard = ops.linear_activation(dev(x[rows]), weight, bias, pkg.ACT_GEGLU)
+        assert torch.equal(shard, full[rows])
+    wq8, ws8 = O.fp8_quantize_weight(H.make_weight(78, 640, 1280).astype(np.float32), O.E4M3, True)
+    weight8 = pkg.Weight(dev(wq8), pkg.ScalarType.Float8E4M3, 640, 1280, dev(ws8), pkg.FP8ScaleMode.PerOutputChannel)
+    x8 = H.make_activations(78, tokens * images, 1280, outliers=False)
+    full8 = ops.linear(dev(x8), weight8).float().cpu().numpy()
+    half8 = ops.linear(dev(x8[: tokens * 2]), weight8).float().cpu().numpy()
+    ctx.check()
+    assert H.max_rel(half8, full8[: tokens * 2], 1e-2) <= 2e-2
