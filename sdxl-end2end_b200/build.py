@@ -36,6 +36,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIBRARY
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     command = [nvcc, *NVCC_FLAGS]
+    if os.environ.get("SDXLQ_BUILD_DIAGNOSTICS"):
+        # tuning build: SDXLQ_DIAGNOSTIC_SKIP can switch parts of the GEMM kernel off
+        command.append("-DSDXLQ_DIAGNOSTICS")
     if verbose:
         command += ["-Xptxas", "-v"]
     command += ["-o", LIBRARY] + [os.path.join(CSRC, s) for s in SOURCES]

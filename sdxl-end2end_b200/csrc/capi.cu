@@ -750,7 +750,9 @@ int sdxlq_context_create(int device, void* stream, size_t workspace_bytes, sdxlq
     if (const char* text = std::getenv("SDXLQ_TILE_N")) ctx->forced_tile_n = std::atoi(text);
     if (const char* text = std::getenv("SDXLQ_PAIR")) ctx->pair_mode = std::atoi(text);
     if (const char* text = std::getenv("SDXLQ_GEGLU_TILE_N")) ctx->geglu_tile_n = std::atoi(text);
+#ifdef SDXLQ_DIAGNOSTICS
     if (const char* text = std::getenv("SDXLQ_DIAGNOSTIC_SKIP")) ctx->diagnostic_skip = static_cast<uint32_t>(std::atoi(text));
+#endif
     if (const char* text = std::getenv("SDXLQ_EARLY_LAUNCH")) ctx->early_launch = std::atoi(text) != 0;
     if (const char* text = std::getenv("SDXLQ_QUANT_THREADS")) {
         const int threads = std::atoi(text);
@@ -827,7 +829,13 @@ int sdxlq_get_stats(const sdxlq_context* ctx, sdxlq_int8_stats* out) {
 
 int sdxlq_valid_convrot_group_size(size_t group_size) { return valid_group(group_size) ? 1 : 0; }
 
-const char* sdxlq_build_info(void) { return "sdxlq sm_100a tcgen05/TMA cta_group::1 128xN + cta_group::2 256xN"; }
+const char* sdxlq_build_info(void) {
+#ifdef SDXLQ_DIAGNOSTICS
+    return "sdxlq sm_100a tcgen05/TMA cta_group::1 128xN + cta_group::2 256xN (diagnostic switches built in)";
+#else
+    return "sdxlq sm_100a tcgen05/TMA cta_group::1 128xN + cta_group::2 256xN";
+#endif
+}
 
 size_t sdxlq_workspace_bytes(const sdxlq_linear_desc* descs, size_t count) {
     if (descs == nullptr) return 0;

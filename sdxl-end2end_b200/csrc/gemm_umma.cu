@@ -493,11 +493,18 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
     const uint32_t num_tiles = params.num_tiles;
     volatile uint32_t* abort_word = &control->abort;
     const long long limit = params.wait_limit_cycles;
+#ifndef SDXLQ_DIAGNOSTICS
+    // regular build: the tuning switches do not exist and the hot loops carry no tests for them
+    // (1.5 % of the kernel time); build with -DSDXLQ_DIAGNOSTICS to get them
+    constexpr bool skip_epilogue = false, skip_loads = false, skip_mma = false, one_mma_per_stage = false,
+                   a_loads_only = false;
+#else
     const bool skip_epilogue = (params.diagnostic_skip & 1u) != 0;
     const bool skip_loads = (params.diagnostic_skip & (2u | 4u)) != 0;
     const bool skip_mma = (params.diagnostic_skip & (2u | 8u)) != 0;
     const bool one_mma_per_stage = (params.diagnostic_skip & 32u) != 0;
     const bool a_loads_only = (params.diagnostic_skip & 64u) != 0;
+#endif
     const uint32_t cta_rank = kPair ? ptx::cluster_cta_rank() : 0u;
     const bool leader = cta_rank == 0;
     const uint32_t first_tile = kPair ? blockIdx.x >> 1 : blockIdx.x;
