@@ -865,7 +865,7 @@ int sdxlq_linear(sdxlq_context* ctx, const sdxlq_linear_desc* desc) {
     if (!prep.fp8_jobs.empty()) {
         const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, nullptr);
         LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8);
-        const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream);
+        const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream, ctx->early_launch && !ctx->profiling);
         if (error != cudaSuccess) return fail_cuda(ctx, error, "FP8 activation quantise launch");
     }
     for (int flavour = 0; flavour < 2; ++flavour) {
@@ -915,7 +915,7 @@ int sdxlq_group_plan_run(sdxlq_context* ctx, sdxlq_group_plan* plan) {
     if (!prep.fp8_jobs.empty()) {
         const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, plan->device_fp8_jobs);
         LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8);
-        const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream);
+        const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream, ctx->early_launch && !ctx->profiling);
         if (error != cudaSuccess) return fail_cuda(ctx, error, "grouped FP8 activation quantise launch");
     }
     for (int flavour = 0; flavour < 2; ++flavour) {
@@ -986,7 +986,7 @@ int sdxlq_quantize_act_fp8(sdxlq_context* ctx, const void* x_f16, uint64_t count
     add_fp8_job(prep, x_f16, count, fmt == SDXLQ_FP8_E4M3 ? 0 : 1, q, scale);
     const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, nullptr);
     LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8);
-    const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream);
+    const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream, ctx->early_launch && !ctx->profiling);
     if (error != cudaSuccess) return fail_cuda(ctx, error, "FP8 activation quantise launch");
     return SDXLQ_OK;
 }

@@ -268,6 +268,7 @@ __device__ __forceinline__ uint8_t encode_fp8(float value, uint32_t fmt) {
 
 __global__ void __launch_bounds__(256)
 fp8_amax_kernel(const __grid_constant__ QuantFp8Launch launch) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // lets the cast kernel be scheduled early
     const uint32_t job_index = find_job_index(launch, blockIdx.x);
     const QuantFp8Job& job = launch.jobs == nullptr ? launch.single : launch.jobs[job_index];
     const uint32_t local_block = blockIdx.x - job.first_block;
@@ -314,6 +315,7 @@ fp8_amax_kernel(const __grid_constant__ QuantFp8Launch launch) {
 __global__ void __launch_bounds__(256)
 fp8_cast_kernel(const __grid_constant__ QuantFp8Launch launch) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // see rotate_quantize_int8_kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");                   // the maxima of fp8_amax_kernel are complete
     const uint32_t job_index = find_job_index(launch, blockIdx.x);
     const QuantFp8Job& job = launch.jobs == nullptr ? launch.single : launch.jobs[job_index];
     const uint32_t local_block = blockIdx.x - job.first_block;
@@ -357,12 +359,23 @@ fp8_cast_kernel(const __grid_constant__ QuantFp8Launch launch) {
     }
 }
 
-cudaError_t launch_fp8_quantize(const QuantFp8Launch& launch, uint32_t blocks, cudaStream_t stream) {
+cudaError_t launch_fp8_quantize(const QuantFp8Launch& launch, uint32_t blocks, cudaStream_t stream, bool early_launch) {
     fp8_amax_kernel<<<blocks, 256, 0, stream>>>(launch);
     cudaError_t status = cudaGetLastError();
     if (status != cudaSuccess) return status;
-    fp8_cast_kernel<<<blocks, 256, 0, stream>>>(launch);
-    return cudaGetLastError();
+    // The cast kernel needs the maxima of the kernel above. Launched with the programmatic-dependency
+    // attribute it is scheduled while that kernel drains and waits (griddepcontrol.wait) before it
+    // reads them; without the attribute the wait does nothing and the stream orders the two.
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(blocks, 1, 1);
+    config.blockDim = dim3(256, 1, 1);
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = early_launch ? &attribute : nullptr;
+    config.numAttrs = early_launch ? 1 : 0;
+    return cudaLaunchKernelEx(&config, fp8_cast_kernel, launch);
 }
 
 // ------------------------------------------------------------------------------------------

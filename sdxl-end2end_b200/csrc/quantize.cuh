@@ -53,7 +53,7 @@ struct QuantFp8Launch {
 
 cudaError_t launch_rotate_quantize_int8(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
                                         cudaStream_t stream);
-cudaError_t launch_fp8_quantize(const QuantFp8Launch& launch, uint32_t blocks, cudaStream_t stream);
+cudaError_t launch_fp8_quantize(const QuantFp8Launch& launch, uint32_t blocks, cudaStream_t stream, bool early_launch);
 cudaError_t launch_fp8_weight_pack(const void* source, int32_t dtype, uint32_t n, uint32_t k, uint32_t fmt,
                                    uint32_t per_channel, uint32_t k_major, uint8_t* destination,
                                    float* scales, cudaStream_t stream);
