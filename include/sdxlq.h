@@ -97,6 +97,12 @@ typedef struct sdxlq_linear_desc {
     const float* xq_scales;
     /* Optional: the raw INT32 accumulators [M,N] of the INT8 path (parity checks). */
     int32_t* acc_out;
+    /* Optional FP16 [M,N] tensor added to the biased projection in FP16, y = __hadd(linear, residual):
+     * the Ops::add_in_place that follows to_out, ff.net.2 and proj_out in the reference's transformer
+     * block (src/cuda/unet.cpp:118, 132, 147, 179; add_in_place_kernel, src/cuda/ops_kernels.cu:60-64)
+     * folded into the epilogue. May alias y (the hidden state updated in place). Requires
+     * activation == NONE. */
+    const void* residual;
 } sdxlq_linear_desc;
 
 /* sdxl::cuda::INT8ExecutionStats (runtime.hpp:106-112). Every INT8 Linear here runs on the
@@ -140,11 +146,18 @@ int sdxlq_linear(sdxlq_context* ctx, const sdxlq_linear_desc* desc);
 /* All `count` independent projections in one grouped launch per kernel kind (one activation-
  * quantise launch, one GEMM launch). Projections that read the same x with the same
  * quantisation share one quantised copy. No counterpart in the reference, which issues the
- * 743 projections of a UNet step one by one (src/cuda/unet.cpp:20-181). */
+ * 743 projections of a UNet step one by one (src/cuda/unet.cpp:20-181).
+ * Up to four projections that share one input per quantiser kind (the to_q/to_k/to_v of an
+ * attention layer) travel in the kernel parameters: no table, no allocation, capturable. Larger
+ * groups upload their tables through a pinned staging buffer and a stream-ordered allocation
+ * (cudaMallocAsync / cudaFreeAsync on the context's stream): the call does not wait for the GPU,
+ * but it cannot be recorded by a stream capture (build a plan for that). */
 int sdxlq_linear_grouped(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count);
 
 /* The same grouped launch split into build-once / run-many (descriptor tables stay on the
- * device). Pointers inside the descriptors must stay valid for the plan's lifetime. */
+ * device). Pointers inside the descriptors must stay valid for the plan's lifetime. Creation
+ * allocates with cudaMalloc and copies synchronously; running never allocates or synchronises.
+ * A plan runs only on the context that created it (its tables address that context's workspace). */
 int sdxlq_group_plan_create(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count,
                             sdxlq_group_plan** out);
 int sdxlq_group_plan_run(sdxlq_context* ctx, sdxlq_group_plan* plan);

@@ -27,10 +27,16 @@ _c_size = ctypes.c_size_t
 _p = ctypes.c_void_p
 
 
+def reference_root() -> str:
+    """Where the reference project's sources lie: $SDXL_REFERENCE_ROOT, else a `reference` directory
+    beside this repository."""
+    return os.environ.get("SDXL_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
 def build(ref_root: str | None = None) -> None:
     """Compile the oracle; also the reference checker when the reference tree is present."""
     subprocess.run(["make", "-C", _HERE, "oracle"], check=True, capture_output=True)
-    ref_root = ref_root or "/root/reference"
+    ref_root = ref_root or reference_root()
     if os.path.isdir(os.path.join(ref_root, "src")):
         subprocess.run(["make", "-C", _HERE, "ref", f"REF={ref_root}"], check=True, capture_output=True)
 
@@ -349,3 +355,96 @@ def ref_safetensors_probe(path: str, key: str, capacity: int = 64):
 
 def ref_hardware_threads() -> int:
     return int(ref_lib().ref_hardware_threads())
+
+
+# ---------------------------------------------------------------------------------------
+# The reference's parameter graph, CPU UNet executor and sigma schedule (oracle/_ref).
+# ---------------------------------------------------------------------------------------
+class RefUNet:
+    """sdxl::SDXLModel + sdxl::SDXLUNet of the reference (src/sdxl.cpp:84-238, src/unet.cpp:699-807)
+    behind the checker library. `config` = (channels[3], heads[3], transformer_depth[3],
+    cross_attention_dim, time_embed_dim, addition_time_embed_dim, addition_input_dim,
+    layers_per_block, norm_groups) or None for SDXL Base 1.0."""
+
+    def __init__(self, config=None):
+        library = ref_lib()
+        library.ref_unet_create.restype = ctypes.c_void_p
+        library.ref_unet_create.argtypes = [ctypes.c_void_p]
+        library.ref_unet_destroy.argtypes = [ctypes.c_void_p]
+        library.ref_unet_parameter_count.restype = ctypes.c_uint64
+        library.ref_unet_parameter_count.argtypes = [ctypes.c_void_p]
+        library.ref_unet_parameter.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_char_p, ctypes.c_uint64,
+                                               ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_uint64)]
+        library.ref_unet_bind_f32.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_uint64]
+        library.ref_unet_forward.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64,
+                                             ctypes.c_uint64, ctypes.c_float, ctypes.c_void_p, ctypes.c_uint64,
+                                             ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_void_p,
+                                             ctypes.c_char_p, ctypes.c_uint64]
+        self._library = library
+        packed = None
+        if config is not None:
+            flat = [int(v) for group in config for v in (group if isinstance(group, (tuple, list)) else (group,))]
+            assert len(flat) == 15
+            packed = (ctypes.c_uint64 * 15)(*flat)
+        self._handle = library.ref_unet_create(packed)
+        if not self._handle:
+            raise RuntimeError("the reference rejected the UNet configuration")
+        self._bound = {}
+
+    def close(self):
+        if self._handle:
+            self._library.ref_unet_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def parameters(self) -> dict:
+        """name (without the `unet.` prefix) -> expected shape, for every UNet parameter of the graph."""
+        out = {}
+        name = ctypes.create_string_buffer(256)
+        rank = ctypes.c_int()
+        shape = (ctypes.c_uint64 * 4)()
+        for index in range(int(self._library.ref_unet_parameter_count(self._handle))):
+            status = self._library.ref_unet_parameter(self._handle, index, name, 256, ctypes.byref(rank), shape)
+            if status != 0:
+                raise RuntimeError(f"ref_unet_parameter({index}) failed with {status}")
+            out[name.value.decode()[len("unet."):]] = tuple(int(shape[d]) for d in range(rank.value))
+        return out
+
+    def bind(self, parameters: dict) -> None:
+        """Binds FP32 arrays by name (without prefix); the arrays are kept alive by this object."""
+        for name, values in parameters.items():
+            array = np.ascontiguousarray(values, dtype=np.float32)
+            status = self._library.ref_unet_bind_f32(self._handle, f"unet.{name}".encode(), _ptr(array), array.size)
+            if status != 0:
+                raise RuntimeError(f"binding {name} failed with {status}")
+            self._bound[name] = array
+
+    def forward(self, latents, timestep, context, pooled, time_ids) -> np.ndarray:
+        latents = _c(latents, np.float32)
+        context = _c(context, np.float32)
+        pooled = _c(pooled, np.float32)
+        time_ids = _c(time_ids, np.float32)
+        batch, _, height, width = latents.shape
+        out = np.empty_like(latents)
+        error = ctypes.create_string_buffer(512)
+        status = self._library.ref_unet_forward(self._handle, _ptr(latents), batch, height, width, float(timestep),
+                                                _ptr(context), context.shape[1], _ptr(pooled), pooled.shape[1],
+                                                _ptr(time_ids), _ptr(out), error, 512)
+        if status != 0:
+            raise RuntimeError(f"reference SDXLUNet::forward threw: {error.value.decode()}")
+        return out
+
+
+def ref_normal_sigma_schedule(steps: int):
+    """(timesteps[steps], sigmas[steps + 1]) of SigmaSchedule(steps, Normal), src/scheduler.cpp:601-668."""
+    timesteps = np.empty(steps, np.float32)
+    sigmas = np.empty(steps + 1, np.float32)
+    status = ref_lib().ref_normal_sigma_schedule(ctypes.c_uint64(steps), _ptr(timesteps), _ptr(sigmas))
+    if status != 0:
+        raise RuntimeError("the reference sigma schedule threw")
+    return timesteps, sigmas

@@ -21,3 +21,5 @@ from .api import (  # noqa: F401
 )
 from .build import build  # noqa: F401
 from . import packed_formats  # noqa: F401
+from . import unet_harness  # noqa: F401
+from .unet_harness import EulerDenoiser, UNetConfig, UNetHarness  # noqa: F401

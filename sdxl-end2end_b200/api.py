@@ -88,6 +88,7 @@ class _CLinearDesc(ctypes.Structure):
         ("xq", ctypes.c_void_p),
         ("xq_scales", ctypes.c_void_p),
         ("acc_out", ctypes.c_void_p),
+        ("residual", ctypes.c_void_p),
     ]
 
 
@@ -264,6 +265,7 @@ class LinearCall:
     xq: Optional[torch.Tensor] = None
     xq_scales: Optional[torch.Tensor] = None
     acc_out: Optional[torch.Tensor] = None
+    residual: Optional[torch.Tensor] = None
     keep: list = field(default_factory=list)
 
 
@@ -378,14 +380,23 @@ class Ops:
             call.y = torch.empty(lead + (n_out,), dtype=torch.float16, device=device)
             if self.poison_outputs:
                 call.y.fill_(float("nan"))
+        if call.residual is not None:
+            if call.residual.dtype != torch.float16 or not call.residual.is_contiguous() or \
+                    call.residual.numel() != m * n_out:
+                raise CudaError("CUDA add requires matching FP16 tensors")
         return _CLinearDesc(_ptr(x), m, weight.c_struct(), _ptr(call.bias), int(call.activation), 0,
-                            _ptr(call.y), _ptr(call.xq), _ptr(call.xq_scales), _ptr(call.acc_out))
+                            _ptr(call.y), _ptr(call.xq), _ptr(call.xq_scales), _ptr(call.acc_out),
+                            _ptr(call.residual))
 
     # -- Ops::linear / Ops::linear_activation ----------------------------------------------------
     def linear(self, input: torch.Tensor, weight: Weight, bias: Optional[torch.Tensor] = None, *,
                xq: Optional[torch.Tensor] = None, xq_scales: Optional[torch.Tensor] = None,
-               acc_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        call = LinearCall(input, weight, bias, ACT_NONE, out, xq, xq_scales, acc_out)
+               acc_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+               residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`residual` folds the Ops::add_in_place that follows the projection in the reference's
+        transformer block (src/cuda/unet.cpp:118, 132, 147) into the epilogue; pass out=residual to
+        update the hidden state in place."""
+        call = LinearCall(input, weight, bias, ACT_NONE, out, xq, xq_scales, acc_out, residual)
         desc = self._desc(call)
         self.ctx.raise_for(self._lib.sdxlq_linear(self.ctx.handle, ctypes.byref(desc)))
         return call.y

@@ -25,7 +25,7 @@
 
 namespace sdxlq {
 cudaError_t launch_umma_gemm(const GemmLaunchParams& params, uint32_t grid, size_t dynamic_smem,
-                             cudaStream_t stream, size_t* attribute_bytes, bool pair, bool early_launch);
+                             cudaStream_t stream, int device, bool pair, bool early_launch);
 size_t umma_gemm_control_bytes();
 cudaError_t launch_small_linear(const void* a, const void* b, const EpilogueParams& ep, uint32_t k_major,
                                 cudaStream_t stream);
@@ -60,11 +60,12 @@ struct sdxlq_context {
     cudaStream_t stream = nullptr;
     uint8_t* workspace = nullptr;
     size_t workspace_bytes = 0;
-    uint32_t* control = nullptr;           // [0] error word, then 2 x kMaxFp8Jobs amax words
-    uint32_t fp8_parity = 0;
-    uint32_t fp8_dirty[2] = {0, 0};        // amax words of each parity left non-zero
+    uint32_t* control = nullptr;           // [0] error word; from word 64: kMaxFp8Jobs amax words, then kMaxFp8Jobs
+                                           // reader counters of the FP8 quantiser (all zero between calls)
     int sm_count = 148;
-    size_t umma_smem_attribute[2] = {0, 0};   // per kernel flavour: single CTA, CTA pair
+    uint8_t* staging = nullptr;            // pinned host image of the tables of a one-shot grouped call
+    size_t staging_bytes = 0;
+    cudaEvent_t staging_event = nullptr;   // completion of the last upload from `staging`
     int geglu_tile_n = 0;                     // tuning: accumulator tile width of GEGLU projections in grouped launches
                                               // (0: cost model). 128 lets the MMA issuer run three tiles ahead of the
                                               // GEGLU epilogues but measured slower (operand traffic, per-tile costs).
@@ -164,6 +165,9 @@ int validate(sdxlq_context* ctx, const sdxlq_linear_desc& d) {
     if (d.activation == SDXLQ_ACT_GEGLU && w.n % 2 != 0) {
         return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "fused linear bias GEGLU requires matching even-width FP16 tensors");
     }
+    if (d.residual != nullptr && d.activation != SDXLQ_ACT_NONE) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "linear: a residual is added to un-activated projections only");
+    }
     if (w.dtype == SDXLQ_INT8) {
         if (w.scales == nullptr || w.scale_mode != SDXLQ_SCALE_PER_OUTPUT_CHANNEL) {
             return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "native INT8 linear received incompatible tensors");
@@ -210,12 +214,13 @@ struct TileChoice {
     bool pair;
 };
 
-TileChoice choose_tile(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool geglu, bool grouped) {
+TileChoice choose_tile(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool geglu, bool grouped, uint32_t siblings = 1) {
     const uint32_t step = geglu ? 32 : 16;
     const uint32_t tiles_m = (m + kTileM - 1) / kTileM;
     const uint32_t sms = static_cast<uint32_t>(ctx->sm_count);
     const uint32_t columns = geglu ? n / 2 : n;            // GEGLU: a tile holds t/2 value + t/2 gate columns
-    const uint64_t tiles_at_widest = static_cast<uint64_t>(tiles_m) * ((columns + (geglu ? 127 : 255)) / (geglu ? 128 : 256));
+    // `siblings`: problems of (about) this shape that share the launch (a small inline group)
+    const uint64_t tiles_at_widest = static_cast<uint64_t>(siblings) * tiles_m * ((columns + (geglu ? 127 : 255)) / (geglu ? 128 : 256));
     const bool traffic_bound = grouped ? tiles_m >= 2 : tiles_at_widest >= 3ull * sms;
     // CTA pairs serve grouped launches only: with a single problem in the kernel parameters the pair
     // flavour mis-scales part of its FP16 output (accumulators are right), so it is not offered there.
@@ -241,7 +246,7 @@ TileChoice choose_tile(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool ge
             if (traffic_bound || pair) {
                 cost = static_cast<double>(tiles_n) * (128.0 + (pair ? tile_n / 2.0 : tile_n));
             } else {
-                const uint64_t tiles = static_cast<uint64_t>(tiles_m) * tiles_n;
+                const uint64_t tiles = static_cast<uint64_t>(siblings) * tiles_m * tiles_n;
                 const uint64_t waves = (tiles + sms - 1) / sms;
                 cost = static_cast<double>(waves) * (tile_n + 32.0);
             }
@@ -515,6 +520,7 @@ int prepare(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count, bo
         ep.a_scales = a_scales;
         ep.w_scales = w.scales;
         ep.bias = static_cast<const __half*>(d.bias);
+        ep.residual = static_cast<const __half*>(d.residual);
         ep.m = static_cast<uint32_t>(d.m);
         ep.n = static_cast<uint32_t>(w.n);
         ep.k = static_cast<uint32_t>(w.k);
@@ -541,7 +547,7 @@ int prepare(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count, bo
 
         GemmProblem problem{};
         problem.ep = ep;
-        const TileChoice choice = choose_tile(ctx, ep.m, ep.n, geglu, grouped);
+        const TileChoice choice = choose_tile(ctx, ep.m, ep.n, geglu, grouped, grouped ? 1u : static_cast<uint32_t>(count));
         const int flavour = choice.pair ? 1 : 0;
         const uint32_t rows_per_tile = choice.pair ? 2 * kTileM : kTileM;
         problem.tile_n = choice.tile_n;
@@ -640,26 +646,21 @@ GemmGeometry gemm_geometry(uint32_t max_cta_b_rows) {
     return g;
 }
 
-// Picks the amax scratch words of this call's parity and returns the launch header. The words
-// of one parity are all zero when a call starts: the cast kernel of the following call (other
-// parity) clears them again.
+// The launch header of the FP8 activation quantiser: one amax word and one reader counter per job,
+// both zero when a call starts (the cast kernel puts them back, see fp8_cast_kernel).
 QuantFp8Launch bind_fp8(sdxlq_context* ctx, const std::vector<QuantFp8Job>& jobs, const QuantFp8Job* device_jobs) {
-    const uint32_t parity = ctx->fp8_parity;
     QuantFp8Launch launch{};
-    launch.amax_bits = ctx->control + 64 + parity * kMaxFp8Jobs;
+    launch.amax_bits = ctx->control + 64;
+    launch.done_counts = ctx->control + 64 + kMaxFp8Jobs;
     launch.jobs = device_jobs;
     launch.num_jobs = static_cast<uint32_t>(jobs.size());
-    launch.clear_bits = ctx->control + 64 + (parity ^ 1u) * kMaxFp8Jobs;
-    launch.clear_count = ctx->fp8_dirty[parity ^ 1u];
     if (!jobs.empty()) launch.single = jobs[0];
-    ctx->fp8_dirty[parity ^ 1u] = 0;
-    ctx->fp8_dirty[parity] = static_cast<uint32_t>(jobs.size());
-    ctx->fp8_parity = parity ^ 1u;
     return launch;
 }
 
 // Launches the tensor-core GEMM of one kernel flavour: `problems` / `tiles` are the device tables
-// of a grouped plan, or null for a single problem passed in the kernel parameters.
+// of a grouped plan, or null when the (at most kInlineProblems) problems travel in the kernel
+// parameters.
 int run_gemm_flavour(sdxlq_context* ctx, const Prepared& prep, int flavour, const GemmProblem* problems,
                      const TileRef* tiles) {
     if (prep.problems[flavour].empty()) return SDXLQ_OK;
@@ -668,9 +669,21 @@ int run_gemm_flavour(sdxlq_context* ctx, const Prepared& prep, int flavour, cons
     GemmLaunchParams params{};
     params.problems = problems;
     params.tiles = tiles;
-    params.single = prep.problems[flavour][0];
-    params.num_tiles = problems != nullptr ? static_cast<uint32_t>(prep.tiles[flavour].size())
-                                           : params.single.tiles_m * params.single.tiles_n;
+    if (problems != nullptr) {
+        params.num_tiles = static_cast<uint32_t>(prep.tiles[flavour].size());
+    } else {
+        const size_t count = prep.problems[flavour].size();
+        if (count > kInlineProblems) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "internal: problem table missing");
+        uint32_t tiles_so_far = 0;
+        for (size_t i = 0; i < count; ++i) {
+            params.inline_problems[i] = prep.problems[flavour][i];
+            params.inline_tile_start[i] = tiles_so_far;
+            tiles_so_far += params.inline_problems[i].tiles_m * params.inline_problems[i].tiles_n;
+        }
+        for (size_t i = count; i <= kInlineProblems; ++i) params.inline_tile_start[i] = tiles_so_far;
+        params.inline_count = static_cast<uint32_t>(count);
+        params.num_tiles = tiles_so_far;
+    }
     params.num_stages = geometry.num_stages;
     params.stage_bytes = geometry.stage_bytes;
     params.b_offset = kTileM * kTileKBytes;
@@ -680,8 +693,8 @@ int run_gemm_flavour(sdxlq_context* ctx, const Prepared& prep, int flavour, cons
     const uint32_t sms = static_cast<uint32_t>(ctx->sm_count);
     const uint32_t grid = pair ? 2 * std::min<uint32_t>(params.num_tiles, sms / 2) : std::min<uint32_t>(params.num_tiles, sms);
     LaunchTimer timer(ctx, SDXLQ_KERNEL_GEMM);
-    const cudaError_t error = launch_umma_gemm(params, grid, geometry.dynamic_smem, ctx->stream,
-                                               ctx->umma_smem_attribute, pair, ctx->early_launch && !ctx->profiling);
+    const cudaError_t error = launch_umma_gemm(params, grid, geometry.dynamic_smem, ctx->stream, ctx->device, pair,
+                                               ctx->early_launch && !ctx->profiling);
     if (error != cudaSuccess) return fail_cuda(ctx, error, "tensor-core GEMM launch");
     return SDXLQ_OK;
 }
@@ -705,12 +718,87 @@ void count_stats(sdxlq_context* ctx, const Prepared& prep) {
 
 struct sdxlq_group_plan {
     Prepared prep;
+    uint8_t* slab = nullptr;                 // one device allocation holding every table below
     GemmProblem* device_problems[2] = {nullptr, nullptr};
     TileRef* device_tiles[2] = {nullptr, nullptr};
     QuantInt8Job* device_int8_jobs[INT8_FLAVOURS] = {nullptr, nullptr, nullptr};
     QuantFp8Job* device_fp8_jobs = nullptr;
     int device = 0;
+    const sdxlq_context* owner = nullptr;    // the tables hold addresses inside this context's workspace
 };
+
+namespace {
+
+// Device tables of a prepared set, laid out back to back in one slab (128-byte aligned sections;
+// tensor maps need 64).
+struct TableLayout {
+    size_t problems[2], tiles[2], int8_jobs[INT8_FLAVOURS], fp8_jobs, total;
+};
+
+TableLayout layout_tables(const Prepared& prep) {
+    TableLayout layout{};
+    size_t offset = 0;
+    auto place = [&](size_t bytes) { const size_t at = offset; offset = align_up(offset + bytes, 128); return at; };
+    for (int f = 0; f < 2; ++f) layout.problems[f] = place(prep.problems[f].size() * sizeof(GemmProblem));
+    for (int f = 0; f < 2; ++f) layout.tiles[f] = place(prep.tiles[f].size() * sizeof(TileRef));
+    for (int f = 0; f < INT8_FLAVOURS; ++f) layout.int8_jobs[f] = place(prep.int8[f].jobs.size() * sizeof(QuantInt8Job));
+    layout.fp8_jobs = place(prep.fp8_jobs.size() * sizeof(QuantFp8Job));
+    layout.total = std::max<size_t>(offset, 128);
+    return layout;
+}
+
+void fill_tables(const Prepared& prep, const TableLayout& layout, uint8_t* image) {
+    auto copy = [&](size_t at, const auto& host) {
+        if (!host.empty()) std::memcpy(image + at, host.data(), host.size() * sizeof(host[0]));
+    };
+    for (int f = 0; f < 2; ++f) { copy(layout.problems[f], prep.problems[f]); copy(layout.tiles[f], prep.tiles[f]); }
+    for (int f = 0; f < INT8_FLAVOURS; ++f) copy(layout.int8_jobs[f], prep.int8[f].jobs);
+    copy(layout.fp8_jobs, prep.fp8_jobs);
+}
+
+void bind_tables(sdxlq_group_plan* plan, const TableLayout& layout, uint8_t* slab) {
+    const Prepared& prep = plan->prep;
+    plan->slab = slab;
+    for (int f = 0; f < 2; ++f) {
+        plan->device_problems[f] = prep.problems[f].empty() ? nullptr : reinterpret_cast<GemmProblem*>(slab + layout.problems[f]);
+        plan->device_tiles[f] = prep.tiles[f].empty() ? nullptr : reinterpret_cast<TileRef*>(slab + layout.tiles[f]);
+    }
+    for (int f = 0; f < INT8_FLAVOURS; ++f) {
+        plan->device_int8_jobs[f] = prep.int8[f].jobs.empty() ? nullptr : reinterpret_cast<QuantInt8Job*>(slab + layout.int8_jobs[f]);
+    }
+    plan->device_fp8_jobs = prep.fp8_jobs.empty() ? nullptr : reinterpret_cast<QuantFp8Job*>(slab + layout.fp8_jobs);
+}
+
+// Quantisers, GEMM flavours and small-shape kernels of a prepared set, in stream order.
+int run_prepared(sdxlq_context* ctx, const Prepared& prep, const sdxlq_group_plan* tables) {
+    int status = run_int8_quantisers(ctx, prep, tables != nullptr ? tables->device_int8_jobs : nullptr);
+    if (status != SDXLQ_OK) return status;
+    if (!prep.fp8_jobs.empty()) {
+        const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, tables != nullptr ? tables->device_fp8_jobs : nullptr);
+        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8);
+        const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream, ctx->early_launch && !ctx->profiling);
+        if (error != cudaSuccess) return fail_cuda(ctx, error, "FP8 activation quantise launch");
+    }
+    for (int flavour = 0; flavour < 2; ++flavour) {
+        status = run_gemm_flavour(ctx, prep, flavour, tables != nullptr ? tables->device_problems[flavour] : nullptr,
+                                  tables != nullptr ? tables->device_tiles[flavour] : nullptr);
+        if (status != SDXLQ_OK) return status;
+    }
+    status = run_small(ctx, prep);
+    if (status != SDXLQ_OK) return status;
+    count_stats(ctx, prep);
+    return SDXLQ_OK;
+}
+
+// True when every kernel of the prepared set can take its operands from the kernel parameters: at
+// most kInlineProblems GEMM problems on single CTAs and one quantiser job per kernel flavour.
+bool fits_inline(const Prepared& prep) {
+    if (!prep.problems[1].empty() || prep.problems[0].size() > kInlineProblems) return false;
+    for (int f = 0; f < INT8_FLAVOURS; ++f) if (prep.int8[f].jobs.size() > 1) return false;
+    return prep.fp8_jobs.size() <= 1;
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -743,6 +831,12 @@ int sdxlq_context_create(int device, void* stream, size_t workspace_bytes, sdxlq
         delete ctx;
         return SDXLQ_ERR_CUDA;
     }
+    if (cudaEventCreateWithFlags(&ctx->staging_event, cudaEventDisableTiming) != cudaSuccess) {
+        cudaFree(ctx->workspace);
+        cudaFree(ctx->control);
+        delete ctx;
+        return SDXLQ_ERR_CUDA;
+    }
     if (const char* text = std::getenv("SDXLQ_WAIT_LIMIT_CYCLES")) {
         const long long parsed = std::atoll(text);
         if (parsed > 0) ctx->wait_limit_cycles = parsed;
@@ -768,6 +862,8 @@ void sdxlq_context_destroy(sdxlq_context* ctx) {
     cudaStreamSynchronize(ctx->stream);
     for (auto& entry : ctx->timed) { cudaEventDestroy(entry.start); cudaEventDestroy(entry.stop); }
     for (auto& events : ctx->event_pool) { cudaEventDestroy(events.first); cudaEventDestroy(events.second); }
+    if (ctx->staging_event != nullptr) cudaEventDestroy(ctx->staging_event);
+    cudaFreeHost(ctx->staging);
     cudaFree(ctx->workspace);
     cudaFree(ctx->control);
     delete ctx;
@@ -858,24 +954,9 @@ size_t sdxlq_workspace_bytes(const sdxlq_linear_desc* descs, size_t count) {
 int sdxlq_linear(sdxlq_context* ctx, const sdxlq_linear_desc* desc) {
     if (ctx == nullptr || desc == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
     Prepared prep;
-    int status = prepare(ctx, desc, 1, false, prep);
+    const int status = prepare(ctx, desc, 1, false, prep);
     if (status != SDXLQ_OK) return status;
-    status = run_int8_quantisers(ctx, prep, nullptr);
-    if (status != SDXLQ_OK) return status;
-    if (!prep.fp8_jobs.empty()) {
-        const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, nullptr);
-        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8);
-        const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream, ctx->early_launch && !ctx->profiling);
-        if (error != cudaSuccess) return fail_cuda(ctx, error, "FP8 activation quantise launch");
-    }
-    for (int flavour = 0; flavour < 2; ++flavour) {
-        status = run_gemm_flavour(ctx, prep, flavour, nullptr, nullptr);
-        if (status != SDXLQ_OK) return status;
-    }
-    status = run_small(ctx, prep);
-    if (status != SDXLQ_OK) return status;
-    count_stats(ctx, prep);
-    return SDXLQ_OK;
+    return run_prepared(ctx, prep, nullptr);
 }
 
 int sdxlq_group_plan_create(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count,
@@ -885,47 +966,31 @@ int sdxlq_group_plan_create(sdxlq_context* ctx, const sdxlq_linear_desc* descs, 
     sdxlq_group_plan* plan = new (std::nothrow) sdxlq_group_plan();
     if (plan == nullptr) return SDXLQ_ERR_CUDA;
     plan->device = ctx->device;
-    int status = prepare(ctx, descs, count, true, plan->prep);
+    plan->owner = ctx;
+    const int status = prepare(ctx, descs, count, true, plan->prep);
     if (status != SDXLQ_OK) { delete plan; return status; }
-    Prepared& prep = plan->prep;
-    auto upload = [&](auto** destination, const auto& host) -> bool {
-        using T = std::remove_reference_t<decltype(host[0])>;
-        if (host.empty()) return true;
-        if (cudaMalloc(reinterpret_cast<void**>(destination), host.size() * sizeof(T)) != cudaSuccess) return false;
-        return cudaMemcpy(*destination, host.data(), host.size() * sizeof(T), cudaMemcpyHostToDevice) == cudaSuccess;
-    };
-    if (!upload(&plan->device_problems[0], prep.problems[0]) || !upload(&plan->device_tiles[0], prep.tiles[0]) ||
-        !upload(&plan->device_problems[1], prep.problems[1]) || !upload(&plan->device_tiles[1], prep.tiles[1]) ||
-        !upload(&plan->device_int8_jobs[0], prep.int8[0].jobs) || !upload(&plan->device_int8_jobs[1], prep.int8[1].jobs) ||
-        !upload(&plan->device_int8_jobs[2], prep.int8[2].jobs) || !upload(&plan->device_fp8_jobs, prep.fp8_jobs)) {
-        sdxlq_group_plan_destroy(plan);
+    const TableLayout layout = layout_tables(plan->prep);
+    std::vector<uint8_t> image(layout.total, 0);
+    fill_tables(plan->prep, layout, image.data());
+    uint8_t* slab = nullptr;
+    if (cudaMalloc(reinterpret_cast<void**>(&slab), layout.total) != cudaSuccess ||
+        cudaMemcpy(slab, image.data(), layout.total, cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaFree(slab);
+        delete plan;
         return fail(ctx, SDXLQ_ERR_CUDA, "grouped plan: device table allocation failed");
     }
+    bind_tables(plan, layout, slab);
     *out = plan;
     return SDXLQ_OK;
 }
 
 int sdxlq_group_plan_run(sdxlq_context* ctx, sdxlq_group_plan* plan) {
     if (ctx == nullptr || plan == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
-    Prepared& prep = plan->prep;
-    {
-        const int quantise_status = run_int8_quantisers(ctx, prep, plan->device_int8_jobs);
-        if (quantise_status != SDXLQ_OK) return quantise_status;
+    if (plan->owner != ctx) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT,
+                    "grouped plan belongs to another context (its tables address that context's workspace)");
     }
-    if (!prep.fp8_jobs.empty()) {
-        const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, plan->device_fp8_jobs);
-        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8);
-        const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream, ctx->early_launch && !ctx->profiling);
-        if (error != cudaSuccess) return fail_cuda(ctx, error, "grouped FP8 activation quantise launch");
-    }
-    for (int flavour = 0; flavour < 2; ++flavour) {
-        const int gemm_status = run_gemm_flavour(ctx, prep, flavour, plan->device_problems[flavour], plan->device_tiles[flavour]);
-        if (gemm_status != SDXLQ_OK) return gemm_status;
-    }
-    const int status = run_small(ctx, prep);
-    if (status != SDXLQ_OK) return status;
-    count_stats(ctx, prep);
-    return SDXLQ_OK;
+    return run_prepared(ctx, plan->prep, plan);
 }
 
 int sdxlq_group_plan_launches(const sdxlq_group_plan* plan) {
@@ -938,21 +1003,62 @@ int sdxlq_group_plan_launches(const sdxlq_group_plan* plan) {
 void sdxlq_group_plan_destroy(sdxlq_group_plan* plan) {
     if (plan == nullptr) return;
     cudaSetDevice(plan->device);
-    for (GemmProblem* table : plan->device_problems) cudaFree(table);
-    for (TileRef* table : plan->device_tiles) cudaFree(table);
-    for (QuantInt8Job* table : plan->device_int8_jobs) cudaFree(table);
-    cudaFree(plan->device_fp8_jobs);
+    cudaFree(plan->slab);
     delete plan;
 }
 
 int sdxlq_linear_grouped(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count) {
-    sdxlq_group_plan* plan = nullptr;
-    int status = sdxlq_group_plan_create(ctx, descs, count, &plan);
+    if (ctx == nullptr || (descs == nullptr && count != 0)) return SDXLQ_ERR_INVALID_ARGUMENT;
+    if (count == 0) return SDXLQ_OK;
+    // Small groups (the three attention projections of one input): everything travels in the kernel
+    // parameters; no table, no allocation, nothing that a stream capture could not record.
+    if (count <= kInlineProblems) {
+        Prepared prep;
+        const int status = prepare(ctx, descs, count, false, prep);
+        if (status != SDXLQ_OK) return status;
+        if (fits_inline(prep)) return run_prepared(ctx, prep, nullptr);
+    }
+    // Larger groups: tables go to the device through the context's pinned staging buffer and a
+    // stream-ordered allocation that is released, in stream order, behind the kernels that read it.
+    // The call returns without waiting for the GPU; it only waits for the previous grouped call's
+    // table upload before it overwrites the staging buffer.
+    if (ctx->staging_event == nullptr) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "grouped calls need a context made by sdxlq_context_create");
+    }
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(ctx->stream, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT,
+                    "a grouped call with device tables cannot be captured: build a plan before the capture and run that");
+    }
+    sdxlq_group_plan plan;
+    plan.device = ctx->device;
+    plan.owner = ctx;
+    int status = prepare(ctx, descs, count, true, plan.prep);
     if (status != SDXLQ_OK) return status;
-    status = sdxlq_group_plan_run(ctx, plan);
-    // The device tables must outlive the kernels that read them.
-    if (cudaStreamSynchronize(ctx->stream) != cudaSuccess && status == SDXLQ_OK) status = SDXLQ_ERR_CUDA;
-    sdxlq_group_plan_destroy(plan);
+    const TableLayout layout = layout_tables(plan.prep);
+    cudaError_t error = cudaEventSynchronize(ctx->staging_event);
+    if (error == cudaSuccess && layout.total > ctx->staging_bytes) {
+        cudaFreeHost(ctx->staging);
+        ctx->staging = nullptr;
+        ctx->staging_bytes = 0;
+        const size_t wanted = align_up(layout.total * 2, size_t(1) << 20);
+        error = cudaMallocHost(reinterpret_cast<void**>(&ctx->staging), wanted);
+        if (error == cudaSuccess) ctx->staging_bytes = wanted;
+    }
+    if (error != cudaSuccess) return fail_cuda(ctx, error, "grouped call: table staging");
+    fill_tables(plan.prep, layout, ctx->staging);
+    uint8_t* slab = nullptr;
+    error = cudaMallocAsync(reinterpret_cast<void**>(&slab), layout.total, ctx->stream);
+    if (error == cudaSuccess) error = cudaMemcpyAsync(slab, ctx->staging, layout.total, cudaMemcpyHostToDevice, ctx->stream);
+    if (error == cudaSuccess) error = cudaEventRecord(ctx->staging_event, ctx->stream);
+    if (error != cudaSuccess) {
+        if (slab != nullptr) cudaFreeAsync(slab, ctx->stream);
+        return fail_cuda(ctx, error, "grouped call: table upload");
+    }
+    bind_tables(&plan, layout, slab);
+    status = run_prepared(ctx, plan.prep, &plan);
+    error = cudaFreeAsync(slab, ctx->stream);        // takes effect after the kernels above, in stream order
+    if (status == SDXLQ_OK && error != cudaSuccess) status = fail_cuda(ctx, error, "grouped call: table release");
     return status;
 }
 

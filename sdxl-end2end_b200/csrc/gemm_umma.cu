@@ -20,6 +20,8 @@
 #include "internal.cuh"
 #include "ptx.cuh"
 
+#include <mutex>
+
 namespace sdxlq {
 
 namespace {
@@ -88,13 +90,22 @@ struct alignas(64) Control {
     alignas(16) __half column_bias_half[kSlots][kMaxTileN];
 };
 
-// The record of tile `index` of the launch. Single-problem launches build it from the kernel
-// parameters (constant bank); grouped launches read it from the tile list in global memory.
-// Indices past the end read the last record, so a role may always fetch one tile ahead.
+// The record of tile `index` of the launch. Launches that carry their problems in the kernel
+// parameters (a single call, a small group) build it from there (constant bank): the tiles of
+// problem p are numbered inline_tile_start[p] .. inline_tile_start[p + 1] - 1, row tiles fastest.
+// Grouped plans read it from the tile list in global memory. Indices past the end read the last
+// record, so a role may always fetch one tile ahead.
 __device__ __forceinline__ TileRef load_tile(const GemmLaunchParams& params, uint32_t index) {
     index = min(index, params.num_tiles - 1u);
     if (params.problems == nullptr) {
-        return make_tile_ref(params.single, 0u, index % params.single.tiles_m, index / params.single.tiles_m);
+        uint32_t p = 0;
+#pragma unroll
+        for (uint32_t i = 1; i < kInlineProblems; ++i) {
+            if (i < params.inline_count && index >= params.inline_tile_start[i]) p = i;
+        }
+        const GemmProblem& problem = params.inline_problems[p];
+        const uint32_t local = index - params.inline_tile_start[p];
+        return make_tile_ref(problem, p, local % problem.tiles_m, local / problem.tiles_m);
     }
     const uint4* source = reinterpret_cast<const uint4*>(params.tiles + index);
     union {
@@ -107,7 +118,7 @@ __device__ __forceinline__ TileRef load_tile(const GemmLaunchParams& params, uin
 }
 
 __device__ __forceinline__ const GemmProblem* tile_problem(const GemmLaunchParams& params, const TileRef& tile) {
-    return params.problems == nullptr ? &params.single : params.problems + tile.problem;
+    return params.problems == nullptr ? &params.inline_problems[tile.problem] : params.problems + tile.problem;
 }
 
 __device__ __forceinline__ void raise_abort(Control* control, uint32_t* error_word, uint32_t code) {
@@ -193,6 +204,32 @@ __device__ __forceinline__ void store_row_16(__half* y, uint32_t n_out, bool vec
     }
 }
 
+// The 16 residual values that belong to one row's 16 outputs (packed two per word), loaded the way
+// store_row_16 writes them: one 256-bit load, two 128-bit loads, or element by element at the edge.
+__device__ __forceinline__ void load_row_16(const __half* source, uint32_t n_out, bool vector_ok, bool wide,
+                                            uint32_t row, uint32_t col0, uint32_t (&words)[8]) {
+    const __half* address = source + static_cast<size_t>(row) * n_out + col0;
+    if (col0 + 16 <= n_out && wide) {
+        asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3]), "=r"(words[4]), "=r"(words[5]),
+                       "=r"(words[6]), "=r"(words[7])
+                     : "l"(address)
+                     : "memory");
+    } else if (col0 + 16 <= n_out && vector_ok) {
+        const uint4 lo = reinterpret_cast<const uint4*>(address)[0];
+        const uint4 hi = reinterpret_cast<const uint4*>(address)[1];
+        words[0] = lo.x; words[1] = lo.y; words[2] = lo.z; words[3] = lo.w;
+        words[4] = hi.x; words[5] = hi.y; words[6] = hi.z; words[7] = hi.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t lo = col0 + 2 * i < n_out ? __half_as_ushort(address[2 * i]) : 0u;
+            const uint32_t hi = col0 + 2 * i + 1 < n_out ? __half_as_ushort(address[2 * i + 1]) : 0u;
+            words[i] = lo | (hi << 16);
+        }
+    }
+}
+
 // Reads W consecutive staged FP32 values starting at column j0 (a multiple of 4) with 16-byte
 // loads, as W / 2 pairs.
 template <int W>
@@ -242,6 +279,7 @@ __device__ __forceinline__ float2 from_half2_bits(uint32_t word) {
 struct EpilogueTile {
     __half* y;
     int32_t* acc_out;
+    const __half* residual;         // [M, n_out] added after the bias, or null (may alias y)
     const float* column_scale;      // shared memory
     const float* column_bias;       // shared memory, FP32
     const __half* column_bias_half; // shared memory, FP16
@@ -336,7 +374,12 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
     if (Act != ACT_GEGLU) {
         // columns this warp drains: c = chunk_first * 16 + m * kStride while c < tile_n and n0 + c < n
         const uint32_t limit = min(t.tile_n, t.n > t.n0 ? t.n - t.n0 : 0u);
-        auto finish = [&](uint32_t c0, const uint32_t (&acc)[16]) {
+        // Residual (Act == ACT_NONE only): __hadd(projection + bias, residual), the FP16 addition the
+        // reference's add_in_place_kernel performs after the Linear (src/cuda/ops_kernels.cu:60-64).
+        // Its 16 values are requested one chunk ahead, next to the tensor-memory load.
+        const __half* const residual = Act == ACT_NONE ? t.residual : nullptr;
+        const bool with_residual = residual != nullptr && row_ok;
+        auto finish = [&](uint32_t c0, const uint32_t (&acc)[16], const uint32_t (&extra)[8]) {
             const uint32_t col0 = t.n0 + c0;
             if (acc_out != nullptr && row_ok) {
                 int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n + col0;
@@ -347,22 +390,38 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
             }
             uint32_t out_words[8];
             finish_chunk_16<Kind, Act>(t, c0, acc, a_scale, has_bias, out_words);
+            if (Act == ACT_NONE && with_residual) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const __half2 sum = __hadd2(*reinterpret_cast<const __half2*>(&out_words[i]),
+                                                *reinterpret_cast<const __half2*>(&extra[i]));
+                    out_words[i] = *reinterpret_cast<const uint32_t*>(&sum);
+                }
+            }
             if (row_ok) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
         };
         uint32_t c = t.chunk_first * 16u;
         if (c >= limit) return;
         uint32_t even[16], odd[16];
+        uint32_t extra_even[8] = {}, extra_odd[8] = {};
         ptx::tmem_ld_32x32b_x16(t.tmem_row + c, even);
+        if (with_residual) load_row_16(residual, t.n_out, store_vector, store_wide, t.row, t.n0 + c, extra_even);
         while (true) {
             ptx::tmem_ld_wait(even);
             const uint32_t c1 = c + kStride;
-            if (c1 < limit) ptx::tmem_ld_32x32b_x16(t.tmem_row + c1, odd);
-            finish(c, even);
+            if (c1 < limit) {
+                ptx::tmem_ld_32x32b_x16(t.tmem_row + c1, odd);
+                if (with_residual) load_row_16(residual, t.n_out, store_vector, store_wide, t.row, t.n0 + c1, extra_odd);
+            }
+            finish(c, even, extra_even);
             if (c1 >= limit) break;
             ptx::tmem_ld_wait(odd);
             c = c1 + kStride;
-            if (c < limit) ptx::tmem_ld_32x32b_x16(t.tmem_row + c, even);
-            finish(c1, odd);
+            if (c < limit) {
+                ptx::tmem_ld_32x32b_x16(t.tmem_row + c, even);
+                if (with_residual) load_row_16(residual, t.n_out, store_vector, store_wide, t.row, t.n0 + c, extra_even);
+            }
+            finish(c1, odd, extra_odd);
             if (c >= limit) break;
         }
     } else {
@@ -729,6 +788,8 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             tile.y = work.y;
             tile.acc_out = nullptr;
             if ((flags & TILE_RAW_ACCUMULATORS) != 0) tile.acc_out = tile_problem(params, work)->ep.acc_out;
+            tile.residual = nullptr;
+            if ((flags & TILE_HAS_RESIDUAL) != 0) tile.residual = tile_problem(params, work)->ep.residual;
             tile.column_scale = control->column_scale[buffer];
             tile.column_bias = control->column_bias[buffer];
             tile.column_bias_half = control->column_bias_half[buffer];
@@ -803,17 +864,27 @@ cudaError_t launch_bounded_wait_probe(uint32_t* error_word, long long limit_cycl
 // the first stage to 1024 bytes.
 size_t umma_gemm_control_bytes() { return (sizeof(Control) + 1023u + 1023u) / 1024u * 1024u; }
 
-// Host-side launcher (called from the dispatch code). `attribute_bytes[pair]` remembers, per
-// context, the dynamic shared memory size each kernel flavour has been opted into. `grid` counts
-// CTAs (even for the CTA-pair flavour, which is launched as clusters of two).
+// Host-side launcher (called from the dispatch code). `grid` counts CTAs (even for the CTA-pair
+// flavour, which is launched as clusters of two). The opt-in to more than 48 KB of dynamic shared
+// memory is a per-device, process-wide property of the kernel, not of a context: both flavours are
+// opted into the architectural maximum once per device, so that contexts with different tile
+// geometries on one GPU cannot lower each other's limit.
 cudaError_t launch_umma_gemm(const GemmLaunchParams& params, uint32_t grid, size_t dynamic_smem,
-                             cudaStream_t stream, size_t* attribute_bytes, bool pair, bool early_launch) {
+                             cudaStream_t stream, int device, bool pair, bool early_launch) {
     auto kernel = pair ? sdxlq_umma_gemm_kernel<true> : sdxlq_umma_gemm_kernel<false>;
-    if (dynamic_smem > attribute_bytes[pair ? 1 : 0]) {
-        const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                        static_cast<int>(dynamic_smem));
-        if (status != cudaSuccess) return status;
-        attribute_bytes[pair ? 1 : 0] = dynamic_smem;
+    constexpr int kMaxDevices = 64;
+    constexpr int kSharedMemoryOptIn = 232448;      // 227 KiB per CTA on sm_100
+    static std::mutex opt_in_mutex;
+    static bool opted_in[kMaxDevices][2] = {};
+    if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+    {
+        std::lock_guard<std::mutex> lock(opt_in_mutex);
+        if (!opted_in[device][pair ? 1 : 0]) {
+            const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                            kSharedMemoryOptIn);
+            if (status != cudaSuccess) return status;
+            opted_in[device][pair ? 1 : 0] = true;
+        }
     }
     cudaLaunchConfig_t config{};
     config.gridDim = dim3(grid, 1, 1);

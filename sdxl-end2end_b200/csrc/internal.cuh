@@ -34,6 +34,7 @@ struct EpilogueParams {
     const float* a_scales;       // INT8: [M]; FP8: [1]; FP16: unused
     const float* w_scales;       // [N] or [1]; FP16: unused
     const __half* bias;          // [N] or null
+    const __half* residual;      // optional [M, N] added to the biased projection (may alias y)
     uint32_t m, n, k;
     uint32_t n_out;              // n, or n / 2 for GEGLU
     uint32_t kind;               // GemmKind
@@ -65,6 +66,7 @@ enum TileFlags : uint16_t {
     TILE_STORE_16 = 4,          // y rows 16-byte aligned and n_out % 8 == 0
     TILE_STORE_32 = 8,          // y rows 32-byte aligned and n_out % 16 == 0
     TILE_RAW_ACCUMULATORS = 16, // the problem also wants its INT32 accumulators (ep.acc_out)
+    TILE_HAS_RESIDUAL = 32,     // ep.residual is added after the bias (no activation)
 };
 
 struct alignas(64) TileRef {
@@ -104,7 +106,8 @@ __host__ __device__ inline TileRef make_tile_ref(const GemmProblem& problem, uin
     r.flags = static_cast<uint16_t>((ep.bias != nullptr ? TILE_HAS_BIAS : 0) |
                                     (ep.kind != KIND_F16 && ep.w_scale_per_channel != 0 ? TILE_SCALE_PER_CHANNEL : 0) |
                                     (ep.vector_store_ok != 0 ? TILE_STORE_16 : 0) | (store_32 ? TILE_STORE_32 : 0) |
-                                    (ep.acc_out != nullptr ? TILE_RAW_ACCUMULATORS : 0));
+                                    (ep.acc_out != nullptr ? TILE_RAW_ACCUMULATORS : 0) |
+                                    (ep.residual != nullptr ? TILE_HAS_RESIDUAL : 0));
     r.m = ep.m;
     r.n = ep.n;
     r.w_scales = ep.w_scales;
@@ -114,9 +117,14 @@ __host__ __device__ inline TileRef make_tile_ref(const GemmProblem& problem, uin
     return r;
 }
 
+// Problems a launch can carry in its kernel parameters instead of a device table: a single call, or a
+// small group (the three attention projections of one input) that then needs no table upload and
+// can be issued inside a stream capture.
+constexpr uint32_t kInlineProblems = 4;
+
 struct GemmLaunchParams {
-    const GemmProblem* problems; // device table (grouped) or null (single: `single` is used)
-    const TileRef* tiles;        // device tile list (grouped) or null
+    const GemmProblem* problems; // device table (grouped plan) or null (`inline_problems` are used)
+    const TileRef* tiles;        // device tile list (grouped plan) or null
     uint32_t num_tiles;
     uint32_t num_stages;
     uint32_t stage_bytes;        // bytes of one pipeline stage (A tile + B tile), multiple of 1024
@@ -127,8 +135,10 @@ struct GemmLaunchParams {
                                  // stores; bit 1: no operand loads, no MMAs; bit 2: no operand loads; bit 3: no
                                  // MMAs; bit 5: one MMA per stage instead
                                  // of four; bit 6: only the A operand is loaded. Barriers are still signalled.
-    uint32_t pad0;
-    GemmProblem single;
+    uint32_t inline_count;       // problems in `inline_problems` (1 for a single call)
+    uint32_t inline_tile_start[kInlineProblems + 1];   // first tile of each inline problem, then the tile count
+    uint32_t pad1[3];
+    GemmProblem inline_problems[kInlineProblems];
 };
 
 // ------------------------------------------------------------------------------------------

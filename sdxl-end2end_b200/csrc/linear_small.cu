@@ -79,6 +79,8 @@ sdxlq_small_linear_kernel(const __grid_constant__ SmallLinearParams p) {
         result = finish_geglu(y, ep.bias[col], y_gate, ep.bias[gate_col]);
     } else {
         result = finish_scalar(y, has_bias, has_bias ? ep.bias[col] : __half(0), ep.activation);
+        // Ops::add_in_place after the Linear, folded in (may alias y: each thread reads its element first)
+        if (ep.residual != nullptr) result = __hadd(result, ep.residual[static_cast<size_t>(row) * ep.n_out + col]);
     }
     ep.y[static_cast<size_t>(row) * ep.n_out + col] = result;
 }

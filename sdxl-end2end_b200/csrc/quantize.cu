@@ -319,13 +319,22 @@ fp8_cast_kernel(const __grid_constant__ QuantFp8Launch launch) {
     const uint32_t job_index = find_job_index(launch, blockIdx.x);
     const QuantFp8Job& job = launch.jobs == nullptr ? launch.single : launch.jobs[job_index];
     const uint32_t local_block = blockIdx.x - job.first_block;
-    const float scale = fp8_scale_from_amax(__uint_as_float(launch.amax_bits[job_index]), job.fmt);
+    // One thread reads the job's maximum and counts this block among its readers; the block that
+    // completes the count clears the maximum and the counter, so the next call (and every replay of
+    // a captured graph) finds both words zero without any host-side bookkeeping.
+    __shared__ uint32_t maximum_bits;
+    if (threadIdx.x == 0) {
+        maximum_bits = *reinterpret_cast<volatile uint32_t*>(launch.amax_bits + job_index);
+        __threadfence();
+        if (atomicAdd(launch.done_counts + job_index, 1u) == job.num_blocks - 1u) {
+            launch.amax_bits[job_index] = 0;
+            launch.done_counts[job_index] = 0;
+        }
+    }
+    __syncthreads();
+    const float scale = fp8_scale_from_amax(__uint_as_float(maximum_bits), job.fmt);
     const float inverse_scale = __fdiv_rn(1.0f, scale);
     if (local_block == 0 && threadIdx.x == 0) *job.scale_out = scale;
-    // Housekeeping for the call after next: clear the amax words of the other parity.
-    if (blockIdx.x == 0 && threadIdx.x < 32) {
-        for (uint32_t j = threadIdx.x; j < launch.clear_count; j += 32) launch.clear_bits[j] = 0;
-    }
     const __half* source = static_cast<const __half*>(job.x);
     uint8_t* destination = job.q;
     const size_t count = job.count;

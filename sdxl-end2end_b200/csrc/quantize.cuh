@@ -45,9 +45,10 @@ struct QuantFp8Job {
 struct QuantFp8Launch {
     const QuantFp8Job* jobs;     // device table (grouped) or null
     uint32_t num_jobs;
-    uint32_t clear_count;        // amax words of the other parity to clear for the call after next
-    uint32_t* clear_bits;
+    uint32_t pad;
     uint32_t* amax_bits;         // one scratch word per job, all zero on entry of the amax kernel
+    uint32_t* done_counts;       // one word per job, zero on entry: cast blocks that have read the job's maximum;
+                                 // the last one to read it puts both words back to zero for the next call
     QuantFp8Job single;
 };
 
