@@ -3,26 +3,28 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
-A "step" is one pass of the hot path over one batch of synthetic input. The default workload is
-the 640-dim transformer-block layer set under W8A8 INT8 ConvRot at 1024^2, CFG batch 2
-(to_q/to_k/to_v/to_out [8192,640]x[640,640], ff.net.0.proj+GEGLU [8192,640]x[5120,640],
-ff.net.2 [8192,2560]x[640,2560]); the three attention projections share one quantised input.
-Other workloads: `layerset1280_fp8` (the 1280-dim set under FP8 E4M3 per-channel, plus the
-skinny cross-attention K/V GEMM), `unet743_int8` / `unet743_e5m2` (all 743 rank-2 projections of
-one UNet step as one grouped launch), `crossattn_kv_int8` (the 140 cross-attention K/V projections
-a per-generation cache removes from every step), `unetstep_int8|e4m3|e5m2` (one denoising step's
-projections for this rank's share of 8 images x CFG 2: strong scaling over 1/2/4/8 ranks by
-sharding images, projections only).
+Default workload `unetloop_e4m3`: the synthetic SDXL Base UNet denoising loop at 1024^2 for a fixed
+job of 8 images x CFG 2 (UNet batch 16), FP8 E4M3 projections (per-output-channel weight scales,
+native FP8 activations), FP16 convolutions / norms / attention from PyTorch around them, Euler
+sampler, sigma schedule of 20 steps. A "step" is one denoising step of the whole job: scale the
+latents, one UNet forward over [uncond | cond], CFG combine, Euler update; every 20 steps a new
+generation starts and the cross-attention K/V projections are recomputed once. With N ranks the
+images are sharded (8 / N images, UNet batch 16 / N per rank), weights are replicated and there
+is no collective in the step: strong scaling. `value` = denoising steps per second of the job.
+Other precisions: `unetloop_e5m2`, `unetloop_int8`, `unetloop_f16`.
 
-Rank 0 prints ONE JSON line. `value` is whole-job throughput (all ranks) with inputs resident in
-HBM, timed on the device with CUDA events, max over ranks. `e2e` is the same metric through the
-public API with host buffers (pinned host -> device copies of the inputs and device -> host reads
-of the results inside the timed region). With N > 1 every rank runs the same workload on its own
-GPU with replicated weights (weak scaling, no collective on the data path).
+Projection-only workloads (`--workload NAME`; the N = 1 default run also times them and reports
+them under `other_workloads`): `layerset640_int8` / `layerset640_int8_g64` (640-dim layer set, W8A8
+INT8 ConvRot, group 256 rule resp. groups of 64), `layerset1280_fp8` (1280-dim set, FP8 E4M3, plus
+the skinny cross-attention K/V GEMM), `unet743_int8` / `unet743_e5m2` (all 743 projections of a UNet
+step as one grouped launch), `geglu640_f16` (the single FP16 GEGLU projection [8192,640]x[5120,640]),
+`crossattn_kv_int8`, `unetstep_<kind>` (projections of one step, sharded like the loop).
 
-`--impl reference` times the reference's own CPU implementation of the path (its threaded AVX2
-Linear compiled from the reference sources, else the CPU port) on a bounded sample of the same
-workload, on the host cores of the box.
+Rank 0 prints ONE JSON line. Device times come from CUDA events on the launching stream, max over
+ranks. `e2e` is the same metric through the public API with host buffers: every step copies its
+inputs from pinned host memory and reads its result back. `--impl reference` times the reference's
+own CPU Linear (compiled from the reference sources, else the CPU port) on a bounded sample of the
+same projections with all host threads and converts it to the same metric.
 """
 from __future__ import annotations
 
@@ -42,12 +44,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-METRIC = "quantized_linear_tops"
-UNIT = "TOPS"
 L2_BYTES = 126 * 1024 * 1024
-# DRAM bytes (read + write) of one grouped GEMM launch of the default workload, from the ncu
-# capture summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum).
-TRAFFIC_BYTES = {"layerset640_int8": 88.75e6}
+JOB_IMAGES = 8                 # images of the fixed job (x CFG 2 = UNet batch 16)
+GENERATION_STEPS = 20          # denoising steps per generation (sigma schedule length)
 
 
 def load_peaks():
@@ -61,8 +60,16 @@ def load_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def package():
+    return importlib.import_module("sdxl-end2end_b200")
+
+
+def unet_shapes():
+    return importlib.import_module("sdxl-end2end_b200.unet_shapes")
+
+
 # ------------------------------------------------------------------------------------------------
-# workloads
+# projection-only workloads
 # ------------------------------------------------------------------------------------------------
 def layer_set(dim: int, tokens: int, batch_rows_context: int):
     """(name, M, N, K, bias, activation, input_key) of one transformer block's projections."""
@@ -76,42 +83,42 @@ def layer_set(dim: int, tokens: int, batch_rows_context: int):
     return rows
 
 
-def workload_rows(name: str):
-    if name == "layerset640_int8":
-        return layer_set(640, 8192, 0), "int8", ("SDXL UNet 640-dim layer set, W8A8 INT8 ConvRot (group 256 rule: K=2560 rotates), "
-                                                "1024^2 CFG batch 2: q,k,v,out [8192,640]x[640,640]; ff.net.0.proj+GEGLU "
-                                                "[8192,640]x[5120,640]; ff.net.2 [8192,2560]x[640,2560]")
+def workload_rows(name: str, world: int = 1):
+    """-> (rows, kind, convrot group, description)"""
+    if name in ("layerset640_int8", "layerset640_int8_g64"):
+        group = 64 if name.endswith("g64") else 256
+        rule = "groups of 64: every projection rotates" if group == 64 else "group 256 rule: only K=2560 rotates"
+        return layer_set(640, 8192, 0), "int8", group, (
+            f"SDXL UNet 640-dim layer set, W8A8 INT8 ConvRot ({rule}), 1024^2 CFG batch 2: q,k,v,out [8192,640]x[640,640]; "
+            "ff.net.0.proj+GEGLU [8192,640]x[5120,640]; ff.net.2 [8192,2560]x[640,2560]")
     if name == "layerset1280_fp8":
-        return layer_set(1280, 2048, 154), "e4m3", ("SDXL UNet 1280-dim layer set, FP8 E4M3 per-channel weights, native FP8 activations, "
-                                                    "M=2048; plus cross-attention to_k/to_v [154,2048]x[1280,2048]")
+        return layer_set(1280, 2048, 154), "e4m3", 0, (
+            "SDXL UNet 1280-dim layer set, FP8 E4M3 per-channel weights, native FP8 activations, M=2048; plus "
+            "cross-attention to_k/to_v [154,2048]x[1280,2048]")
+    if name == "geglu640_f16":
+        return [("ff.net.0.proj", 8192, 5120, 640, True, 4, "norm3")], "f16", 0, (
+            "single SDXL GEGLU ff.net.0.proj Linear, FP16 weights: X [8192,640] x W [5120,640] + bias, GEGLU")
     if name == "crossattn_kv_int8":
-        # what a cross-attention K/V cache takes out of every denoising step
-        shapes = importlib.import_module("sdxl-end2end_b200.unet_shapes")
-        rows = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in shapes.unet_projections(2)
+        rows = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in unet_shapes().unet_projections(2)
                 if ".attn2.to_k" in p.name or ".attn2.to_v" in p.name]
-        return rows, "int8", (f"the {len(rows)} cross-attention to_k/to_v projections [154,2048]x[640|1280,2048] of one SDXL UNet step, "
-                              "INT8 ConvRot, one grouped launch (HBM-bound: weights are read once)")
+        return rows, "int8", 256, (
+            f"the {len(rows)} cross-attention to_k/to_v projections [154,2048]x[640|1280,2048] of one SDXL UNet step, INT8 "
+            "ConvRot, one grouped launch (HBM-bound: weights are read once)")
     if name.startswith("unetstep_"):
-        # unetstep_<int8|e4m3|e5m2>: every projection of one denoising step for this rank's share of a
-        # fixed job of 8 images x CFG 2 (UNet batch 16), images sharded over the ranks with replicated
-        # weights (UNet batch 16 / world per rank). Only the projections run: convolutions, norms and
-        # attention are not part of this path, so steps/s here bounds the UNet's from above.
         kind = name.split("_", 1)[1]
         if kind not in ("int8", "e4m3", "e5m2"):
             raise SystemExit(f"unknown workload {name}")
-        world = int(os.environ.get("WORLD_SIZE", "1"))
         if 16 % world != 0 or 16 // world < 2:
             raise SystemExit("unetstep shards 8 CFG pairs: 1, 2, 4 or 8 ranks")
         local_batch = 16 // world
-        shapes = importlib.import_module("sdxl-end2end_b200.unet_shapes")
-        rows = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in shapes.unet_projections(local_batch)]
-        return rows, kind, (f"all 743 rank-2 projections of one SDXL UNet step at 1024^2 for {local_batch // 2} of 8 images x CFG 2 "
-                            f"(UNet batch {local_batch} of 16 on this rank), one grouped launch, {kind}; projections only")
+        rows = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in unet_shapes().unet_projections(local_batch)]
+        return rows, kind, 256, (
+            f"all 743 rank-2 projections of one SDXL UNet step at 1024^2 for {local_batch // 2} of 8 images x CFG 2 (UNet batch "
+            f"{local_batch} of 16 on this rank), one grouped launch, {kind}; projections only")
     if name in ("unet743_int8", "unet743_e5m2"):
-        shapes = importlib.import_module("sdxl-end2end_b200.unet_shapes")
-        rows = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in shapes.unet_projections(2)]
+        rows = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in unet_shapes().unet_projections(2)]
         kind = "int8" if name.endswith("int8") else "e5m2"
-        return rows, kind, f"all 743 rank-2 projections of one SDXL UNet step at 1024^2, CFG batch 2, one grouped launch, {kind}"
+        return rows, kind, 256, f"all 743 rank-2 projections of one SDXL UNet step at 1024^2, CFG batch 2, one grouped launch, {kind}"
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -119,21 +126,30 @@ def total_ops(rows) -> float:
     return float(sum(2 * m * n * k for (_, m, n, k, _, _, _) in rows))
 
 
+def minimum_bytes(rows, kind) -> float:
+    """Bytes a GEMM launch must move at least: each distinct (quantised) input and each weight read
+    once, each FP16 output written once."""
+    element = 2 if kind == "f16" else 1
+    inputs = {key: m * k * element for (_, m, _, k, _, _, key) in rows}
+    weights = sum(n * k * element for (_, _, n, k, _, _, _) in rows)
+    outputs = sum(m * (n // 2 if act == 4 else n) * 2 for (_, m, n, _, _, act, _) in rows)
+    return float(sum(inputs.values()) + weights + outputs)
+
+
 class DeviceWorkload:
     """Weights (quantised once), and `sets` rotating sets of inputs / outputs with one plan each."""
 
-    def __init__(self, pkg, ops, rows, kind, sets, seed=1234):
+    def __init__(self, pkg, ops, rows, kind, group, sets, seed=1234):
         import torch
-        import helpers as H
         self.pkg, self.ops, self.rows, self.kind = pkg, ops, rows, kind
         device = torch.device("cuda", torch.cuda.current_device())
         generator = torch.Generator(device=device)
         generator.manual_seed(seed)
-        self.weights, self.biases = [], []
+        self.weights, self.biases, self.dense = [], [], []
         for index, (name, m, n, k, bias, activation, key) in enumerate(rows):
             w = (torch.randn((n, k), generator=generator, device=device, dtype=torch.float32) / (k ** 0.5)).half()
             if kind == "int8":
-                options = pkg.INT8WeightLoadOptions(enable_convrot=True, convrot_group_size=256)
+                options = pkg.INT8WeightLoadOptions(enable_convrot=True, convrot_group_size=group)
                 weight = ops.upload_or_quantize_int8_weight(w, None, options)
             elif kind in ("e4m3", "e5m2"):
                 fmt = pkg.ScalarType.Float8E4M3 if kind == "e4m3" else pkg.ScalarType.Float8E5M2
@@ -169,6 +185,153 @@ class DeviceWorkload:
     def launches_per_step(self) -> int:
         return self.plans[0].launches
 
+    def close(self):
+        for plan in self.plans:
+            plan.close()
+
+
+def quantiser_bytes(input_shapes, kind) -> float:
+    """Algorithmic bytes of the activation quantisers of one step: FP16 read + 8-bit write (+ one FP32
+    scale per row for INT8). The FP8 quantiser needs the tensor-wide maximum before it can write a
+    byte, so its input is read twice: 2 + 2 + 1 bytes per element."""
+    if kind == "int8":
+        return float(sum(m * k * 3 + 4 * m for (m, k) in input_shapes))
+    if kind in ("e4m3", "e5m2"):
+        return float(sum(m * k * 5 for (m, k) in input_shapes))
+    return 0.0
+
+
+def time_projection_workload(torch, pkg, context, ops, name, peaks, min_seconds=0.4, world=1, library=False):
+    """Device-timed grouped plan of a projection-only workload: TOPS, per-kernel times, roofline."""
+    rows, kind, group, description = workload_rows(name, world)
+    sets = 3 if (name.startswith("layerset") or name.startswith("geglu")) else 1
+    work = DeviceWorkload(pkg, ops, rows, kind, group, sets)
+    ops_per_step = total_ops(rows)
+    stream = torch.cuda.current_stream()
+    for step in range(6):
+        work.plans[step % sets].run()
+    torch.cuda.synchronize()
+    # size the timed region: at least `min_seconds`
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for step in range(3):
+        work.plans[step % sets].run()
+    stop.record(stream)
+    torch.cuda.synchronize()
+    probe_ms = start.elapsed_time(stop) / 3
+    steps = int(max(10, min(20000, min_seconds * 1e3 / max(probe_ms, 1e-3))))
+    start.record(stream)
+    for step in range(steps):
+        work.plans[step % sets].run()
+    stop.record(stream)
+    torch.cuda.synchronize()
+    ms_per_step = start.elapsed_time(stop) / steps
+    # per-kernel times: event pairs around every launch, second pass
+    profile_steps = max(3, min(steps, 200))
+    context.profile(True)
+    context.kernel_times()
+    for step in range(profile_steps):
+        work.plans[step % sets].run()
+    kernel_times = context.kernel_times()
+    context.profile(False)
+    gemm_ms = kernel_times["gemm"][0] / profile_steps
+    quant_ms = (kernel_times["quant_int8"][0] + kernel_times["quant_fp8"][0]) / profile_steps
+    eight_bit = kind != "f16"
+    tensor_peak = peaks["bf16_tflops"] * (2.0 if eight_bit else 1.0)
+    achieved = ops_per_step / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    quant_bytes = quantiser_bytes(work.input_shapes.values(), kind)
+    result = {
+        "workload": description, "kind": kind, "projections": len(rows), "ops_per_step": ops_per_step,
+        "tops": ops_per_step / (ms_per_step * 1e-3) / 1e12, "ms_per_step": ms_per_step, "steps_timed": steps,
+        "launches_per_step": work.launches_per_step(),
+        "gemm": {"ms": gemm_ms, "tops": achieved, "frac_of_peak": achieved / tensor_peak, "peak_tflops": tensor_peak,
+                 "min_bytes": minimum_bytes(rows, kind),
+                 "hbm_frac_at_min_bytes": (minimum_bytes(rows, kind) / (gemm_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]) if gemm_ms > 0 else None},
+        "quantize": {"ms": quant_ms, "bytes": quant_bytes,
+                     "gbs": quant_bytes / (quant_ms * 1e-3) / 1e9 if quant_ms > 0 else None,
+                     "frac_of_hbm": (quant_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]) if quant_ms > 0 else None},
+        "l2": f"{sets} rotating input/output sets, {sets * work.working_set / 1e6:.0f} MB per cycle" if sets > 1
+              else f"working set {work.working_set / 1e6:.0f} MB per step",
+    }
+    if library:
+        result["library_same_shapes"] = library_same_shapes(torch, rows, kind, work)
+    work.close()
+    del work
+    torch.cuda.empty_cache()
+    return result
+
+
+def library_same_shapes(torch, rows, kind, work):
+    """The reference's launch structure with the vendor library's GEMM on the same shapes: per
+    projection a quantise step, a cuBLASLt GEMM (torch._int_mm = I8 x I8 -> I32 for INT8, as
+    int8_convrot_linear calls it, src/cuda/int8_convrot.cu:634-698; torch._scaled_mm = FP8 x FP8 -> FP16
+    with device scales, as native_fp8_linear does, src/cuda/ops_blas.cpp:153-225), then the separate
+    dequantise / bias / GEGLU kernels the reference runs afterwards (ops_blas.cpp:388-397). The
+    quantise step here is a plain absmax + cast in PyTorch (no rotation), which only flatters the
+    library arm. Timed with CUDA events, outside this benchmark's timed region."""
+    import torch.nn.functional as F
+    try:
+        prepared = []
+        for index, (name, m, n, k, bias, activation, key) in enumerate(rows):
+            x = work.inputs[0][key]
+            w = work.weights[index]
+            b = work.biases[index]
+            if kind == "int8":
+                prepared.append((x, w.data, w.scales, b, activation, m))
+            elif kind in ("e4m3", "e5m2"):
+                dtype = torch.float8_e4m3fn if kind == "e4m3" else torch.float8_e5m2
+                prepared.append((x, w.data.view(dtype), w.scales, b, activation, m))
+            else:
+                prepared.append((x, w.data, None, b, activation, m))
+
+        def epilogue(y, b, activation):
+            if activation == 4:
+                y = y + b
+                value, gate = y.chunk(2, dim=-1)
+                return value * F.gelu(gate)
+            return y + b if b is not None else y
+
+        def step():
+            outs = []
+            for x, w, scales, b, activation, m in prepared:
+                if kind == "int8":
+                    if m <= 16:
+                        continue                          # _int_mm needs more than 16 rows; the embeddings carry no work
+                    amax = x.abs().amax(dim=1, keepdim=True).float().clamp_min(1e-30)
+                    xq = torch.round(x.float() * (127.0 / amax)).clamp_(-128, 127).to(torch.int8)
+                    acc = torch._int_mm(xq, w.t())
+                    y = (acc.float() * (amax / 127.0) * scales[None, :]).half()
+                elif kind in ("e4m3", "e5m2"):
+                    limit = 448.0 if kind == "e4m3" else 57344.0
+                    scale = (x.abs().amax().float() / limit).clamp_min(1e-12)
+                    xq = (x.float() / scale).to(w.dtype)
+                    if m % 16 or w.shape[0] % 16 or w.shape[1] % 16:
+                        continue
+                    # tensor-wide scales inside the GEMM (what the reference passes to cuBLASLt); the
+                    # per-output-channel weight scale is one more elementwise pass
+                    y = torch._scaled_mm(xq, w.t(), scale_a=scale.reshape(()), scale_b=torch.ones((), device=x.device),
+                                         out_dtype=torch.float16) * scales[None, :].half()
+                else:
+                    y = x @ w.t()
+                outs.append(epilogue(y, b, activation))
+            return outs
+
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        repeats = 10
+        start.record()
+        for _ in range(repeats):
+            step()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / repeats
+        return {"ms_per_step": ms, "tops": total_ops(rows) / (ms * 1e-3) / 1e12,
+                "what": "PyTorch quantise + cuBLASLt GEMM (torch._int_mm / torch._scaled_mm) + separate dequant, bias, GEGLU kernels"}
+    except Exception as error:      # context only: the benchmark does not depend on the library arm
+        return {"ms_per_step": None, "tops": None, "what": f"library arm unavailable: {type(error).__name__}: {error}"}
+
 
 # ------------------------------------------------------------------------------------------------
 # clocks
@@ -187,10 +350,13 @@ class ClockSampler:
                 stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.process = None
-        self.marks = []
+        self.window = [None, None]
 
-    def mark(self, label: str):
-        self.marks.append((label, time.time()))
+    def mark_start(self):
+        self.window[0] = time.time()
+
+    def mark_stop(self):
+        self.window[1] = time.time()
 
     def stop(self):
         if self.process is not None:
@@ -222,35 +388,12 @@ class ClockSampler:
                 "samples_under_load": len(loaded)}
 
 
-def library_int8_rate(torch, steps: int = 20):
-    """INT8 x INT8 -> INT32 rate of the vendor library GEMM (torch._int_mm -> cuBLASLt) on an
-    [8192, 8192] x [8192, 8192] product, device-timed: the rate a plain library GEMM without any
-    epilogue reaches on this GPU, reported beside the roofline for context (it is not the peak the
-    roofline fraction uses)."""
-    try:
-        a = torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device="cuda")
-        b = torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device="cuda")
-        for _ in range(3):
-            torch._int_mm(a, b)
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        start.record()
-        for _ in range(steps):
-            torch._int_mm(a, b)
-        stop.record()
-        torch.cuda.synchronize()
-        seconds = start.elapsed_time(stop) * 1e-3 / steps
-        return {"value": 2.0 * 8192 ** 3 / seconds / 1e12, "unit": "TOPS", "what": "torch._int_mm (cuBLASLt) 8192^3, no epilogue"}
-    except Exception as error:  # the library call is context only; the bench does not depend on it
-        return {"value": None, "unit": "TOPS", "what": f"torch._int_mm unavailable: {error}"}
-
-
 # ------------------------------------------------------------------------------------------------
 # CPU arms
 # ------------------------------------------------------------------------------------------------
-def cpu_single_core_baseline(budget_seconds: float = 15.0):
+def cpu_single_core_rate(budget_seconds: float = 15.0):
     """The reference's scalar `linear_2d` + `geglu` on a row slice of the FP16 GEGLU projection
-    X[rows,640] x W[5120,640]: one host core."""
+    X[rows,640] x W[5120,640]: one host core. Returns (TOPS, kind, description)."""
     from oracle import oracle as O
     import helpers as H
     w = H.make_weight(7, 5120, 640)
@@ -274,23 +417,22 @@ def cpu_single_core_baseline(budget_seconds: float = 15.0):
     rows = int(max(32, min(8192, probe_rows * budget_seconds / max(probe, 1e-6))))
     elapsed = run(rows)
     ops = 2.0 * rows * 5120 * 640
-    return {"value": ops / elapsed / 1e12, "unit": UNIT, "cores": 1, "kind": "reference" if use_reference else "port",
-            "sample": f"linear_2d+geglu, FP16 weights, X[{rows},640] x W[5120,640] of the [8192,640] GEGLU projection, "
-                      f"{elapsed:.1f} s single-threaded"}
+    return ops / elapsed / 1e12, ("reference" if use_reference else "port"), (
+        f"linear_2d+geglu, FP16 weights, X[{rows},640] x W[5120,640] of the [8192,640] GEGLU projection, {elapsed:.1f} s single-threaded")
 
 
-def reference_arm(args, rows, description):
-    """Times the reference's threaded AVX2 Linear on a bounded row sample of every projection."""
+def reference_threaded_rate(rows_table, sample_rows, steps, warmup):
+    """The reference's threaded AVX2 Linear on the first `sample_rows` rows of every projection:
+    (seconds per sample step, ops per sample step, threads, kind)."""
     from oracle import oracle as O
     import helpers as H
     use_reference = O.ref_available()
     threads = O.ref_hardware_threads() if use_reference else O.threads()
-    sample_rows = args.reference_rows
     problems = []
-    for index, (name, m, n, k, bias, activation, key) in enumerate(rows):
+    for index, (name, m, n, k, bias, activation, key) in enumerate(rows_table):
         mm = min(m, sample_rows)
         x = H.make_activations(index, mm, k).astype(np.float32)
-        w = H.make_weight(index, n, k)
+        w = H.make_weight(index % 64, n, k)            # 64 distinct weight draws are plenty for a timing
         b = H.make_bias(index, n) if bias else None
         problems.append((x, w, b, activation, 2.0 * mm * n * k))
     ops_per_step = sum(p[4] for p in problems)
@@ -306,25 +448,300 @@ def reference_arm(args, rows, description):
                 if activation == 4:
                     O.geglu_f32(y)
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     start = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
     elapsed = time.perf_counter() - start
-    value = ops_per_step * args.steps / elapsed / 1e12
+    return elapsed / steps, ops_per_step, threads, ("reference" if use_reference else "port")
+
+
+def reference_arm(args):
+    """`--impl reference`: the reference's CPU Linear on a bounded sample, in this arm's metric."""
+    loop = args.workload.startswith("unetloop_")
+    if loop:
+        rows = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in unet_shapes().unet_projections(2 * JOB_IMAGES)]
+        description = unetloop_description(args.workload.split("_", 1)[1])
+        sample_rows = args.reference_rows or 16
+    else:
+        rows, _, _, description = workload_rows(args.workload, 1)
+        sample_rows = args.reference_rows or 256
+    seconds, sample_ops, threads, kind = reference_threaded_rate(rows, sample_rows, args.steps, args.warmup)
+    tops = sample_ops / seconds / 1e12
+    full_ops = total_ops(rows)
     sample = (f"threaded AVX2 Linear of the reference (dense FP16 weights; it has no CPU INT8/FP8 arithmetic) on the first "
-              f"{sample_rows} rows of every projection, {threads} host threads")
+              f"{sample_rows} rows of every projection ({sample_ops / 1e9:.1f} GOP per sample step), {threads} host threads")
+    if loop:
+        # steps/s of the job if its projections ran at the sampled CPU rate; the CPU reference's
+        # convolutions, norms and attention would add to the step time, so this bounds it from above
+        value = tops * 1e12 / full_ops
+        metric, unit = "sdxl_unet_steps_per_s", "steps/s"
+        sample += (f"; converted to denoising steps/s of the 8-image x CFG 2 job by its {full_ops / 1e12:.2f} TOP of projections per step "
+                   "(projections only: an upper bound for the CPU reference's full step)")
+        ms_per_step = 1e3 / value
+    else:
+        value, metric, unit = tops, "quantized_linear_tops", "TOPS"
+        ms_per_step = seconds * 1e3
     return {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if (loop or args.workload.startswith("unetstep_")) else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": description, "sample_rows": sample_rows},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "reference" if use_reference else "port",
-                         "sample": sample},
-        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": {"workload": description, "name": args.workload, "sample_rows": sample_rows, "cpu_tops": tops},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+
+
+# ------------------------------------------------------------------------------------------------
+# the UNet loop
+# ------------------------------------------------------------------------------------------------
+def unetloop_description(kind: str) -> str:
+    names = {"e4m3": "FP8 E4M3 (per-output-channel weight scales, native FP8 activations)",
+             "e5m2": "FP8 E5M2 (per-output-channel weight scales, native FP8 activations)",
+             "int8": "W8A8 INT8 ConvRot (group 256 rule)", "f16": "FP16"}
+    return (f"synthetic SDXL Base UNet denoising loop, 1024^2, 8 images x CFG 2 (latents [16,4,128,128], context [16,77,2048], "
+            f"pooled [16,1280]), {GENERATION_STEPS} Euler steps per generation, random-init weights; projections {names[kind]}; "
+            "FP16 convolutions / norms / attention (PyTorch)")
+
+
+def run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks):
+    kind = args.workload.split("_", 1)[1]
+    if kind not in ("e4m3", "e5m2", "int8", "f16"):
+        raise SystemExit(f"unknown workload {args.workload}")
+    if JOB_IMAGES % world != 0:
+        raise SystemExit("the job has 8 images: 1, 2, 4 or 8 ranks")
+    harness = importlib.import_module("sdxl-end2end_b200.unet_harness")
+    sharding = importlib.import_module("sdxl-end2end_b200.sharding")
+    first, end = sharding.shard_images(JOB_IMAGES, world, rank)
+    images = end - first
+    local_batch = 2 * images
+    device = torch.device("cuda", local_rank)
+    distributed = world > 1
+
+    def barrier():
+        torch.cuda.synchronize()
+        if distributed:
+            dist.barrier()
+
+    # scratch: the largest quantised activation of a single call, and the K/V plan's shared input
+    largest = max(local_batch * 16384 * 640, local_batch * 4096 * 2560, local_batch * 1024 * 5120)
+    context = pkg.Context(local_rank, workspace_bytes=int(largest * 1.05) + (64 << 20))
+    ops = pkg.Ops(context)
+    unet = harness.UNetHarness(ops, harness.BASE_1_0, precision=kind, seed=0)
+    loop = harness.EulerDenoiser(unet, images, 1024, 1024, GENERATION_STEPS, guidance_scale=5.0, use_graph=not args.no_graph)
+
+    # the job's inputs, seeded per image so that every sharding sees the same job; host copies pinned
+    def image_tensor(shape, seed, scale=1.0):
+        generator = torch.Generator(device="cpu")
+        generator.manual_seed(seed)
+        return torch.randn(shape, generator=generator, dtype=torch.float32) * scale
+
+    mine = range(first, first + images)
+    noise = torch.stack([image_tensor((4, 128, 128), 1000 + i) for i in mine])
+    cond = torch.stack([image_tensor((77, 2048), 2000 + i) for i in mine])
+    uncond = torch.stack([image_tensor((77, 2048), 3000) for _ in mine])                 # the empty prompt, shared
+    pooled_cond = torch.stack([image_tensor((1280,), 4000 + i) for i in mine])
+    pooled_uncond = torch.stack([image_tensor((1280,), 5000) for _ in mine])
+    host = {
+        "latents": noise.pin_memory(),
+        "context": torch.cat([uncond, cond]).half().pin_memory(),
+        "pooled": torch.cat([pooled_uncond, pooled_cond]).half().pin_memory(),
+        "time_ids": torch.tensor([[1024, 1024, 0, 0, 1024, 1024]] * local_batch, dtype=torch.float16).pin_memory(),
+    }
+    staged = {name: value.to(device) for name, value in host.items()}
+    result_host = torch.empty((images, 4, 128, 128), dtype=torch.float32).pin_memory()
+    h2d_bytes = sum(v.numel() * v.element_size() for v in host.values())
+    d2h_bytes = result_host.numel() * 4
+
+    def start_generation():
+        loop.set_conditioning(staged["context"], staged["pooled"], staged["time_ids"])
+        loop.set_latents(staged["latents"])
+
+    stream = torch.cuda.current_stream()
+    start_generation()
+    for _ in range(max(args.warmup, 3)):
+        loop.step()
+    barrier()
+    # The K steps are repeated until the timed region lasts about a second (clock samples, sustained
+    # figure): estimate the step time from two more steps, agree on the count across ranks.
+    probe_start, probe_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    probe_start.record(stream)
+    loop.step()
+    loop.step()
+    probe_stop.record(stream)
+    torch.cuda.synchronize()
+    probe = torch.tensor([probe_start.elapsed_time(probe_stop) / 2], device=device)
+    if distributed:
+        dist.all_reduce(probe, op=dist.ReduceOp.MAX)
+    repeats = int(max(1, min(50, -(-args.min_seconds * 1e3 // (float(probe.item()) * args.steps)))))
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    # ---- device-resident: K steps, a new generation every 20 ------------------------------------
+    start_generation()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sampler:
+        sampler.mark_start()
+    start.record(stream)
+    for step in range(args.steps * repeats):
+        if step and step % GENERATION_STEPS == 0:
+            start_generation()
+        loop.step()
+    stop.record(stream)
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.mark_stop()
+    elapsed_ms = start.elapsed_time(stop) / repeats
+    final_latents = loop.latents.clone()
+    barrier()
+    if distributed:
+        tensor = torch.tensor([elapsed_ms], device=device)
+        dist.all_reduce(tensor, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(tensor.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = 1e3 / ms_per_step
+
+    # ---- end to end: every step copies its inputs from pinned host memory and reads its result ----
+    e2e_steps = args.e2e_steps or max(3, min(args.steps, GENERATION_STEPS))
+    def e2e_step(step):
+        for name in ("context", "pooled", "time_ids"):
+            staged[name].copy_(host[name], non_blocking=True)
+        if step % GENERATION_STEPS == 0:
+            staged["latents"].copy_(host["latents"], non_blocking=True)     # a new generation starts from noise
+            start_generation()
+        else:
+            loop.latents.copy_(result_host, non_blocking=True)              # the state the caller holds on the host
+        loop.step()
+        result_host.copy_(loop.latents, non_blocking=True)
+        torch.cuda.current_stream().synchronize()       # the caller reads the step's result
+    e2e_step(0)
+    barrier()
+    wall = time.perf_counter()
+    for step in range(e2e_steps):
+        e2e_step(step)
+    torch.cuda.synchronize()
+    e2e_seconds = time.perf_counter() - wall
+    barrier()
+    if distributed:
+        tensor = torch.tensor([e2e_seconds], device=device)
+        dist.all_reduce(tensor, op=dist.ReduceOp.MAX)
+        e2e_seconds = float(tensor.item())
+    e2e_value = e2e_steps / e2e_seconds
+    clocks = sampler.stop() if sampler else None
+
+    # ---- per-kernel times of the operator inside the loop (eager pass, event pairs per launch) ------
+    projections = unet_shapes().unet_projections(local_batch)
+    ops_per_forward = float(unet_shapes().total_ops(projections))
+    kv_ops = float(sum(2 * p.m * p.n * p.k for p in projections if ".attn2.to_k" in p.name or ".attn2.to_v" in p.name))
+    step_ops = ops_per_forward - kv_ops                          # the K/V projections run once per generation
+    eager = harness.EulerDenoiser(unet, images, 1024, 1024, GENERATION_STEPS, guidance_scale=5.0, use_graph=False)
+    eager.set_conditioning(staged["context"], staged["pooled"], staged["time_ids"])
+    eager.set_latents(staged["latents"])
+    eager.step()
+    torch.cuda.synchronize()
+    context.profile(True)
+    context.kernel_times()
+    profile_steps = 2
+    eager_start, eager_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    eager_start.record(stream)
+    for _ in range(profile_steps):
+        eager.step()
+    eager_stop.record(stream)
+    kernel_times = context.kernel_times()
+    context.profile(False)
+    eager_ms = eager_start.elapsed_time(eager_stop) / profile_steps
+    gemm_ms = kernel_times["gemm"][0] / profile_steps
+    gemm_launches = kernel_times["gemm"][1] // profile_steps
+    quant_ms = (kernel_times["quant_int8"][0] + kernel_times["quant_fp8"][0]) / profile_steps
+    quant_launches = (kernel_times["quant_int8"][1] + kernel_times["quant_fp8"][1]) // profile_steps
+    small_launches = kernel_times["small"][1] // profile_steps
+    launches_per_step = int(gemm_launches + quant_launches + small_launches)
+    # time of the K/V plan (once per generation)
+    context.profile(True)
+    context.kernel_times()
+    unet.prepare_conditioning(staged["context"])
+    kv_times = context.kernel_times()
+    context.profile(False)
+    kv_gemm_ms = kv_times["gemm"][0]
+    kv_launches = sum(v[1] for v in kv_times.values())
+    context.check()
+
+    eight_bit = kind != "f16"
+    tensor_peak = peaks["bf16_tflops"] * (2.0 if eight_bit else 1.0)
+    sustained_peak = peaks["bf16_tflops_sustained"] * (2.0 if eight_bit else 1.0)
+    achieved = step_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    # quantised inputs of one step: every projection input that is not the text context, once per key
+    quant_inputs = {}
+    for p in projections:
+        if ".attn2.to_k" in p.name or ".attn2.to_v" in p.name:
+            continue
+        quant_inputs.setdefault(p.input_key, (p.m, p.k))
+    quant_bytes = quantiser_bytes(quant_inputs.values(), kind)
+    rows_table = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in projections
+                  if not (".attn2.to_k" in p.name or ".attn2.to_v" in p.name)]
+    roofline = {
+        "bound": "tensor", "kernel": "sdxlq_umma_gemm_kernel", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
+        "frac": achieved / tensor_peak, "frac_of_sustained": achieved / sustained_peak,
+        "traffic": None,
+        "traffic_note": "not captured on this workload (a step holds several GB); see profiles/ for the ncu captures of the "
+                        "640- and 1280-dim sets. Algorithmic minimum per step below.",
+        "min_bytes_per_step": minimum_bytes(rows_table, kind),
+        "peak_source": (f"{peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s x2 for 8-bit operands; sustained "
+                        f"{peaks['bf16_tflops_sustained']} x2" if eight_bit else f"{peaks['source']} bf16"),
+        "launch_ms": gemm_ms / max(gemm_launches, 1), "gemm_ms_per_step": gemm_ms, "gemm_launches_per_step": int(gemm_launches),
+        "ops_per_step": step_ops, "ops_per_launch": step_ops / max(gemm_launches, 1),
+        "how": "CUDA event pairs around every launch of the operator, eager pass over 2 steps of the same loop on the "
+               "launching stream (the timed region replays a captured graph, where single launches cannot be bracketed)",
+        "quantize_kernel": {"bound": "hbm", "bytes_per_step": quant_bytes, "ms_per_step": quant_ms,
+                            "achieved": quant_bytes / (quant_ms * 1e-3) / 1e9 if quant_ms > 0 else None,
+                            "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": (quant_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]) if quant_ms > 0 else None},
+    }
+    projection_ms = gemm_ms + quant_ms
+    line = {
+        "metric": "sdxl_unet_steps_per_s", "value": value, "unit": "steps/s", "n_gpus": world, "steps": args.steps,
+        "repeats": repeats, "timed_region_ms": elapsed_ms * repeats,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": {"int8": "int8", "e4m3": "fp8_e4m3", "e5m2": "fp8_e5m2"}.get(kind, "f16"),
+        "data": "synthetic",
+        "config": {"workload": unetloop_description(kind), "name": args.workload, "projections_per_forward": len(projections),
+                   "images_per_rank": images, "unet_batch_per_rank": local_batch,
+                   "parallelism": f"dp{world} by image / CFG pair (replicated weights, no collective in the step)",
+                   "cuda_graph": not args.no_graph,
+                   "l2": "inputs larger than L2: one step streams the 2.2 GB of 8-bit projection weights plus its activations "
+                         f"(> {L2_BYTES / 1e6:.0f} MB L2) between repeats of any kernel",
+                   "timing": "CUDA events on the launching stream around `repeats` x K steps (region of about a second), "
+                             "divided by `repeats`, max over ranks"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "steps/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                "steps": e2e_steps, "ms_per_step": e2e_seconds / e2e_steps * 1e3},
+        "gpu_launches": repeats * (launches_per_step * args.steps + kv_launches * ((args.steps + GENERATION_STEPS - 1) // GENERATION_STEPS)),
+        "launches_per_step": launches_per_step,
+        "projection_tops_per_gpu": step_ops / (projection_ms * 1e-3) / 1e12 if projection_ms > 0 else None,
+        "projection_gemm_tops_per_gpu": achieved,
+        "projection_share_of_step": projection_ms / ms_per_step if ms_per_step > 0 else None,
+        "projection_ms_per_step": {"gemm": gemm_ms, "quantize": quant_ms},
+        "eager_ms_per_step": eager_ms,
+        "kv_cache": {"gemm_ms_per_generation": kv_gemm_ms, "ops": kv_ops, "launches": int(kv_launches)},
+        "roofline": roofline,
+        "library": pkg.load_library().sdxlq_build_info().decode(),
+    }
+
+    # ---- the final latents of every rank gathered on rank 0 (the only collective; outside the step) ----
+    if distributed:
+        gathered = [torch.empty_like(final_latents) for _ in range(world)] if rank == 0 else None
+        dist.gather(final_latents, gathered, dst=0)
+        if rank == 0:
+            line["final_latents"] = {"shape": [JOB_IMAGES, 4, 128, 128], "finite": bool(torch.isfinite(torch.cat(gathered)).all()),
+                                     "abs_mean": float(torch.cat(gathered).abs().mean())}
+    else:
+        line["final_latents"] = {"shape": [JOB_IMAGES, 4, 128, 128], "finite": bool(torch.isfinite(final_latents).all()),
+                                 "abs_mean": float(final_latents.abs().mean())}
+    unet.close()
+    return line, context, ops
 
 
 # ------------------------------------------------------------------------------------------------
@@ -335,37 +752,39 @@ def main():
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=None)
     parser.add_argument("--warmup", type=int, default=None)
-    parser.add_argument("--workload", default="layerset640_int8")
+    parser.add_argument("--workload", default="unetloop_e4m3")
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    parser.add_argument("--reference-rows", type=int, default=256)
+    parser.add_argument("--reference-rows", type=int, default=None)
     parser.add_argument("--e2e-steps", type=int, default=None)
+    parser.add_argument("--min-seconds", type=float, default=1.0, help="the K steps are repeated until the timed region lasts this long")
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--library-rate", action="store_true",
-                        help="also time the vendor library's plain INT8 GEMM (context for the roofline; off by default so "
-                             "that the default run launches this repository's kernels only)")
+    parser.add_argument("--no-other-workloads", action="store_true")
+    parser.add_argument("--no-graph", action="store_true", help="run the UNet loop eagerly instead of replaying a captured step")
+    parser.add_argument("--no-library", action="store_true", help="skip the vendor-library comparison on the same shapes")
     args = parser.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    rows, kind, description = workload_rows(args.workload)
+    loop = args.workload.startswith("unetloop_")
 
     if args.impl == "reference":
         if args.steps is None:
             args.steps = 5
         if args.warmup is None:
             args.warmup = 1
+        args.steps = min(args.steps, 20)
         if rank == 0:
-            print(json.dumps(reference_arm(args, rows, description)), flush=True)
+            print(json.dumps(reference_arm(args)), flush=True)
         return 0
 
     import torch
     import torch.distributed as dist
 
     if args.steps is None:
-        args.steps = 2000 if args.workload.startswith("layerset") else (20 if args.workload.startswith("unetstep_") else 200)
+        args.steps = GENERATION_STEPS if loop else 0
     if args.warmup is None:
-        args.warmup = 20
+        args.warmup = 3
     args.warmup = max(args.warmup, 3)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
@@ -375,17 +794,42 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    pkg = importlib.import_module("sdxl-end2end_b200")
+    pkg = package()
     peaks = load_peaks()
-    sets = 3 if args.workload.startswith("layerset") else 1
-    # scratch for the quantised copy of every distinct input of a step (bytes + per-row scales)
+
+    if loop:
+        line, context, ops = run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks)
+        if rank == 0 and world == 1 and not args.no_other_workloads:
+            others = {}
+            for name in ("layerset640_int8", "layerset640_int8_g64", "layerset1280_fp8", "geglu640_f16", "unet743_int8", "unet743_e5m2"):
+                try:
+                    others[name] = time_projection_workload(torch, pkg, context, ops, name, peaks,
+                                                            library=(not args.no_library) and name.startswith(("layerset", "geglu")))
+                except Exception as error:       # a side measurement must not lose the headline line
+                    others[name] = {"error": f"{type(error).__name__}: {error}"}
+            line["other_workloads"] = others
+        if rank == 0 and world == 1 and not args.no_cpu_baseline:
+            tops, kind, sample = cpu_single_core_rate()
+            full_ops = float(unet_shapes().total_ops(unet_shapes().unet_projections(2 * JOB_IMAGES)))
+            line["cpu_baseline"] = {"value": tops * 1e12 / full_ops, "unit": "steps/s", "cores": 1, "kind": kind,
+                                    "cpu_tops": tops,
+                                    "sample": sample + f"; converted to steps/s of the job by its {full_ops / 1e12:.2f} TOP of projections "
+                                                       "per step (projections only: an upper bound for the CPU reference's step)"}
+        else:
+            line["cpu_baseline"] = None
+        context.check()
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if distributed:
+            dist.destroy_process_group()
+        return 0
+
+    # ---- a projection-only workload as the main line ---------------------------------------------------
+    rows, kind, group, description = workload_rows(args.workload, world)
     unique_inputs = {key: (m, k) for (_, m, _, k, _, _, key) in rows}
     scratch = sum(m * k + 4 * m + 1024 for (m, k) in unique_inputs.values())
     context = pkg.Context(local_rank, workspace_bytes=max(1 << 30, int(scratch * 1.1)))
     ops = pkg.Ops(context)
-    work = DeviceWorkload(pkg, ops, rows, kind, sets)
-    ops_per_step = total_ops(rows)
-    stream = torch.cuda.current_stream()
 
     def barrier():
         torch.cuda.synchronize()
@@ -393,106 +837,42 @@ def main():
             dist.barrier()
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
-
-    # ---- device-resident throughput --------------------------------------------------------------
-    for step in range(args.warmup):
-        work.plans[step % sets].run()
     barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if sampler:
-        sampler.mark("timed_start")
-    start.record(stream)
-    for step in range(args.steps):
-        work.plans[step % sets].run()
-    stop.record(stream)
-    torch.cuda.synchronize()
+        sampler.mark_start()
+    result = time_projection_workload(torch, pkg, context, ops, args.workload, peaks, min_seconds=1.0, world=world,
+                                      library=(rank == 0 and not args.no_library))
     if sampler:
-        sampler.mark("timed_stop")
-    elapsed_ms = start.elapsed_time(stop)
+        sampler.mark_stop()
     barrier()
+    ms_per_step = result["ms_per_step"]
     if distributed:
-        tensor = torch.tensor([elapsed_ms], device="cuda")
+        tensor = torch.tensor([ms_per_step], device="cuda")
         dist.all_reduce(tensor, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(tensor.item())
-    value = world * ops_per_step * args.steps / (elapsed_ms * 1e-3) / 1e12
+        ms_per_step = float(tensor.item())
+    ops_per_step = result["ops_per_step"]
+    value = world * ops_per_step / (ms_per_step * 1e-3) / 1e12
 
-    # ---- per-kernel times (second pass over the same steps, event pairs around each launch) --------
-    context.profile(True)
-    context.kernel_times()
-    for step in range(args.steps):
-        work.plans[step % sets].run()
-    kernel_times = context.kernel_times()
-    context.profile(False)
-    gemm_ms, gemm_launches = kernel_times["gemm"]
-    quant_ms = kernel_times["quant_int8"][0] + kernel_times["quant_fp8"][0]
-    quant_launches = kernel_times["quant_int8"][1] + kernel_times["quant_fp8"][1]
-    gemm_launches_per_step = max(gemm_launches // max(args.steps, 1), 1)
-    gemm_ms_per_launch = gemm_ms / max(args.steps, 1)      # all GEMM launches of one step together
-    eight_bit = kind in ("int8", "e4m3", "e5m2")
-    tensor_peak = peaks["bf16_tflops"] * (2.0 if eight_bit else 1.0)
-    achieved = ops_per_step / (gemm_ms_per_launch * 1e-3) / 1e12 if gemm_ms_per_launch > 0 else 0.0
-    quant_bytes = sum((m * k * 3 + (4 * m if kind == "int8" else 0)) for (m, k) in work.input_shapes.values()) if eight_bit else 0
-    quant_ms_per_step = quant_ms / max(args.steps, 1)
-    quant_gbs = quant_bytes / (quant_ms_per_step * 1e-3) / 1e9 if (quant_bytes and quant_ms_per_step > 0) else 0.0
-    roofline = {
-        "bound": "tensor", "kernel": "sdxlq_umma_gemm_kernel", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
-        "frac": achieved / tensor_peak, "traffic": TRAFFIC_BYTES.get(args.workload),
-        "peak_source": (f"{peaks['source']} bf16 {peaks['bf16_tflops']} TFLOP/s x2 for 8-bit operands" if eight_bit
-                        else f"{peaks['source']} bf16"),
-        "launch_ms": gemm_ms_per_launch, "ops_per_launch": ops_per_step, "gemm_launches_per_step": gemm_launches_per_step,
-        "quantize_kernel": {"bound": "hbm", "achieved": quant_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                            "bytes_per_step": quant_bytes, "ms_per_step": quant_ms_per_step},
-    }
-    roofline["quantize_kernel"]["frac"] = roofline["quantize_kernel"]["achieved"] / peaks["hbm_gbs"]
-    if rank == 0 and kind == "int8" and args.library_rate:
-        roofline["library_int8_gemm"] = library_int8_rate(torch)
+    # end to end: pinned host inputs -> device, plan, results -> pinned host
+    work = DeviceWorkload(pkg, ops, rows, kind, group, 1)
+    e2e_value, e2e_ms, e2e_steps = None, None, 0
+    if work.h2d_bytes + work.d2h_bytes <= (8 << 30):
+        e2e_steps = args.e2e_steps or 10
+        host_inputs = {key: torch.empty(x.shape, dtype=x.dtype).pin_memory().copy_(x) for key, x in work.inputs[0].items()}
+        host_outputs = [torch.empty(y.shape, dtype=y.dtype).pin_memory() for y in work.outputs[0]]
 
-    # ---- end to end: pinned host inputs -> device, run, results -> pinned host ----------------------
-    # (skipped when one step moves more than 16 GB over PCIe: pinned host copies of that size are not
-    # what this measurement is for; only the sharded UNet-step workloads are that large)
-    e2e_skipped = work.h2d_bytes + work.d2h_bytes > (16 << 30)
-    e2e_value, e2e_seconds, e2e_steps = None, 0.0, 0
-    if not e2e_skipped:
-        e2e_steps = args.e2e_steps or max(3, min(args.steps, 20))
-        host_inputs = [{key: torch.empty(x.shape, dtype=x.dtype).pin_memory().copy_(x) for key, x in work.inputs[s].items()}
-                       for s in range(min(sets, 2))]
-        host_outputs = [[torch.empty(y.shape, dtype=y.dtype).pin_memory() for y in work.outputs[s]] for s in range(min(sets, 2))]
-        copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
-        # Per buffer set: inputs uploaded / plan finished / outputs downloaded. The upload of step i + 1
-        # waits only for the plan that last read its input buffers, so it overlaps the download of step
-        # i (PCIe is full duplex); the plan waits for its inputs and for the download that last read
-        # its output buffers.
-        uploaded = [torch.cuda.Event() for _ in host_inputs]
-        computed = [torch.cuda.Event() for _ in host_inputs]
-        downloaded = [torch.cuda.Event() for _ in host_inputs]
-        for s in range(len(host_inputs)):
-            computed[s].record(stream)
-            downloaded[s].record(copy_out)
-
-        def e2e_step(step):
-            s = step % len(host_inputs)
-            with torch.cuda.stream(copy_in):
-                copy_in.wait_event(computed[s])
-                for key, host in host_inputs[s].items():
-                    work.inputs[s][key].copy_(host, non_blocking=True)
-                uploaded[s].record(copy_in)
-            stream.wait_event(uploaded[s])
-            stream.wait_event(downloaded[s])
-            work.plans[s].run()
-            computed[s].record(stream)
-            with torch.cuda.stream(copy_out):
-                copy_out.wait_event(computed[s])
-                for host, y in zip(host_outputs[s], work.outputs[s]):
-                    host.copy_(y, non_blocking=True)
-                downloaded[s].record(copy_out)
-
-        for step in range(2):
-            e2e_step(step)
+        def e2e_step():
+            for key, hostbuf in host_inputs.items():
+                work.inputs[0][key].copy_(hostbuf, non_blocking=True)
+            work.plans[0].run()
+            for hostbuf, y in zip(host_outputs, work.outputs[0]):
+                hostbuf.copy_(y, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        e2e_step()
         barrier()
         wall = time.perf_counter()
-        for step in range(e2e_steps):
-            e2e_step(step)
-        torch.cuda.synchronize()
+        for _ in range(e2e_steps):
+            e2e_step()
         e2e_seconds = time.perf_counter() - wall
         barrier()
         if distributed:
@@ -500,37 +880,38 @@ def main():
             dist.all_reduce(tensor, op=dist.ReduceOp.MAX)
             e2e_seconds = float(tensor.item())
         e2e_value = world * ops_per_step * e2e_steps / e2e_seconds / 1e12
+        e2e_ms = e2e_seconds / e2e_steps * 1e3
     context.check()
-
     clocks = sampler.stop() if sampler else None
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu_baseline = cpu_single_core_baseline()
-
+        tops, cpu_kind, sample = cpu_single_core_rate()
+        cpu_baseline = {"value": tops, "unit": "TOPS", "cores": 1, "kind": cpu_kind, "sample": sample}
     if rank == 0:
+        gemm = result["gemm"]
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "metric": "quantized_linear_tops", "value": value, "unit": "TOPS", "n_gpus": world, "steps": result["steps_timed"],
+            "warmup": 6, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if args.workload.startswith("unetstep_") else "weak", "vs_baseline": None,
             "dtype": {"int8": "int8", "e4m3": "fp8_e4m3", "e5m2": "fp8_e5m2"}.get(kind, "f16"), "data": "synthetic",
-            "config": {"workload": description, "name": args.workload, "projections": len(rows),
-                       "ops_per_step": ops_per_step, "parallelism": f"dp{world} (replicated weights, no collective)",
-                       "l2": (f"{sets} rotating input/output sets, {sets * work.working_set / 1e6:.0f} MB touched per cycle "
-                              f"(> {L2_BYTES / 1e6:.0f} MB L2)") if sets > 1 else
-                             f"working set {work.working_set / 1e6:.0f} MB per step (> {L2_BYTES / 1e6:.0f} MB L2)",
-                       "timing": "CUDA events on the launching stream, max over ranks"},
+            "config": {"workload": description, "name": args.workload, "projections": len(rows), "ops_per_step": ops_per_step,
+                       "parallelism": f"dp{world} (replicated weights, no collective)", "l2": result["l2"],
+                       "timing": "CUDA events on the launching stream, max over ranks; steps sized for a timed region of >= 1 s"},
             "clocks": clocks,
-            **({"unet_steps_per_s_projections_only": 1e3 / (elapsed_ms / args.steps)} if args.workload.startswith("unetstep_") else {}),
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": work.h2d_bytes, "d2h_bytes_per_step": work.d2h_bytes,
-                    "steps": e2e_steps, "ms_per_step": (e2e_seconds / e2e_steps * 1e3) if e2e_steps else None},
-            "gpu_launches": work.launches_per_step() * args.steps,
-            "launches_per_step": work.launches_per_step(),
-            "roofline": roofline,
-            "kernel_ms_per_step": {name: times[0] / args.steps for name, times in kernel_times.items()},
+            "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": work.h2d_bytes, "d2h_bytes_per_step": work.d2h_bytes,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms},
+            "gpu_launches": result["launches_per_step"] * result["steps_timed"], "launches_per_step": result["launches_per_step"],
+            "roofline": {"bound": "tensor", "kernel": "sdxlq_umma_gemm_kernel", "achieved": gemm["tops"], "peak": gemm["peak_tflops"],
+                         "unit": "TFLOP/s", "frac": gemm["frac_of_peak"], "traffic": None, "min_bytes": gemm["min_bytes"],
+                         "launch_ms": gemm["ms"], "ops_per_launch": ops_per_step,
+                         "peak_source": f"{peaks['source']} bf16 {peaks['bf16_tflops']} TFLOP/s" + (" x2 for 8-bit operands" if kind != "f16" else ""),
+                         "quantize_kernel": result["quantize"]},
+            "library_same_shapes": result.get("library_same_shapes"),
             "cpu_baseline": cpu_baseline,
             "library": pkg.load_library().sdxlq_build_info().decode(),
         }
         print(json.dumps(line), flush=True)
+    work.close()
     if distributed:
         dist.destroy_process_group()
     return 0

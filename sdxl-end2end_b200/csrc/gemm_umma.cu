@@ -475,11 +475,94 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
     }
 }
 
+// The same arithmetic without software pipelining: one chunk at a time, tensor-memory load, wait,
+// finish, store. It needs far fewer registers, which is what lets 16 epilogue warps (four per
+// scheduler) share the SM: with that many warps the scheduler hides the load and arithmetic
+// latencies by switching warps instead of by interleaving two chunks inside one warp.
+template <uint32_t Kind, uint32_t Act>
+__device__ __forceinline__ void epilogue_tile_lean(const EpilogueTile& t) {
+    const bool row_ok = (t.flags & 1u) != 0;
+    const bool has_bias = (t.flags & 2u) != 0;
+    const bool store_vector = (t.flags & 4u) != 0;
+    const bool store_wide = (t.flags & 8u) != 0;
+    const float2 a_scale = make_float2(t.a_scale, t.a_scale);
+    int32_t* const acc_out = Kind == KIND_I8 ? t.acc_out : nullptr;
+    constexpr uint32_t kStride = kWarpsPerQuadrant * 16u;
+    if (Act != ACT_GEGLU) {
+        const uint32_t limit = min(t.tile_n, t.n > t.n0 ? t.n - t.n0 : 0u);
+        const __half* const residual = Act == ACT_NONE ? t.residual : nullptr;
+        const bool with_residual = residual != nullptr && row_ok;
+        for (uint32_t c = t.chunk_first * 16u; c < limit; c += kStride) {
+            const uint32_t col0 = t.n0 + c;
+            uint32_t acc[16];
+            uint32_t extra[8] = {};
+            ptx::tmem_ld_32x32b_x16(t.tmem_row + c, acc);
+            if (with_residual) load_row_16(residual, t.n_out, store_vector, store_wide, t.row, col0, extra);
+            ptx::tmem_ld_wait(acc);
+            if (acc_out != nullptr && row_ok) {
+                int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n + col0;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (col0 + i < t.n) raw[i] = static_cast<int32_t>(acc[i]);
+                }
+            }
+            uint32_t out_words[8];
+            finish_chunk_16<Kind, Act>(t, c, acc, a_scale, has_bias, out_words);
+            if (Act == ACT_NONE && with_residual) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const __half2 sum = __hadd2(*reinterpret_cast<const __half2*>(&out_words[i]),
+                                                *reinterpret_cast<const __half2*>(&extra[i]));
+                    out_words[i] = *reinterpret_cast<const uint32_t*>(&sum);
+                }
+            }
+            if (row_ok) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
+        }
+    } else {
+        const uint32_t half = t.tile_n / 2;
+        const uint32_t limit = min(half, t.n_out > t.n0 ? t.n_out - t.n0 : 0u);
+        for (uint32_t c0 = t.chunk_first * 16u; c0 < limit; c0 += kStride) {
+            const uint32_t col0 = t.n0 + c0;
+            uint32_t out_words[8];
+#pragma unroll
+            for (uint32_t step = 0; step < 2; ++step) {
+                uint32_t value[8], gate[8];
+                ptx::tmem_ld_32x32b_x8(t.tmem_row + c0 + 8u * step, value);
+                ptx::tmem_ld_32x32b_x8(t.tmem_row + half + c0 + 8u * step, gate);
+                ptx::tmem_ld_wait(value, gate);
+                if (acc_out != nullptr && row_ok) {
+                    int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        if (col0 + 8u * step + i < t.n_out) {
+                            raw[col0 + 8u * step + i] = static_cast<int32_t>(value[i]);
+                            raw[t.n_out + col0 + 8u * step + i] = static_cast<int32_t>(gate[i]);
+                        }
+                    }
+                }
+                finish_geglu_8<Kind>(t, c0 + 8u * step, half, value, gate, a_scale, out_words + 4 * step);
+            }
+            if (row_ok) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
+        }
+    }
+}
+
+// Epilogue strategy: software-pipelined chunks with few warps, plain chunks with many.
+#ifndef SDXLQ_LEAN_EPILOGUE
+#define SDXLQ_LEAN_EPILOGUE (SDXLQ_EPILOGUE_WARPS >= 16)
+#endif
+
 template <uint32_t Kind>
 __device__ __forceinline__ void epilogue_dispatch(uint32_t activation, const EpilogueTile& t) {
+#if SDXLQ_LEAN_EPILOGUE
+    if (activation == ACT_NONE) epilogue_tile_lean<Kind, ACT_NONE>(t);
+    else if (activation == ACT_GEGLU) epilogue_tile_lean<Kind, ACT_GEGLU>(t);
+    else epilogue_tile_lean<Kind, kActRuntime>(t);
+#else
     if (activation == ACT_NONE) epilogue_tile<Kind, ACT_NONE>(t);
     else if (activation == ACT_GEGLU) epilogue_tile<Kind, ACT_GEGLU>(t);
     else epilogue_tile<Kind, kActRuntime>(t);
+#endif
 }
 
 }  // namespace

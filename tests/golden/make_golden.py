@@ -1,4 +1,4 @@
-"""Generates tests/golden/reference_dense.npz by running the UNMODIFIED reference CPU Linear
+"""Generates tests/golden/reference_dense.npz and tests/golden/config1_rows.npz by running the UNMODIFIED reference CPU Linear
 (`linear_2d` + `geglu`, src/unet.cpp:202-235, 483-493 of the reference, reached through
 oracle/_ref/libsdxl_ref.so) on seeded inputs shaped like the GEGLU feed-forward projection
 (K = 640, a slice of N = 5120) and on FP8-stored weights. Run from the repository root in a
@@ -37,6 +37,20 @@ def main() -> None:
         out[f"linear_2d_{name}"] = O.ref_linear_2d(x8.astype(np.float32), wq, None, fp8_fmt=fmt)
     path = os.path.join(ROOT, "tests", "golden", "reference_dense.npz")
     np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+    # The first benchmark configuration at full size: X [8192, 640] x W [5120, 640] + bias, GEGLU,
+    # FP16 weights. 40 rows spread over the 64 row tiles, each a full output row of the reference's
+    # linear_2d + geglu (inputs are regenerated from the seed by the test, only rows and results are
+    # stored).
+    seed = 4242
+    x = H.make_activations(seed, 8192, 640)
+    w = H.make_weight(seed, 5120, 640)
+    bias = H.make_bias(seed, 5120)
+    rows = np.unique(np.concatenate([[0, 127, 128, 8191], np.random.default_rng(seed).integers(0, 8192, size=36)]))
+    result = O.ref_geglu(O.ref_linear_2d(x[rows].astype(np.float32), w, bias))
+    path = os.path.join(ROOT, "tests", "golden", "config1_rows.npz")
+    np.savez_compressed(path, seed=np.int64(seed), rows=rows.astype(np.int64), out=result.astype(np.float32))
     print("wrote", path, os.path.getsize(path), "bytes")
 
 

@@ -1,0 +1,136 @@
+"""GPU tests of the synthetic UNet loop: the executor with the real operator behind every
+projection against the reference's own CPU UNet (SDXLUNet::forward compiled from the reference
+sources into oracle/_ref), graph replay against eager execution, and sharding by image."""
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+harness = importlib.import_module("sdxl-end2end_b200.unet_harness")
+
+MINIATURE = harness.UNetConfig(channels=(64, 128, 256), heads=(1, 2, 4), transformer_depth=(1, 1, 2),
+                               cross_attention_dim=96, time_embed_dim=128, addition_time_embed_dim=8,
+                               addition_input_dim=80, layers_per_block=2, norm_groups=32)
+
+
+def config_tuple(c):
+    return (c.channels, c.heads, c.transformer_depth, c.cross_attention_dim, c.time_embed_dim,
+            c.addition_time_embed_dim, c.addition_input_dim, c.layers_per_block, c.norm_groups)
+
+
+def inputs(batch, size=16, seed=5):
+    rng = np.random.default_rng(seed)
+    h = lambda a: a.astype(np.float16).astype(np.float32)
+    latents = h(rng.standard_normal((batch, 4, size, size), dtype=np.float32))
+    context = h(rng.standard_normal((batch, 77, MINIATURE.cross_attention_dim), dtype=np.float32))
+    pooled = h(rng.standard_normal((batch, MINIATURE.pooled_dim), dtype=np.float32))
+    time_ids = np.tile(np.array([[128, 128, 0, 0, 128, 128]], np.float32), (batch, 1))
+    return latents, context, pooled, time_ids
+
+
+def parameters(seed=3):
+    values = harness.synthetic_parameters(MINIATURE, torch.device("cuda"), seed=seed)
+    return {name: value.to(torch.float16).to(torch.float32) for name, value in values.items()}
+
+
+def run_forward(ops, precision, params, data, **options):
+    latents, context, pooled, time_ids = data
+    unet = harness.UNetHarness(ops, MINIATURE, precision=precision, parameters=params, **options)
+    unet.prepare_conditioning(torch.from_numpy(context).cuda().half())
+    out = unet.forward(torch.from_numpy(latents).cuda().half(), 801.0, torch.from_numpy(pooled).cuda().half(),
+                       torch.from_numpy(time_ids).cuda().half())
+    ops.ctx.check()
+    calls = unet.projection_calls
+    unet.close()
+    return out.float().cpu().numpy(), calls
+
+
+@pytest.mark.skipif(not O.ref_available(), reason="oracle/_ref was not built")
+@pytest.mark.parametrize("precision,tolerance", [("f16", 2e-2), ("e4m3", 1.5e-1), ("int8", 8e-2)])
+def test_forward_matches_the_reference_cpu_unet(gpu, precision, tolerance):
+    """All projections on the tensor-core path, everything else PyTorch FP16, against the
+    reference's FP32 CPU executor on the same FP16-representable parameters. The FP16 profile differs
+    only by FP16 rounding of the activations; the quantised profiles add their quantisation error
+    (random weights, so it does not average out over channels the way a trained model's does)."""
+    pkg, ctx, ops = gpu
+    params = parameters()
+    data = inputs(2)
+    got, calls = run_forward(ops, precision, params, data)
+    reference = O.RefUNet(config_tuple(MINIATURE))
+    reference.bind({name: value.cpu().numpy() for name, value in params.items()})
+    want = reference.forward(data[0], 801.0, data[1], data[2], data[3])
+    reference.close()
+    count = sum(1 for name, shape in harness.unet_parameter_shapes(MINIATURE).items() if harness.is_projection_weight(name, shape))
+    assert calls == count
+    scale = float(np.max(np.abs(want)))
+    error = float(np.max(np.abs(got - want))) / scale
+    rms = float(np.sqrt(np.mean((got - want) ** 2)) / np.sqrt(np.mean(want ** 2)))
+    print(f"{precision}: max|a-b|/max|b| = {error:.3e}, rms rel = {rms:.3e}")
+    assert np.isfinite(got).all() and error <= tolerance
+
+
+@pytest.mark.parametrize("precision", ["int8", "e4m3"])
+def test_fused_residual_and_grouping_do_not_change_results(gpu, precision):
+    """Residual add in the epilogue and grouped q/k/v against the call-by-call form of the reference
+    (separate Linear, then add_in_place): bit-identical."""
+    pkg, ctx, ops = gpu
+    params = parameters(7)
+    data = inputs(2, seed=8)
+    fused, _ = run_forward(ops, precision, params, data)
+    plain, _ = run_forward(ops, precision, params, data, fuse_residual=False, group_attention_inputs=False)
+    assert np.array_equal(fused, plain)
+
+
+def test_graph_replay_equals_eager_loop(gpu):
+    pkg, ctx, ops = gpu
+    params = parameters(9)
+    latents, context, pooled, time_ids = inputs(2 * 2, seed=10)
+    results = []
+    for use_graph in (False, True):
+        unet = harness.UNetHarness(ops, MINIATURE, precision="e4m3", parameters=params)
+        loop = harness.EulerDenoiser(unet, 2, height=128, width=128, steps=4, use_graph=use_graph)
+        loop.set_conditioning(torch.from_numpy(context).cuda().half(), torch.from_numpy(pooled).cuda().half(),
+                              torch.from_numpy(time_ids).cuda().half())
+        loop.set_latents(torch.from_numpy(latents[:2]).cuda())
+        results.append(loop.run().clone())
+        # a second generation through the same (captured) step
+        loop.set_latents(torch.from_numpy(latents[2:]).cuda())
+        results.append(loop.run().clone())
+        torch.cuda.synchronize()
+        ctx.check()
+        unet.close()
+    assert torch.isfinite(results[0]).all()
+    assert torch.equal(results[0], results[2]) and torch.equal(results[1], results[3])
+
+
+def test_sharding_by_image_keeps_each_image(gpu):
+    """Two images denoised together ([uncond x 2 | cond x 2]) against each image on its own
+    ([uncond | cond]), as ranks of a 2-GPU run would hold them. INT8 activations are scaled per token,
+    so the projections are bit-identical per image; the PyTorch scaffolding (cuDNN, attention) may
+    pick different kernels for different batch sizes, hence a tolerance instead of equality."""
+    pkg, ctx, ops = gpu
+    params = parameters(11)
+    latents, context, pooled, time_ids = inputs(4, seed=12)       # rows 0-1 uncond, 2-3 cond of images 0, 1
+
+    def denoise(image_rows, cond_rows):
+        images = len(image_rows)
+        unet = harness.UNetHarness(ops, MINIATURE, precision="int8", parameters=params)
+        loop = harness.EulerDenoiser(unet, images, height=128, width=128, steps=3, use_graph=False)
+        rows = image_rows + cond_rows
+        loop.set_conditioning(torch.from_numpy(context[rows]).cuda().half(), torch.from_numpy(pooled[rows]).cuda().half(),
+                              torch.from_numpy(time_ids[rows]).cuda().half())
+        loop.set_latents(torch.from_numpy(latents[image_rows]).cuda())
+        out = loop.run().clone()
+        ctx.check()
+        unet.close()
+        return out
+
+    together = denoise([0, 1], [2, 3])
+    alone = torch.cat([denoise([0], [2]), denoise([1], [3])])
+    scale = float(together.abs().max())
+    assert float((together - alone).abs().max()) <= 2e-2 * scale
