@@ -254,35 +254,47 @@ def time_projection_workload(torch, pkg, context, ops, name, peaks, min_seconds=
               else f"working set {work.working_set / 1e6:.0f} MB per step",
     }
     if library:
-        result["library_same_shapes"] = library_same_shapes(torch, rows, kind, work)
+        result["library_same_shapes"] = library_same_shapes(torch, ops, rows, kind, work)
     work.close()
     del work
     torch.cuda.empty_cache()
     return result
 
 
-def library_same_shapes(torch, rows, kind, work):
-    """The reference's launch structure with the vendor library's GEMM on the same shapes: per
-    projection a quantise step, a cuBLASLt GEMM (torch._int_mm = I8 x I8 -> I32 for INT8, as
-    int8_convrot_linear calls it, src/cuda/int8_convrot.cu:634-698; torch._scaled_mm = FP8 x FP8 -> FP16
-    with device scales, as native_fp8_linear does, src/cuda/ops_blas.cpp:153-225), then the separate
-    dequantise / bias / GEGLU kernels the reference runs afterwards (ops_blas.cpp:388-397). The
-    quantise step here is a plain absmax + cast in PyTorch (no rotation), which only flatters the
-    library arm. Timed with CUDA events, outside this benchmark's timed region."""
+def library_same_shapes(torch, ops, rows, kind, work):
+    """The vendor library's GEMM in place of this repository's GEMM kernel, on the same shapes and on
+    the same quantised activations (produced beforehand by this repository's quantiser, not timed):
+    per projection one cuBLASLt GEMM (torch._int_mm = I8 x I8 -> I32 for INT8, as int8_convrot_linear
+    calls it, src/cuda/int8_convrot.cu:634-698; torch._scaled_mm = FP8 x FP8 -> FP16 with tensor-wide
+    device scales, as native_fp8_linear does, src/cuda/ops_blas.cpp:153-225; a plain FP16 matmul), then
+    the separate kernels the reference runs after it: dequantise (int8_convrot.cu:388-402), bias,
+    bias + GEGLU (ops_blas.cpp:388-397). Compare `ms_per_step` with this repository's GEMM kernel time
+    (`gemm.ms`), which includes all of that in its epilogue. CUDA events, outside the timed region."""
     import torch.nn.functional as F
     try:
         prepared = []
+        quantised = {}
         for index, (name, m, n, k, bias, activation, key) in enumerate(rows):
             x = work.inputs[0][key]
             w = work.weights[index]
             b = work.biases[index]
             if kind == "int8":
-                prepared.append((x, w.data, w.scales, b, activation, m))
+                tag = (key, w.convrot_group_size)
+                if tag not in quantised:
+                    quantised[tag] = ops.quantize_int8(x, w.convrot_group_size)
+                xq, a_scales = quantised[tag]
+                prepared.append((xq, a_scales, w.data, w.scales, b, activation, m))
             elif kind in ("e4m3", "e5m2"):
                 dtype = torch.float8_e4m3fn if kind == "e4m3" else torch.float8_e5m2
-                prepared.append((x, w.data.view(dtype), w.scales, b, activation, m))
+                if key not in quantised:
+                    q = ops.quantize_fp8(x, w.type)
+                    quantised[key] = (q.data.view(dtype), q.scales)
+                xq, a_scale = quantised[key]
+                prepared.append((xq, a_scale, w.data.view(dtype), w.scales, b, activation, m))
             else:
-                prepared.append((x, w.data, None, b, activation, m))
+                prepared.append((x, None, w.data, None, b, activation, m))
+        torch.cuda.synchronize()
+        one = torch.ones((), device="cuda")
 
         def epilogue(y, b, activation):
             if activation == 4:
@@ -291,44 +303,43 @@ def library_same_shapes(torch, rows, kind, work):
                 return value * F.gelu(gate)
             return y + b if b is not None else y
 
+        skipped = []
+
         def step():
             outs = []
-            for x, w, scales, b, activation, m in prepared:
+            for xq, a_scale, w, w_scales, b, activation, m in prepared:
                 if kind == "int8":
                     if m <= 16:
-                        continue                          # _int_mm needs more than 16 rows; the embeddings carry no work
-                    amax = x.abs().amax(dim=1, keepdim=True).float().clamp_min(1e-30)
-                    xq = torch.round(x.float() * (127.0 / amax)).clamp_(-128, 127).to(torch.int8)
-                    acc = torch._int_mm(xq, w.t())
-                    y = (acc.float() * (amax / 127.0) * scales[None, :]).half()
-                elif kind in ("e4m3", "e5m2"):
-                    limit = 448.0 if kind == "e4m3" else 57344.0
-                    scale = (x.abs().amax().float() / limit).clamp_min(1e-12)
-                    xq = (x.float() / scale).to(w.dtype)
-                    if m % 16 or w.shape[0] % 16 or w.shape[1] % 16:
+                        skipped.append(m)                 # _int_mm needs more than 16 rows
                         continue
-                    # tensor-wide scales inside the GEMM (what the reference passes to cuBLASLt); the
-                    # per-output-channel weight scale is one more elementwise pass
-                    y = torch._scaled_mm(xq, w.t(), scale_a=scale.reshape(()), scale_b=torch.ones((), device=x.device),
-                                         out_dtype=torch.float16) * scales[None, :].half()
+                    acc = torch._int_mm(xq, w.t())
+                    y = (acc.float() * a_scale[:, None] * w_scales[None, :]).half()
+                elif kind in ("e4m3", "e5m2"):
+                    if m % 16 or w.shape[0] % 16 or w.shape[1] % 16:
+                        skipped.append(m)                 # the library's FP8 GEMM wants multiples of 16
+                        continue
+                    y = torch._scaled_mm(xq, w.t(), scale_a=a_scale.reshape(()), scale_b=one, out_dtype=torch.float16)
+                    y = y * w_scales[None, :].half()      # per-output-channel weight scale: one more pass
                 else:
-                    y = x @ w.t()
+                    y = xq @ w.t()
                 outs.append(epilogue(y, b, activation))
             return outs
 
         for _ in range(3):
             step()
         torch.cuda.synchronize()
+        skipped.clear()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        repeats = 10
+        repeats = 20
         start.record()
         for _ in range(repeats):
             step()
         stop.record()
         torch.cuda.synchronize()
         ms = start.elapsed_time(stop) / repeats
-        return {"ms_per_step": ms, "tops": total_ops(rows) / (ms * 1e-3) / 1e12,
-                "what": "PyTorch quantise + cuBLASLt GEMM (torch._int_mm / torch._scaled_mm) + separate dequant, bias, GEGLU kernels"}
+        return {"ms_per_step": ms, "tops": total_ops(rows) / (ms * 1e-3) / 1e12, "projections_skipped": len(skipped) // repeats,
+                "what": "cuBLASLt GEMM (torch._int_mm / torch._scaled_mm / matmul) + separate dequant, bias, GEGLU kernels on "
+                        "activations quantised beforehand; to be compared with gemm.ms"}
     except Exception as error:      # context only: the benchmark does not depend on the library arm
         return {"ms_per_step": None, "tops": None, "what": f"library arm unavailable: {type(error).__name__}: {error}"}
 
@@ -801,12 +812,19 @@ def main():
         line, context, ops = run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks)
         if rank == 0 and world == 1 and not args.no_other_workloads:
             others = {}
+            # the loop is done with its buffers: give the memory back, and use a context whose scratch holds the
+            # quantised copy of every input of a whole-UNet plan
+            torch.cuda.empty_cache()
+            side_context = pkg.Context(local_rank, workspace_bytes=3 << 30)
+            side_ops = pkg.Ops(side_context)
             for name in ("layerset640_int8", "layerset640_int8_g64", "layerset1280_fp8", "geglu640_f16", "unet743_int8", "unet743_e5m2"):
                 try:
-                    others[name] = time_projection_workload(torch, pkg, context, ops, name, peaks,
+                    others[name] = time_projection_workload(torch, pkg, side_context, side_ops, name, peaks,
                                                             library=(not args.no_library) and name.startswith(("layerset", "geglu")))
                 except Exception as error:       # a side measurement must not lose the headline line
                     others[name] = {"error": f"{type(error).__name__}: {error}"}
+            side_context.check()
+            side_context.close()
             line["other_workloads"] = others
         if rank == 0 and world == 1 and not args.no_cpu_baseline:
             tops, kind, sample = cpu_single_core_rate()

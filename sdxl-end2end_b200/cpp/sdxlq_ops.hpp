@@ -135,6 +135,33 @@ public:
         return run(input, weight, &bias, activation);
     }
 
+    // Ops::linear followed by Ops::add_in_place(hidden, result) as the reference's transformer block
+    // issues them (src/cuda/unet.cpp:114-118, 128-132, 143-147, 174-179), in one call: the FP16 add
+    // runs in the projection's epilogue and `hidden` is updated in place.
+    void linear_add_in_place(TensorRef& hidden, const TensorRef& input, const TensorRef& weight,
+                             const TensorRef* bias = nullptr) const {
+        TensorRef output = hidden;
+        sdxlq_linear_desc desc = describe(input, weight, bias, LinearActivation::None, output, /*allocate_output=*/false);
+        if (output.shape != hidden.shape || hidden.type != ScalarType::Float16) throw CudaError("CUDA add requires matching FP16 tensors");
+        desc.y = hidden.data;
+        desc.residual = hidden.data;
+        runtime_->check(sdxlq_linear(runtime_->context(), &desc));
+    }
+
+    // Up to four projections of the same input in one launch per kernel kind and one quantisation of
+    // the input: to_q / to_k / to_v of a transformer block (src/cuda/unet.cpp:110-112). Nothing is
+    // allocated besides the outputs; the call can be recorded by a stream capture.
+    [[nodiscard]] std::vector<TensorRef> linear_group(const TensorRef& input, const std::vector<const TensorRef*>& weights) const {
+        std::vector<TensorRef> outputs(weights.size());
+        std::vector<sdxlq_linear_desc> descs;
+        descs.reserve(weights.size());
+        for (std::size_t i = 0; i < weights.size(); ++i) {
+            descs.push_back(describe(input, *weights[i], nullptr, LinearActivation::None, outputs[i]));
+        }
+        runtime_->check(sdxlq_linear_grouped(runtime_->context(), descs.data(), descs.size()));
+        return outputs;
+    }
+
     // Ops::quantize_fp8 / quantize_e4m3 / quantize_e5m2 (src/cuda/ops_blas.cpp:231-242).
     [[nodiscard]] TensorRef quantize_fp8(const TensorRef& input, ScalarType fp8_type) const {
         if (input.type != ScalarType::Float16 || !is_fp8(fp8_type)) {
@@ -209,7 +236,8 @@ private:
 
     // Validates like Ops::linear, allocates the output and fills the C descriptor.
     [[nodiscard]] sdxlq_linear_desc describe(const TensorRef& input, const TensorRef& weight, const TensorRef* bias,
-                                             LinearActivation activation, TensorRef& output) const {
+                                             LinearActivation activation, TensorRef& output,
+                                             bool allocate_output = true) const {
         // The type / role / rank checks of Ops::linear, with its messages.
         if (weight.type == ScalarType::Int8) {
             if (input.type != ScalarType::Float16 || input.role != TensorRole::Model || input.rank() < 2 ||
@@ -239,7 +267,7 @@ private:
         output.shape.back() = activation == LinearActivation::GEGLU ? n / 2 : n;
         output.type = ScalarType::Float16;
         output.role = input.role;
-        output.data = allocate_(output.elements() * sizeof(std::uint16_t));
+        output.data = allocate_output ? allocate_(output.elements() * sizeof(std::uint16_t)) : nullptr;
 
         sdxlq_linear_desc desc{};
         desc.x = input.data;

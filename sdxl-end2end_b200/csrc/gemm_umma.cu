@@ -353,134 +353,22 @@ __device__ __forceinline__ void finish_geglu_8(const EpilogueTile& t, uint32_t c
     }
 }
 
-// Drains this warp's share of one accumulator tile in chunks of 16 output columns. The tensor-
-// memory load of the next chunk is in flight while the current one is finished (two register
-// buffers used alternately).
+// Drains this warp's share of one accumulator tile in chunks of 16 output columns (the warps of a
+// TMEM lane quadrant take the chunks round-robin): tensor-memory load, wait, finish, store, one chunk
+// at a time, one output row per lane. Measured slower on B200, same GPU, same run: a
+// software-pipelined form (next chunk's load in flight while the current one is finished: larger
+// code, 7 % slower); swapping chunks between the four lanes of a quad with register shuffles so
+// that every store writes 128 contiguous bytes per row (a quarter of the memory transactions, but the
+// shuffles and selects cost more issue slots than the stores save: 10 % slower); more epilogue warps
+// (12 to 24: no gain, the epilogue is not latency-bound per warp).
 // Kind: 0 INT8, 1 FP8 (either format), 3 FP16.
 // Arithmetic per output, as the reference runs it after the GEMM:
 //   y = half_rn(dequantised accumulator)
-//   no activation : __hadd(y, bias)                           (add_last_dim_bias_kernel)
+//   no activation : __hadd(y, bias), then __hadd(.., residual)  (add_last_dim_bias_kernel, add_in_place_kernel)
 //   SiLU/GELU/QuickGELU : half_rn(act(float(y) + float(bias))) (bias_activation_in_place_kernel)
 //   GEGLU : half_rn((float(y_v) + float(b_v)) * gelu(float(y_g) + float(b_g)))   (bias_geglu_kernel)
 template <uint32_t Kind, uint32_t Act>
 __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
-    const bool row_ok = (t.flags & 1u) != 0;
-    const bool has_bias = (t.flags & 2u) != 0;
-    const bool store_vector = (t.flags & 4u) != 0;
-    const bool store_wide = (t.flags & 8u) != 0;
-    const float2 a_scale = make_float2(t.a_scale, t.a_scale);
-    int32_t* const acc_out = Kind == KIND_I8 ? t.acc_out : nullptr;
-    constexpr uint32_t kStride = kWarpsPerQuadrant * 16u;
-    if (Act != ACT_GEGLU) {
-        // columns this warp drains: c = chunk_first * 16 + m * kStride while c < tile_n and n0 + c < n
-        const uint32_t limit = min(t.tile_n, t.n > t.n0 ? t.n - t.n0 : 0u);
-        // Residual (Act == ACT_NONE only): __hadd(projection + bias, residual), the FP16 addition the
-        // reference's add_in_place_kernel performs after the Linear (src/cuda/ops_kernels.cu:60-64).
-        // Its 16 values are requested one chunk ahead, next to the tensor-memory load.
-        const __half* const residual = Act == ACT_NONE ? t.residual : nullptr;
-        const bool with_residual = residual != nullptr && row_ok;
-        auto finish = [&](uint32_t c0, const uint32_t (&acc)[16], const uint32_t (&extra)[8]) {
-            const uint32_t col0 = t.n0 + c0;
-            if (acc_out != nullptr && row_ok) {
-                int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n + col0;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    if (col0 + i < t.n) raw[i] = static_cast<int32_t>(acc[i]);
-                }
-            }
-            uint32_t out_words[8];
-            finish_chunk_16<Kind, Act>(t, c0, acc, a_scale, has_bias, out_words);
-            if (Act == ACT_NONE && with_residual) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const __half2 sum = __hadd2(*reinterpret_cast<const __half2*>(&out_words[i]),
-                                                *reinterpret_cast<const __half2*>(&extra[i]));
-                    out_words[i] = *reinterpret_cast<const uint32_t*>(&sum);
-                }
-            }
-            if (row_ok) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
-        };
-        uint32_t c = t.chunk_first * 16u;
-        if (c >= limit) return;
-        uint32_t even[16], odd[16];
-        uint32_t extra_even[8] = {}, extra_odd[8] = {};
-        ptx::tmem_ld_32x32b_x16(t.tmem_row + c, even);
-        if (with_residual) load_row_16(residual, t.n_out, store_vector, store_wide, t.row, t.n0 + c, extra_even);
-        while (true) {
-            ptx::tmem_ld_wait(even);
-            const uint32_t c1 = c + kStride;
-            if (c1 < limit) {
-                ptx::tmem_ld_32x32b_x16(t.tmem_row + c1, odd);
-                if (with_residual) load_row_16(residual, t.n_out, store_vector, store_wide, t.row, t.n0 + c1, extra_odd);
-            }
-            finish(c, even, extra_even);
-            if (c1 >= limit) break;
-            ptx::tmem_ld_wait(odd);
-            c = c1 + kStride;
-            if (c < limit) {
-                ptx::tmem_ld_32x32b_x16(t.tmem_row + c, even);
-                if (with_residual) load_row_16(residual, t.n_out, store_vector, store_wide, t.row, t.n0 + c, extra_even);
-            }
-            finish(c1, odd, extra_odd);
-            if (c >= limit) break;
-        }
-    } else {
-        const uint32_t half = t.tile_n / 2;
-        const uint32_t limit = min(half, t.n_out > t.n0 ? t.n_out - t.n0 : 0u);
-        uint32_t c0 = t.chunk_first * 16u;
-        if (c0 >= limit) return;
-        // a chunk is two steps of 8 columns (8 value + 8 gate accumulators each); buffer 0 always
-        // holds the first step, buffer 1 the second
-        uint32_t value0[8], gate0[8], value1[8], gate1[8];
-        ptx::tmem_ld_32x32b_x8(t.tmem_row + c0, value0);
-        ptx::tmem_ld_32x32b_x8(t.tmem_row + half + c0, gate0);
-        while (true) {
-            const uint32_t col0 = t.n0 + c0;
-            uint32_t out_words[8];
-            ptx::tmem_ld_wait(value0, gate0);
-            ptx::tmem_ld_32x32b_x8(t.tmem_row + c0 + 8u, value1);
-            ptx::tmem_ld_32x32b_x8(t.tmem_row + half + c0 + 8u, gate1);
-            finish_geglu_8<Kind>(t, c0, half, value0, gate0, a_scale, out_words);
-            if (acc_out != nullptr && row_ok) {
-                int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if (col0 + i < t.n_out) {
-                        raw[col0 + i] = static_cast<int32_t>(value0[i]);
-                        raw[t.n_out + col0 + i] = static_cast<int32_t>(gate0[i]);
-                    }
-                }
-            }
-            ptx::tmem_ld_wait(value1, gate1);
-            const uint32_t next = c0 + kStride;
-            if (next < limit) {
-                ptx::tmem_ld_32x32b_x8(t.tmem_row + next, value0);
-                ptx::tmem_ld_32x32b_x8(t.tmem_row + half + next, gate0);
-            }
-            finish_geglu_8<Kind>(t, c0 + 8u, half, value1, gate1, a_scale, out_words + 4);
-            if (acc_out != nullptr && row_ok) {
-                int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if (col0 + 8u + i < t.n_out) {
-                        raw[col0 + 8u + i] = static_cast<int32_t>(value1[i]);
-                        raw[t.n_out + col0 + 8u + i] = static_cast<int32_t>(gate1[i]);
-                    }
-                }
-            }
-            if (row_ok) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
-            if (next >= limit) break;
-            c0 = next;
-        }
-    }
-}
-
-// The same arithmetic without software pipelining: one chunk at a time, tensor-memory load, wait,
-// finish, store. It needs far fewer registers, which is what lets 16 epilogue warps (four per
-// scheduler) share the SM: with that many warps the scheduler hides the load and arithmetic
-// latencies by switching warps instead of by interleaving two chunks inside one warp.
-template <uint32_t Kind, uint32_t Act>
-__device__ __forceinline__ void epilogue_tile_lean(const EpilogueTile& t) {
     const bool row_ok = (t.flags & 1u) != 0;
     const bool has_bias = (t.flags & 2u) != 0;
     const bool store_vector = (t.flags & 4u) != 0;
@@ -547,22 +435,11 @@ __device__ __forceinline__ void epilogue_tile_lean(const EpilogueTile& t) {
     }
 }
 
-// Epilogue strategy: software-pipelined chunks with few warps, plain chunks with many.
-#ifndef SDXLQ_LEAN_EPILOGUE
-#define SDXLQ_LEAN_EPILOGUE (SDXLQ_EPILOGUE_WARPS >= 16)
-#endif
-
 template <uint32_t Kind>
 __device__ __forceinline__ void epilogue_dispatch(uint32_t activation, const EpilogueTile& t) {
-#if SDXLQ_LEAN_EPILOGUE
-    if (activation == ACT_NONE) epilogue_tile_lean<Kind, ACT_NONE>(t);
-    else if (activation == ACT_GEGLU) epilogue_tile_lean<Kind, ACT_GEGLU>(t);
-    else epilogue_tile_lean<Kind, kActRuntime>(t);
-#else
     if (activation == ACT_NONE) epilogue_tile<Kind, ACT_NONE>(t);
     else if (activation == ACT_GEGLU) epilogue_tile<Kind, ACT_GEGLU>(t);
     else epilogue_tile<Kind, kActRuntime>(t);
-#endif
 }
 
 }  // namespace
