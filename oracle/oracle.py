@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import shutil
 import subprocess
 
 import numpy as np
@@ -39,6 +40,12 @@ def build(ref_root: str | None = None) -> None:
     ref_root = ref_root or reference_root()
     if os.path.isdir(os.path.join(ref_root, "src")):
         subprocess.run(["make", "-C", _HERE, "ref", f"REF={ref_root}"], check=True, capture_output=True)
+        if os.path.isdir(os.path.join(ref_root, "src", "cuda")) and shutil.which("nvcc", path=_nvcc_path()):
+            subprocess.run(["make", "-C", _HERE, "refcuda", f"REF={ref_root}"], check=True, capture_output=True)
+
+
+def _nvcc_path() -> str:
+    return os.pathsep.join([os.environ.get("PATH", ""), "/usr/local/cuda/bin"])
 
 
 _lib = None
@@ -448,3 +455,103 @@ def ref_normal_sigma_schedule(steps: int):
     if status != 0:
         raise RuntimeError("the reference sigma schedule threw")
     return timesteps, sigmas
+
+
+class RefCuda:
+    """The reference's own CUDA Ops class compiled for sm_100 (oracle/_ref/libsdxl_ref_cuda*.so; recipe in
+    the Makefile, entry points in ref_harness_cuda.cpp). `ieee=True` picks the build without the
+    reference's --use_fast_math switch. Needs a GPU; a checker and a comparator, never shipped."""
+
+    WEIGHT_CODE = {"e4m3": 0, "e5m2": 1, "f16": 2}
+
+    def __init__(self, ieee: bool = False):
+        name = "libsdxl_ref_cuda_ieee.so" if ieee else "libsdxl_ref_cuda.so"
+        path = os.path.join(_HERE, "_ref", name)
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        self._lib = ctypes.CDLL(path)
+        self._error = ctypes.create_string_buffer(512)
+
+    @staticmethod
+    def available(ieee: bool = False) -> bool:
+        name = "libsdxl_ref_cuda_ieee.so" if ieee else "libsdxl_ref_cuda.so"
+        return os.path.exists(os.path.join(_HERE, "_ref", name))
+
+    def _check(self, status: int, what: str) -> None:
+        if status != 0:
+            raise RuntimeError(f"reference {what} threw: {self._error.value.decode(errors='replace')}")
+
+    def quantize_fp8(self, x_bits: np.ndarray, fmt: int):
+        """quantize_tensor_fp8 (src/cuda/fp8_kernels.cu:157-190) -> (fp8 bytes, dequantisation scale)."""
+        x_bits = _c(x_bits, np.uint16)
+        rows, columns = x_bits.shape
+        q = np.empty((rows, columns), np.uint8)
+        scale = np.zeros(1, np.float32)
+        self._check(self._lib.refcuda_quantize_fp8(_ptr(x_bits), ctypes.c_uint64(rows), ctypes.c_uint64(columns),
+                                                   ctypes.c_int(fmt), _ptr(q), _ptr(scale), self._error,
+                                                   ctypes.c_uint64(len(self._error))), "quantize_tensor_fp8")
+        return q, float(scale[0])
+
+    def fp8_weight_only_linear(self, x_bits: np.ndarray, wq: np.ndarray, fmt: int, scales: np.ndarray,
+                               k_major: bool = False) -> np.ndarray:
+        """fp8_weight_only_linear (src/cuda/fp8_kernels.cu:192-245) -> FP16 bits [m, n]. wq is [n, k], or
+        [k, n] with k_major."""
+        x_bits = _c(x_bits, np.uint16)
+        wq = _c(wq, np.uint8)
+        scales = _c(scales, np.float32).reshape(-1)
+        m, k = x_bits.shape
+        n = wq.shape[1] if k_major else wq.shape[0]
+        y = np.empty((m, n), np.uint16)
+        self._check(self._lib.refcuda_fp8_weight_only_linear(
+            _ptr(x_bits), ctypes.c_uint64(m), ctypes.c_uint64(k), _ptr(wq), ctypes.c_uint64(n), ctypes.c_int(fmt),
+            _ptr(scales), ctypes.c_uint64(scales.size), ctypes.c_int(1 if k_major else 0), _ptr(y), self._error,
+            ctypes.c_uint64(len(self._error))), "fp8_weight_only_linear")
+        return y
+
+    def ops_linear(self, x_bits: np.ndarray, w: np.ndarray, kind: str, scales: np.ndarray | None = None,
+                   bias_bits: np.ndarray | None = None, activation: int = ACT_NONE,
+                   fp32_accumulation: bool = False) -> np.ndarray:
+        """Ops::linear / Ops::linear_activation (src/cuda/ops_blas.cpp:244-397) -> FP16 bits. `kind` is
+        "f16" (w holds FP16 bits), "e4m3" or "e5m2" (w holds FP8 bytes, `scales` 1 or n values)."""
+        x_bits = _c(x_bits, np.uint16)
+        m, k = x_bits.shape
+        n = w.shape[0]
+        w = _c(w.view(np.uint16) if kind == "f16" else w, np.uint16 if kind == "f16" else np.uint8)
+        scales = _c(scales if scales is not None else np.ones(1), np.float32).reshape(-1)
+        columns = n // 2 if activation == ACT_GEGLU else n
+        y = np.empty((m, columns), np.uint16)
+        bias = None if bias_bits is None else _c(bias_bits, np.uint16)
+        self._check(self._lib.refcuda_ops_linear(
+            _ptr(x_bits), ctypes.c_uint64(m), ctypes.c_uint64(k), _ptr(w), ctypes.c_uint64(n),
+            ctypes.c_int(self.WEIGHT_CODE[kind]), _ptr(scales), ctypes.c_uint64(scales.size),
+            _ptr(bias) if bias is not None else None, ctypes.c_int(activation),
+            ctypes.c_int(1 if fp32_accumulation else 0), _ptr(y), ctypes.c_uint64(columns), self._error,
+            ctypes.c_uint64(len(self._error))), "Ops::linear")
+        return y
+
+    def time_linear(self, m: int, k: int, n: int, kind: str, activation: int = ACT_NONE, has_bias: bool = True,
+                    fp32_accumulation: bool = False, warmup: int = 3, iterations: int = 10) -> float:
+        """Milliseconds per Ops::linear_activation call with device-resident operands, timed with CUDA
+        events on the reference's stream."""
+        ms = ctypes.c_float(0.0)
+        self._check(self._lib.refcuda_time_linear(
+            ctypes.c_uint64(m), ctypes.c_uint64(k), ctypes.c_uint64(n), ctypes.c_int(self.WEIGHT_CODE[kind]),
+            ctypes.c_int(activation), ctypes.c_int(1 if has_bias else 0), ctypes.c_int(1 if fp32_accumulation else 0),
+            ctypes.c_int(warmup), ctypes.c_int(iterations), ctypes.byref(ms), self._error,
+            ctypes.c_uint64(len(self._error))), "Ops::linear timing")
+        return float(ms.value)
+
+    def layer_norm(self, x_bits: np.ndarray, gamma_bits: np.ndarray, beta_bits: np.ndarray,
+                   epsilon: float = 1e-5) -> np.ndarray:
+        """Ops::layer_norm (src/cuda/ops_kernels.cu:1425-1470) -> FP16 bits."""
+        x_bits = _c(x_bits, np.uint16)
+        rows, width = x_bits.shape
+        y = np.empty((rows, width), np.uint16)
+        self._check(self._lib.refcuda_layer_norm(
+            _ptr(x_bits), ctypes.c_uint64(rows), ctypes.c_uint64(width), _ptr(_c(gamma_bits, np.uint16)),
+            _ptr(_c(beta_bits, np.uint16)), ctypes.c_float(epsilon), _ptr(y), self._error,
+            ctypes.c_uint64(len(self._error))), "Ops::layer_norm")
+        return y
+
+    def shutdown(self) -> None:
+        self._lib.refcuda_shutdown()
