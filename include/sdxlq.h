@@ -202,6 +202,40 @@ int sdxlq_quantize_act_int8(sdxlq_context* ctx, const void* x, int32_t x_dtype, 
 int sdxlq_quantize_act_fp8(sdxlq_context* ctx, const void* x_f16, uint64_t count, int32_t fmt,
                            uint8_t* q, float* scale);
 
+/* ---- LayerNorm feeding a projection ------------------------------------------------------- */
+
+/* Ops::layer_norm (include/sdxl/cuda/ops.hpp:39-42, src/cuda/ops_kernels.cu:185-256, 1425-1470) over the
+ * last dimension of FP16 x[rows, width], optionally fused with the activation quantiser of the
+ * projection that consumes the result, so that the normalised FP16 tensor is never written:
+ *   out_dtype SDXLQ_FP16      y[rows, width] FP16, the reference's result.
+ *   out_dtype SDXLQ_INT8      xq[rows, width] INT8 + xq_scales[rows]: LayerNorm, rounding to FP16, ConvRot
+ *                             rotation (convrot_group_size, 0 = none) and per-row quantisation in one
+ *                             call, equal to sdxlq_quantize_act_int8 applied to the FP16 result (one launch
+ *                             without rotation; with rotation the FP16 rows pass through the context's
+ *                             workspace on their way to the rotation kernel).
+ *   out_dtype SDXLQ_FP8_E4M3 / SDXLQ_FP8_E5M2
+ *                             xq[rows, width] FP8 + xq_scales[1], equal to sdxlq_quantize_act_fp8 applied
+ *                             to the FP16 result (two launches: statistics, then normalise + cast).
+ * Pass xq / xq_scales to sdxlq_linear_desc.xq / .xq_scales of every projection that reads the
+ * normalised activations (to_q / to_k / to_v, ff.net.0.proj). The FP16 and FP8 forms want width a
+ * multiple of 8, at most 2048, and 16-byte aligned rows (every SDXL width: 640, 1280);
+ * SDXLQ_ERR_UNSUPPORTED_SHAPE otherwise. rows == 0 is a no-op. */
+typedef struct sdxlq_layer_norm_desc {
+    const void* x;               /* FP16 [rows, width] */
+    uint64_t rows;
+    uint64_t width;
+    const void* gamma;           /* FP16 [width] */
+    const void* beta;            /* FP16 [width] */
+    float epsilon;               /* the reference's default is 1e-5 */
+    int32_t out_dtype;
+    uint32_t convrot_group_size; /* SDXLQ_INT8 only */
+    uint32_t reserved;
+    void* y;                     /* SDXLQ_FP16 */
+    void* xq;                    /* quantised forms */
+    float* xq_scales;
+} sdxlq_layer_norm_desc;
+int sdxlq_layer_norm(sdxlq_context* ctx, const sdxlq_layer_norm_desc* desc);
+
 /* ---- load-time weight packers ------------------------------------------------------------- */
 
 /* upload_or_quantize_int8_weight (int8_convrot.cu:498-577) for a weight already on the device:
@@ -247,7 +281,8 @@ enum {
     SDXLQ_KERNEL_QUANT_FP8 = 1,
     SDXLQ_KERNEL_GEMM = 2,
     SDXLQ_KERNEL_SMALL = 3,
-    SDXLQ_KERNEL_CLASSES = 4
+    SDXLQ_KERNEL_LAYER_NORM = 4,
+    SDXLQ_KERNEL_CLASSES = 5
 };
 typedef struct sdxlq_kernel_times {
     double milliseconds[SDXLQ_KERNEL_CLASSES];

@@ -264,6 +264,17 @@ def geglu_f32(y: np.ndarray) -> np.ndarray:
     return out
 
 
+def layer_norm_f16(x_bits: np.ndarray, gamma_bits: np.ndarray, beta_bits: np.ndarray,
+                   epsilon: float = 1e-5) -> np.ndarray:
+    """layer_norm_kernel (src/cuda/ops_kernels.cu:185-221) on FP16 bits [rows, width] -> FP16 bits."""
+    x_bits = _c(x_bits, np.uint16)
+    rows, width = x_bits.shape
+    out = np.empty((rows, width), np.uint16)
+    lib().orc_layer_norm_f16(_ptr(x_bits), _ptr(_c(gamma_bits, np.uint16)), _ptr(_c(beta_bits, np.uint16)),
+                             _c_size(rows), _c_size(width), ctypes.c_float(epsilon), _ptr(out))
+    return out
+
+
 def threads() -> int:
     return int(lib().orc_threads())
 

@@ -11,7 +11,10 @@
  * implementation in the reference, so it is restated here line by line from the CUDA
  * sources cited at each function; divisions and reciprocals are IEEE round-to-nearest
  * (the reference's default build uses --use_fast_math, whose approximate division
- * cannot be restated on a CPU).
+ * cannot be restated on a CPU). (3) The FP8 activation quantiser, the native FP8 and
+ * FP16 projections with their epilogues and LayerNorm are additionally checked on the
+ * GPU against the reference's own CUDA translation units compiled for sm_100
+ * (oracle/ref_harness_cuda.cpp, tests/test_reference_device_gpu.py).
  *
  * Build: see oracle/Makefile (gcc -O2 -ffp-contract=off -pthread -shared).
  */
@@ -593,6 +596,35 @@ void orc_geglu_f32(const float* input, size_t rows, size_t width, float* output)
             const float gate = source[width + column];
             output[row * width + column] =
                 source[column] * (0.5f * gate * (1.0f + erff(gate * 0.7071067811865475244f)));
+        }
+    }
+}
+
+/* layer_norm_kernel (src/cuda/ops_kernels.cu:185-221): per row, FP32 sum -> mean, FP32 sum of the
+ * centred squares -> variance clamped at 0, inverse = 1 / sqrt(variance + epsilon), output =
+ * half_rn((x - mean) * inverse * gamma + beta) with the last multiply-add fused as nvcc contracts
+ * it. The reference adds the partial sums of 256 threads through a shared-memory tree and takes
+ * rsqrtf (2 ulp); here the sums run in column order and the reciprocal square root is the
+ * correctly rounded quotient, so results may differ from the device in the last FP32 bits of the
+ * statistics. */
+void orc_layer_norm_f16(const uint16_t* input, const uint16_t* gamma, const uint16_t* beta, size_t rows,
+                        size_t width, float epsilon, uint16_t* output) {
+    for (size_t row = 0; row < rows; ++row) {
+        const uint16_t* x = input + row * width;
+        float sum = 0.0f;
+        for (size_t c = 0; c < width; ++c) sum += orc_h2f(x[c]);
+        const float mean = sum / (float)width;
+        float squares = 0.0f;
+        for (size_t c = 0; c < width; ++c) {
+            const float centred = orc_h2f(x[c]) - mean;
+            squares = fmaf(centred, centred, squares);
+        }
+        float variance = squares / (float)width;
+        if (!(variance > 0.0f)) variance = 0.0f;
+        const float inverse = 1.0f / sqrtf(variance + epsilon);
+        for (size_t c = 0; c < width; ++c) {
+            const float scaled = (orc_h2f(x[c]) - mean) * inverse;
+            output[row * width + c] = orc_f2h(fmaf(scaled, orc_h2f(gamma[c]), orc_h2f(beta[c])));
         }
     }
 }

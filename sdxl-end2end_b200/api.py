@@ -102,11 +102,21 @@ class _CStats(ctypes.Structure):
     ]
 
 
+class _CLayerNormDesc(ctypes.Structure):
+    """sdxlq_layer_norm_desc."""
+    _fields_ = [
+        ("x", ctypes.c_void_p), ("rows", ctypes.c_uint64), ("width", ctypes.c_uint64),
+        ("gamma", ctypes.c_void_p), ("beta", ctypes.c_void_p), ("epsilon", ctypes.c_float),
+        ("out_dtype", ctypes.c_int32), ("convrot_group_size", ctypes.c_uint32), ("reserved", ctypes.c_uint32),
+        ("y", ctypes.c_void_p), ("xq", ctypes.c_void_p), ("xq_scales", ctypes.c_void_p),
+    ]
+
+
 class _CKernelTimes(ctypes.Structure):
-    _fields_ = [("milliseconds", ctypes.c_double * 4), ("launches", ctypes.c_uint64 * 4)]
+    _fields_ = [("milliseconds", ctypes.c_double * 5), ("launches", ctypes.c_uint64 * 5)]
 
 
-KERNEL_CLASSES = ("quant_int8", "quant_fp8", "gemm", "small")
+KERNEL_CLASSES = ("quant_int8", "quant_fp8", "gemm", "small", "layer_norm")
 
 EXPORTED_SYMBOLS = [
     "sdxlq_context_create", "sdxlq_context_destroy", "sdxlq_context_set_stream", "sdxlq_context_check",
@@ -116,7 +126,7 @@ EXPORTED_SYMBOLS = [
     "sdxlq_pack_weight_int8", "sdxlq_pack_weight_fp8", "sdxlq_valid_convrot_group_size",
     "sdxlq_workspace_bytes", "sdxlq_build_info", "sdxlq_context_set_tile_n",
     "sdxlq_selftest_bounded_wait", "sdxlq_profile_enable", "sdxlq_profile_read", "sdxlq_linear_static",
-    "sdxlq_context_set_pair_mode",
+    "sdxlq_context_set_pair_mode", "sdxlq_layer_norm",
 ]
 
 _lib: Optional[ctypes.CDLL] = None
@@ -168,6 +178,7 @@ def load_library() -> ctypes.CDLL:
     lib.sdxlq_profile_enable.argtypes = [vp, ctypes.c_int]
     lib.sdxlq_profile_read.argtypes = [vp, ctypes.POINTER(_CKernelTimes)]
     lib.sdxlq_linear_static.argtypes = [ctypes.c_int, vp, ctypes.POINTER(_CLinearDesc), ctypes.c_char_p, sz]
+    lib.sdxlq_layer_norm.argtypes = [vp, ctypes.POINTER(_CLayerNormDesc)]
     _lib = lib
     return lib
 
@@ -429,6 +440,54 @@ class Ops:
     def workspace_bytes(self, calls: Sequence[LinearCall]) -> int:
         array = self._desc_array(calls)
         return int(self._lib.sdxlq_workspace_bytes(array, len(calls)))
+
+    # -- Ops::layer_norm, alone or fused with the next projection's quantiser -------------------------
+    def _layer_norm_check(self, input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor) -> tuple:
+        if input.dtype != torch.float16 or weight.dtype != torch.float16 or bias.dtype != torch.float16 or \
+                input.dim() < 1 or weight.dim() != 1 or bias.dim() != 1:
+            raise CudaError("CUDA layer_norm expects an FP16 input with rank-1 FP16 weight and bias")
+        width = int(input.shape[-1])
+        if weight.shape[0] != width or bias.shape[0] != width:
+            raise CudaError("CUDA layer_norm width mismatch")
+        if width == 0:
+            raise CudaError("layer_norm requires a non-empty last dimension")
+        if not input.is_contiguous():
+            raise CudaError("CUDA layer_norm expects a contiguous input")
+        return input.numel() // width, width
+
+    def layer_norm(self, input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+                   epsilon: float = 1.0e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Ops::layer_norm (include/sdxl/cuda/ops.hpp:39-42): FP16 in, FP16 out."""
+        rows, width = self._layer_norm_check(input, weight, bias)
+        y = out if out is not None else torch.empty_like(input)
+        desc = _CLayerNormDesc(input.data_ptr(), rows, width, weight.data_ptr(), bias.data_ptr(), epsilon,
+                               int(ScalarType.Float16), 0, 0, y.data_ptr(), None, None)
+        self.ctx.raise_for(self._lib.sdxlq_layer_norm(self.ctx.handle, ctypes.byref(desc)))
+        return y
+
+    def layer_norm_quantized(self, input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+                             consumer: Weight, epsilon: float = 1.0e-5):
+        """LayerNorm fused with the activation quantiser of the projection(s) that read the result:
+        returns (xq, xq_scales) in the form `consumer` (an INT8 or FP8 projection weight) wants, to be
+        passed as linear(None, consumer, ..., xq=xq, xq_scales=xq_scales). Equal to quantising
+        layer_norm(input) with quantize_int8 / quantize_fp8, without the FP16 tensor in between."""
+        rows, width = self._layer_norm_check(input, weight, bias)
+        if consumer.k != width:
+            raise CudaError("CUDA linear feature mismatch")
+        if consumer.type == ScalarType.Int8:
+            xq = torch.empty(input.shape, dtype=torch.int8, device=input.device)
+            scales = torch.empty(rows, dtype=torch.float32, device=input.device)
+            group = consumer.convrot_group_size
+        elif consumer.type in _TORCH_FP8:
+            xq = torch.empty(input.shape, dtype=torch.uint8, device=input.device)
+            scales = torch.empty(1, dtype=torch.float32, device=input.device)
+            group = 0
+        else:
+            raise CudaError("layer_norm_quantized wants an INT8 or FP8 projection weight")
+        desc = _CLayerNormDesc(input.data_ptr(), rows, width, weight.data_ptr(), bias.data_ptr(), epsilon,
+                               int(consumer.type), group, 0, None, xq.data_ptr(), scales.data_ptr())
+        self.ctx.raise_for(self._lib.sdxlq_layer_norm(self.ctx.handle, ctypes.byref(desc)))
+        return xq, scales
 
     # -- Ops::quantize_fp8 / quantize_e4m3 / quantize_e5m2 ------------------------------------------
     def quantize_fp8(self, input: torch.Tensor, fp8_type: ScalarType) -> Weight:

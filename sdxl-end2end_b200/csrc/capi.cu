@@ -83,7 +83,7 @@ struct sdxlq_context {
     std::string last_error = "";
     // Optional per-kernel timing: CUDA event pairs recorded around each launch on the stream.
     bool profiling = false;
-    struct TimedLaunch { int kernel_class; cudaEvent_t start; cudaEvent_t stop; };
+    struct TimedLaunch { int kernel_class; cudaEvent_t start; cudaEvent_t stop; int launches; };
     std::vector<TimedLaunch> timed;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> event_pool;
 };
@@ -93,7 +93,7 @@ namespace {
 // Records an event pair around the launches issued while it is alive (profiling mode only).
 class LaunchTimer {
 public:
-    LaunchTimer(sdxlq_context* ctx, int kernel_class) : ctx_(ctx) {
+    LaunchTimer(sdxlq_context* ctx, int kernel_class, int launches = 1) : ctx_(ctx) {
         if (!ctx_->profiling) return;
         std::pair<cudaEvent_t, cudaEvent_t> events{nullptr, nullptr};
         if (!ctx_->event_pool.empty()) {
@@ -102,7 +102,7 @@ public:
         } else if (cudaEventCreate(&events.first) != cudaSuccess || cudaEventCreate(&events.second) != cudaSuccess) {
             return;
         }
-        entry_ = {kernel_class, events.first, events.second};
+        entry_ = {kernel_class, events.first, events.second, launches};
         active_ = cudaEventRecord(entry_.start, ctx_->stream) == cudaSuccess;
     }
     ~LaunchTimer() {
@@ -324,8 +324,12 @@ uint32_t best_int8_block(uint32_t threads_per_row) {
 }
 
 int add_int8_job(sdxlq_context* ctx, Prepared& prep, const void* x, bool x_is_f32, uint64_t m, uint64_t k,
-                 uint32_t group, int8_t* xq, float* scales, bool grouped) {
+                 uint32_t group, int8_t* xq, float* scales, bool grouped, const __half* gamma = nullptr,
+                 const __half* beta = nullptr, float epsilon = 0.0f) {
     QuantInt8Job job{};
+    job.gamma = gamma;           // a LayerNorm in front of the rotation: general kernel only
+    job.beta = beta;
+    job.epsilon = epsilon;
     job.x = x;
     job.xq = xq;
     job.scales = scales;
@@ -337,9 +341,10 @@ int add_int8_job(sdxlq_context* ctx, Prepared& prep, const void* x, bool x_is_f3
     job.x_is_f32 = x_is_f32 ? 1 : 0;
     const size_t element = x_is_f32 ? 4 : 2;
     job.vector_ok = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && ((k * element) % 16 == 0) &&
-                    (reinterpret_cast<uintptr_t>(xq) % 8 == 0) && (k % 8 == 0);
+                    (reinterpret_cast<uintptr_t>(xq) % 8 == 0) && (k % 8 == 0) &&
+                    reinterpret_cast<uintptr_t>(gamma) % 16 == 0 && reinterpret_cast<uintptr_t>(beta) % 16 == 0;
     // FP16 rows with a 16-byte pitch take the throughput kernels; everything else the general one.
-    const bool fast = !x_is_f32 && job.vector_ok;
+    const bool fast = !x_is_f32 && job.vector_ok && gamma == nullptr;
     Int8Flavour flavour = INT8_GENERIC;
     if (fast && job.stages == 0 && k <= 5120) flavour = INT8_PLAIN;
     else if (fast && job.stages != 0) flavour = INT8_ROTATED;
@@ -775,7 +780,7 @@ int run_prepared(sdxlq_context* ctx, const Prepared& prep, const sdxlq_group_pla
     if (status != SDXLQ_OK) return status;
     if (!prep.fp8_jobs.empty()) {
         const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, tables != nullptr ? tables->device_fp8_jobs : nullptr);
-        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8);
+        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8, 2);
         const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream, ctx->early_launch && !ctx->profiling);
         if (error != cudaSuccess) return fail_cuda(ctx, error, "FP8 activation quantise launch");
     }
@@ -1091,9 +1096,91 @@ int sdxlq_quantize_act_fp8(sdxlq_context* ctx, const void* x_f16, uint64_t count
     Prepared prep;
     add_fp8_job(prep, x_f16, count, fmt == SDXLQ_FP8_E4M3 ? 0 : 1, q, scale);
     const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, nullptr);
-    LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8);
+    LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8, 2);
     const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream, ctx->early_launch && !ctx->profiling);
     if (error != cudaSuccess) return fail_cuda(ctx, error, "FP8 activation quantise launch");
+    return SDXLQ_OK;
+}
+
+int sdxlq_layer_norm(sdxlq_context* ctx, const sdxlq_layer_norm_desc* desc) {
+    if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    if (desc == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "layer_norm: null descriptor");
+    const sdxlq_layer_norm_desc& d = *desc;
+    if (d.width == 0) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "layer_norm requires a non-empty last dimension");
+    if (d.rows == 0) return SDXLQ_OK;
+    if (d.x == nullptr || d.gamma == nullptr || d.beta == nullptr) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "layer_norm: null input, weight or bias");
+    }
+    if (d.rows > 0x7FFFFFFFull || d.width > 0x7FFFFFFFull) {
+        return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE, "layer_norm: dimensions too large");
+    }
+    const auto aligned = [](const void* pointer, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(pointer) % bytes == 0; };
+    // what the warp-per-row kernels take: rows of 16-byte vectors that fit a warp's registers
+    const bool row_kernel_ok = d.width % 8 == 0 && d.width <= 2048 && aligned(d.x, 16) && aligned(d.gamma, 16) && aligned(d.beta, 16);
+    LayerNormLaunch launch{};
+    launch.x = static_cast<const __half*>(d.x);
+    launch.gamma = static_cast<const __half*>(d.gamma);
+    launch.beta = static_cast<const __half*>(d.beta);
+    launch.rows = static_cast<uint32_t>(d.rows);
+    launch.width = static_cast<uint32_t>(d.width);
+    launch.epsilon = d.epsilon;
+
+    if (d.out_dtype == SDXLQ_INT8) {
+        if (d.xq == nullptr || d.xq_scales == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "layer_norm: null quantised output");
+        if (d.convrot_group_size != 0 && (!valid_group(d.convrot_group_size) || d.width % d.convrot_group_size != 0)) {
+            return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "native INT8 linear has invalid ConvRot group metadata");
+        }
+        if (row_kernel_ok && d.convrot_group_size == 0 && aligned(d.xq, 8)) {
+            // one launch: normalise, per-row maximum, cast
+            launch.q = static_cast<uint8_t*>(d.xq);
+            launch.scale_out = d.xq_scales;
+            LaunchTimer timer(ctx, SDXLQ_KERNEL_LAYER_NORM);
+            const cudaError_t error = launch_layer_norm_int8(launch, ctx->stream);
+            if (error != cudaSuccess) return fail_cuda(ctx, error, "layer_norm launch");
+            return SDXLQ_OK;
+        }
+        const size_t scratch = static_cast<size_t>(d.rows) * d.width * sizeof(__half);
+        const void* source = d.x;
+        const __half* gamma = static_cast<const __half*>(d.gamma);
+        const __half* beta = static_cast<const __half*>(d.beta);
+        if (row_kernel_ok && scratch <= ctx->workspace_bytes) {
+            // rotated rows: the normalised FP16 tensor goes through the workspace (it stays in L2 for
+            // the sizes of this model) and the throughput rotation kernels read it from there
+            launch.y = reinterpret_cast<__half*>(ctx->workspace);
+            LaunchTimer timer(ctx, SDXLQ_KERNEL_LAYER_NORM);
+            const cudaError_t error = launch_layer_norm_f16(launch, ctx->stream);
+            if (error != cudaSuccess) return fail_cuda(ctx, error, "layer_norm launch");
+            source = ctx->workspace;
+            gamma = beta = nullptr;
+        }
+        // otherwise (odd widths, rows past 2048 elements, no room): the general quantiser normalises
+        // the row itself before it rotates it
+        Prepared prep;
+        const int status = add_int8_job(ctx, prep, source, false, d.rows, d.width, d.convrot_group_size,
+                                        static_cast<int8_t*>(d.xq), d.xq_scales, false, gamma, beta, d.epsilon);
+        if (status != SDXLQ_OK) return status;
+        return run_int8_quantisers(ctx, prep, nullptr);
+    }
+    const bool fp8 = is_fp8(d.out_dtype);
+    if (!fp8 && d.out_dtype != SDXLQ_FP16) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "layer_norm: unknown output type");
+    void* const destination = fp8 ? d.xq : d.y;
+    if (destination == nullptr || (fp8 && d.xq_scales == nullptr)) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "layer_norm: null output");
+    }
+    if (!row_kernel_ok || !aligned(destination, fp8 ? 8 : 16)) {
+        return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE,
+                    "layer_norm: rows must be 16-byte aligned, a multiple of 8 and at most 2048 elements wide");
+    }
+    launch.y = static_cast<__half*>(d.y);
+    launch.q = static_cast<uint8_t*>(d.xq);
+    launch.scale_out = d.xq_scales;
+    launch.amax_bits = ctx->control + 64;
+    launch.done_count = ctx->control + 64 + kMaxFp8Jobs;
+    launch.fmt = d.out_dtype == SDXLQ_FP8_E5M2 ? 1u : 0u;
+    LaunchTimer timer(ctx, SDXLQ_KERNEL_LAYER_NORM, fp8 ? 2 : 1);
+    const cudaError_t error = fp8 ? launch_layer_norm_fp8(launch, ctx->stream, ctx->early_launch && !ctx->profiling)
+                                  : launch_layer_norm_f16(launch, ctx->stream);
+    if (error != cudaSuccess) return fail_cuda(ctx, error, "layer_norm launch");
     return SDXLQ_OK;
 }
 
@@ -1163,7 +1250,7 @@ int sdxlq_profile_read(sdxlq_context* ctx, sdxlq_kernel_times* out) {
         if (cudaEventElapsedTime(&milliseconds, entry.start, entry.stop) == cudaSuccess &&
             entry.kernel_class >= 0 && entry.kernel_class < SDXLQ_KERNEL_CLASSES) {
             out->milliseconds[entry.kernel_class] += milliseconds;
-            out->launches[entry.kernel_class] += entry.kernel_class == SDXLQ_KERNEL_QUANT_FP8 ? 2 : 1;
+            out->launches[entry.kernel_class] += static_cast<uint64_t>(entry.launches);
         }
         ctx->event_pool.emplace_back(entry.start, entry.stop);
     }

@@ -21,8 +21,7 @@
 // (src/cuda/weights.cu:119-170).
 
 #include "quantize.cuh"
-
-#include <cuda_fp8.h>
+#include "fp8_math.cuh"
 
 namespace sdxlq {
 
@@ -74,9 +73,9 @@ __device__ __forceinline__ const QuantInt8Job& find_job(const QuantInt8Launch& l
 
 }  // namespace
 
-template <typename In>
+template <typename In, bool Normalize>
 __device__ __forceinline__ void rotate_quantize_rows(const QuantInt8Job& job, uint32_t local_block,
-                                                     uint32_t* row_max_bits) {
+                                                     uint32_t* row_max_bits, float* row_partials) {
     const uint32_t threads_per_row = job.threads_per_row;
     const uint32_t row_in_block = threadIdx.x / threads_per_row;
     const uint32_t thread_in_row = threadIdx.x - row_in_block * threads_per_row;
@@ -101,6 +100,59 @@ __device__ __forceinline__ void rotate_quantize_rows(const QuantInt8Job& job, ui
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[u][i] = 0.0f;
+        }
+    }
+
+    if constexpr (Normalize) {
+        // LayerNorm of the row before it is rotated, with the arithmetic of the reference's
+        // layer_norm_kernel (src/cuda/ops_kernels.cu:185-256): FP32 mean, FP32 mean of the centred
+        // squares clamped at 0, rsqrtf(variance + epsilon), and the result rounded to FP16 like the
+        // tensor the reference would hand to its quantiser. The partial sums of a row's threads are
+        // added in thread order, so the result does not depend on scheduling.
+        const float width = static_cast<float>(k);
+        const uint32_t first = row_in_block * threads_per_row;
+        float partial = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) partial += v[u][i];                  // absent elements hold 0
+        }
+        row_partials[threadIdx.x] = partial;
+        __syncthreads();
+        float total = 0.0f;
+        if (active) for (uint32_t t = 0; t < threads_per_row; ++t) total += row_partials[first + t];
+        const float mean = __fdiv_rn(total, width);
+        __syncthreads();
+        partial = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t col = base_col + 32u * u;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float centred = v[u][i] - mean;
+                if (active && col + i < k) partial = fmaf(centred, centred, partial);
+            }
+        }
+        row_partials[threadIdx.x] = partial;
+        __syncthreads();
+        total = 0.0f;
+        if (active) for (uint32_t t = 0; t < threads_per_row; ++t) total += row_partials[first + t];
+        const float variance = fmaxf(0.0f, __fdiv_rn(total, width));
+        const float inverse = rsqrtf(variance + job.epsilon);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t col = base_col + 32u * u;
+            uint32_t valid = 0;
+            if (active && col < k) valid = min(8u, k - col);
+            if (valid == 0) continue;
+            float gamma[8], beta[8];
+            load8(job.gamma + col, vector_ok, valid, gamma);
+            load8(job.beta + col, vector_ok, valid, beta);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float normalised = fmaf(__fmul_rn(v[u][i] - mean, inverse), gamma[i], beta[i]);
+                v[u][i] = static_cast<uint32_t>(i) < valid ? __half2float(__float2half_rn(normalised)) : 0.0f;
+            }
         }
     }
 
@@ -223,13 +275,25 @@ rotate_quantize_int8_kernel(const __grid_constant__ QuantInt8Launch launch) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const QuantInt8Job& job = find_job(launch, blockIdx.x);
     const uint32_t local_block = blockIdx.x - job.first_block;
-    if (job.x_is_f32) rotate_quantize_rows<float>(job, local_block, row_max_bits);
-    else rotate_quantize_rows<__half>(job, local_block, row_max_bits);
+    if (job.x_is_f32) rotate_quantize_rows<float, false>(job, local_block, row_max_bits, nullptr);
+    else rotate_quantize_rows<__half, false>(job, local_block, row_max_bits, nullptr);
+}
+
+// The same pass with a LayerNorm of the FP16 row in front of the rotation (every job carries gamma /
+// beta). A kernel of its own so that its larger register need does not weigh on the one above.
+__global__ void __launch_bounds__(256, 1)
+normalize_rotate_quantize_int8_kernel(const __grid_constant__ QuantInt8Launch launch) {
+    __shared__ uint32_t row_max_bits[64];
+    __shared__ float row_partials[256];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const QuantInt8Job& job = find_job(launch, blockIdx.x);
+    rotate_quantize_rows<__half, true>(job, blockIdx.x - job.first_block, row_max_bits, row_partials);
 }
 
 cudaError_t launch_rotate_quantize_int8(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
                                         cudaStream_t stream) {
-    rotate_quantize_int8_kernel<<<blocks, threads, 0, stream>>>(launch);
+    if (launch.single.gamma != nullptr) normalize_rotate_quantize_int8_kernel<<<blocks, threads, 0, stream>>>(launch);
+    else rotate_quantize_int8_kernel<<<blocks, threads, 0, stream>>>(launch);
     return cudaGetLastError();
 }
 
@@ -246,22 +310,6 @@ __device__ __forceinline__ uint32_t find_job_index(const QuantFp8Launch& launch,
         if (launch.jobs[mid].first_block <= block) lo = mid; else hi = mid;
     }
     return lo;
-}
-
-__device__ __forceinline__ float fp8_scale_from_amax(float maximum, uint32_t fmt) {
-    const float fp8_maximum = fmt == 0 ? 448.0f : 57344.0f;
-    return maximum > 0.0f ? fmaxf(__fdiv_rn(maximum, fp8_maximum), 1.0e-12f) : 1.0f;
-}
-
-__device__ __forceinline__ uint32_t encode_fp8x2(float lo, float hi, uint32_t fmt) {
-    const float2 pair = make_float2(lo, hi);
-    return fmt == 0 ? __nv_cvt_float2_to_fp8x2(pair, __NV_SATFINITE, __NV_E4M3)
-                    : __nv_cvt_float2_to_fp8x2(pair, __NV_SATFINITE, __NV_E5M2);
-}
-
-__device__ __forceinline__ uint8_t encode_fp8(float value, uint32_t fmt) {
-    return fmt == 0 ? __nv_cvt_float_to_fp8(value, __NV_SATFINITE, __NV_E4M3)
-                    : __nv_cvt_float_to_fp8(value, __NV_SATFINITE, __NV_E5M2);
 }
 
 }  // namespace

@@ -21,6 +21,11 @@ struct QuantInt8Job {
     uint32_t first_block;        // first block of this job inside a grouped launch
     uint32_t num_blocks;
     uint32_t pad;                // 1: group of 256 with 16-byte aligned output rows (rotated256_rows_kernel)
+    // LayerNorm over the row before the rotation (general kernel only): gamma == null means none.
+    const __half* gamma;         // [k]
+    const __half* beta;          // [k]
+    float epsilon;
+    uint32_t pad2;
 };
 
 struct QuantInt8Launch {
@@ -59,5 +64,28 @@ cudaError_t launch_fp8_weight_pack(const void* source, int32_t dtype, uint32_t n
                                    uint32_t per_channel, uint32_t k_major, uint8_t* destination,
                                    float* scales, cudaStream_t stream);
 cudaError_t launch_fill_f32(float* values, uint32_t count, float value, cudaStream_t stream);
+
+// LayerNorm over the last dimension of FP16 x[rows, width] (width a multiple of 8, at most 2048, 16-byte
+// aligned rows), one warp per row with the row in registers. Three outputs:
+//   FP16            y[rows, width]
+//   FP8             q[rows, width] in `fmt` with one tensor-wide dynamic scale: a statistics launch that only
+//                   reduces max |y| into *amax_bits, then a launch that normalises again and casts
+//   INT8            q[rows, width] with per-row scales scale_out[rows], no rotation
+struct LayerNormLaunch {
+    const __half* x;
+    const __half* gamma;
+    const __half* beta;
+    __half* y;
+    uint8_t* q;
+    float* scale_out;
+    uint32_t* amax_bits;         // zero on entry; put back to zero by the cast launch
+    uint32_t* done_count;        // zero on entry; put back to zero by the cast launch
+    uint32_t rows, width;
+    uint32_t fmt;                // 0 = E4M3, 1 = E5M2
+    float epsilon;
+};
+cudaError_t launch_layer_norm_f16(const LayerNormLaunch& launch, cudaStream_t stream);
+cudaError_t launch_layer_norm_int8(const LayerNormLaunch& launch, cudaStream_t stream);
+cudaError_t launch_layer_norm_fp8(const LayerNormLaunch& launch, cudaStream_t stream, bool early_launch);
 
 }  // namespace sdxlq

@@ -35,10 +35,14 @@ def test_ctypes_structures_match_the_c_layout(pkg, tmp_path):
     source.write_text(
         '#include "sdxlq.h"\n#include <stdio.h>\n#include <stddef.h>\n'
         "int main(void) {\n"
-        '  printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(sdxlq_weight), sizeof(sdxlq_linear_desc),\n'
+        '  printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(sdxlq_weight),\n'
+        "         sizeof(sdxlq_linear_desc),\n"
         "         offsetof(sdxlq_linear_desc, weight), offsetof(sdxlq_linear_desc, bias),\n"
         "         offsetof(sdxlq_linear_desc, y), offsetof(sdxlq_linear_desc, acc_out),\n"
-        "         offsetof(sdxlq_weight, convrot_group_size), sizeof(sdxlq_int8_stats));\n"
+        "         offsetof(sdxlq_weight, convrot_group_size), sizeof(sdxlq_int8_stats),\n"
+        "         offsetof(sdxlq_linear_desc, residual), sizeof(sdxlq_layer_norm_desc),\n"
+        "         offsetof(sdxlq_layer_norm_desc, epsilon), offsetof(sdxlq_layer_norm_desc, y),\n"
+        "         offsetof(sdxlq_layer_norm_desc, xq_scales), sizeof(sdxlq_kernel_times));\n"
         "  return 0;\n}\n")
     binary = tmp_path / "layout"
     subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(source), "-o", str(binary)], check=True)
@@ -46,7 +50,10 @@ def test_ctypes_structures_match_the_c_layout(pkg, tmp_path):
     api = pkg.api
     py_sizes = [ctypes.sizeof(api._CWeight), ctypes.sizeof(api._CLinearDesc), api._CLinearDesc.weight.offset,
                 api._CLinearDesc.bias.offset, api._CLinearDesc.y.offset, api._CLinearDesc.acc_out.offset,
-                api._CWeight.convrot_group_size.offset, ctypes.sizeof(api._CStats)]
+                api._CWeight.convrot_group_size.offset, ctypes.sizeof(api._CStats),
+                api._CLinearDesc.residual.offset, ctypes.sizeof(api._CLayerNormDesc),
+                api._CLayerNormDesc.epsilon.offset, api._CLayerNormDesc.y.offset,
+                api._CLayerNormDesc.xq_scales.offset, ctypes.sizeof(api._CKernelTimes)]
     assert c_sizes == py_sizes
 
 

@@ -14,7 +14,7 @@ Bars, stated here and asserted below:
     cuBLASLt FP8 route): max |a-b| / max|b| <= 5e-3 and <= 4 FP16 ulps on outputs of at least 1 % of
     the largest; both sides accumulate on the tensor cores and round to FP16 once, but the library
     kernel's accumulation order and the order of the scale multiplications differ (measured on
-    B200: up to 3 ulps, 4.2e-3 of the largest output at K = 2816). Against the exact
+    B200: up to 3 ulps at K = 2816). Against the exact
     FP64-accumulated product of the same FP8 operands this library is asserted to be no further
     away than the reference's own result (plus one FP16 ulp of the largest output).
   * FP16 projection against the reference with FP32 accumulation: the same bounds as FP8 above
@@ -92,9 +92,13 @@ def test_fp8_quantiser_equals_reference_device_code(gpu, ref_ieee, ref_fast, fmt
     (256, 1280, 1280, 0, True), (2048, 640, 640, 0, False), (160, 1280, 2048, 0, True), (512, 2560, 640, 4, True),
     (32, 1280, 2816, 1, True), (256, 5120, 1280, 2, True),
 ])
-def test_native_fp8_linear_matches_reference_device_code(gpu, ref_fast, fmt, m, n, k, activation, bias):
+def test_native_fp8_linear_matches_reference_device_code(gpu, ref_ieee, ref_fast, fmt, m, n, k, activation, bias):
     """Tensor-wide E4M3 weights on aligned shapes: the reference takes its cuBLASLt FP8 route
-    (src/cuda/ops_blas.cpp:262-298, 153-225)."""
+    (src/cuda/ops_blas.cpp:262-298, 153-225). The tight bars are against its IEEE build, whose
+    activation quantiser produces the same bytes as this library's; under --use_fast_math the
+    reference's scale differs in its last bit (approximate division), a share of its FP8 bytes land
+    one step away and its projection moves by up to 6e-3 of the largest output, so that build is
+    held to an RMS bound only."""
     pkg, ctx, ops = gpu
     x = H.make_activations(320, m, k, outliers=False)
     w = H.make_weight(321, n, k)
@@ -106,11 +110,14 @@ def test_native_fp8_linear_matches_reference_device_code(gpu, ref_fast, fmt, m, 
     else:
         y = ops.linear(dev(x), weight, dev(b) if bias else None)
     ctx.check()
-    want_bits = ref_fast.ops_linear(x.view(np.uint16), wq, "e4m3" if fmt == 0 else "e5m2", ws,
+    want_bits = ref_ieee.ops_linear(x.view(np.uint16), wq, "e4m3" if fmt == 0 else "e5m2", ws,
                                     None if b is None else b.view(np.uint16), activation)
     got_bits = y.cpu().numpy().view(np.uint16)
     got, want = O.h2f(got_bits), O.h2f(want_bits)
     assert got.shape == want.shape
+    fast = O.h2f(ref_fast.ops_linear(x.view(np.uint16), wq, "e4m3" if fmt == 0 else "e5m2", ws,
+                                     None if b is None else b.view(np.uint16), activation))
+    assert H.rms_rel(got, fast) <= 5e-3, H.rms_rel(got, fast)
     assert H.max_abs_over_max(got, want) <= 5e-3, H.max_abs_over_max(got, want)
     large = np.abs(want) >= 1e-2 * np.max(np.abs(want))
     worst = int(H.f16_ulp_distance(got_bits, want_bits)[large].max(initial=0))
