@@ -5,7 +5,8 @@
 
 Default workload `unetloop_e4m3`: the synthetic SDXL Base UNet denoising loop at 1024^2 for a fixed
 job of 8 images x CFG 2 (UNet batch 16), FP8 E4M3 projections (per-output-channel weight scales,
-native FP8 activations), FP16 convolutions / norms / attention from PyTorch around them, Euler
+native FP8 activations), the transformer LayerNorms fused with the quantisers of the projections
+they feed, FP16 convolutions / GroupNorm / attention from PyTorch around them, Euler
 sampler, sigma schedule of 20 steps. A "step" is one denoising step of the whole job: scale the
 latents, one UNet forward over [uncond | cond], CFG combine, Euler update; every 20 steps a new
 generation starts and the cross-attention K/V projections are recomputed once. With N ranks the
@@ -468,6 +469,42 @@ def reference_threaded_rate(rows_table, sample_rows, steps, warmup):
     return elapsed / steps, ops_per_step, threads, ("reference" if use_reference else "port")
 
 
+def reference_device_projections(rows_table, kind):
+    """Context for the reference arm, not its value: the reference's own CUDA operators (its Ops class
+    compiled unmodified for sm_100, oracle/_ref/libsdxl_ref_cuda.so) timed on this box's GPU for every
+    distinct projection shape of the job at full size, operands resident, CUDA events on the reference's
+    stream. Each call is what the reference runs per projection: its FP8 quantiser + cuBLASLt FP8 GEMM
+    (tensor-wide weight scale) or cuBLASLt FP16 GEMM, then its bias / activation kernel. The INT8
+    translation unit of the reference does not compile with this toolchain, so INT8 has no such figure."""
+    try:
+        from oracle import oracle as O
+        if kind == "int8":
+            return {"unavailable": "the reference's INT8 translation unit does not compile with nvcc 12.9"}
+        if not O.RefCuda.available():
+            return {"unavailable": "oracle/_ref/libsdxl_ref_cuda.so was not built"}
+        import torch
+        if not torch.cuda.is_available():
+            return {"unavailable": "no GPU"}
+        reference = O.RefCuda()
+        shapes = {}
+        for (name, m, n, k, bias, activation, key) in rows_table:
+            shapes[(m, n, k, bool(bias), int(activation))] = shapes.get((m, n, k, bool(bias), int(activation)), 0) + 1
+        total_ms, ops, fallbacks = 0.0, 0.0, 0
+        for (m, n, k, bias, activation), count in shapes.items():
+            if kind in ("e4m3", "e5m2") and (m % 16 or n % 16 or k % 16):
+                fallbacks += count                 # the reference takes its weight-only kernel for these
+            ms = reference.time_linear(m, k, n, kind, activation if bias else 0, bias, False, 2, 5)
+            total_ms += ms * count
+            ops += 2.0 * m * n * k * count
+        reference.shutdown()
+        return {"projection_ms_per_step": total_ms, "projection_tops": ops / (total_ms * 1e-3) / 1e12,
+                "distinct_shapes": len(shapes), "projections": len(rows_table), "weight_only_fallbacks": fallbacks,
+                "what": "sum over the job's projections of the reference's CUDA Ops::linear / linear_activation device time "
+                        "on this GPU (sm_100 build of the reference's sources), per call: quantise + GEMM + bias/activation kernel"}
+    except Exception as error:
+        return {"unavailable": f"{type(error).__name__}: {error}"}
+
+
 def reference_arm(args):
     """`--impl reference`: the reference's CPU Linear on a bounded sample, in this arm's metric."""
     loop = args.workload.startswith("unetloop_")
@@ -503,6 +540,8 @@ def reference_arm(args):
         "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "reference_device": reference_device_projections(
+            rows, next((k for k in ("int8", "e4m3", "e5m2", "f16") if k in args.workload), "e4m3" if "fp8" in args.workload else "f16")),
     }
 
 
@@ -515,7 +554,8 @@ def unetloop_description(kind: str) -> str:
              "int8": "W8A8 INT8 ConvRot (group 256 rule)", "f16": "FP16"}
     return (f"synthetic SDXL Base UNet denoising loop, 1024^2, 8 images x CFG 2 (latents [16,4,128,128], context [16,77,2048], "
             f"pooled [16,1280]), {GENERATION_STEPS} Euler steps per generation, random-init weights; projections {names[kind]}; "
-            "FP16 convolutions / norms / attention (PyTorch)")
+            "transformer LayerNorms fused with the activation quantisers (library kernel); FP16 convolutions / GroupNorm / "
+            "attention (PyTorch)")
 
 
 def run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks):
@@ -666,8 +706,12 @@ def run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks):
     eager_ms = eager_start.elapsed_time(eager_stop) / profile_steps
     gemm_ms = kernel_times["gemm"][0] / profile_steps
     gemm_launches = kernel_times["gemm"][1] // profile_steps
-    quant_ms = (kernel_times["quant_int8"][0] + kernel_times["quant_fp8"][0]) / profile_steps
-    quant_launches = (kernel_times["quant_int8"][1] + kernel_times["quant_fp8"][1]) // profile_steps
+    # the LayerNorm -> quantiser kernels do the quantisers' work for the inputs they feed (same algorithmic
+    # bytes: the normalised tensor is read where the stand-alone quantiser would read its input)
+    norm_ms = kernel_times["layer_norm"][0] / profile_steps
+    norm_launches = kernel_times["layer_norm"][1] // profile_steps
+    quant_ms = (kernel_times["quant_int8"][0] + kernel_times["quant_fp8"][0]) / profile_steps + (norm_ms if kind != "f16" else 0.0)
+    quant_launches = (kernel_times["quant_int8"][1] + kernel_times["quant_fp8"][1]) // profile_steps + norm_launches
     small_launches = kernel_times["small"][1] // profile_steps
     launches_per_step = int(gemm_launches + quant_launches + small_launches)
     # time of the K/V plan (once per generation)
@@ -734,7 +778,7 @@ def run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks):
         "projection_tops_per_gpu": step_ops / (projection_ms * 1e-3) / 1e12 if projection_ms > 0 else None,
         "projection_gemm_tops_per_gpu": achieved,
         "projection_share_of_step": projection_ms / ms_per_step if ms_per_step > 0 else None,
-        "projection_ms_per_step": {"gemm": gemm_ms, "quantize": quant_ms},
+        "projection_ms_per_step": {"gemm": gemm_ms, "quantize": quant_ms, "of_which_layer_norm_fused": norm_ms},
         "eager_ms_per_step": eager_ms,
         "kv_cache": {"gemm_ms_per_generation": kv_gemm_ms, "ops": kv_ops, "launches": int(kv_launches)},
         "roofline": roofline,

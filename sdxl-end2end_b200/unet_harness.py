@@ -233,11 +233,16 @@ class UNetHarness:
 
     precision: "e4m3" / "e5m2" (FP8 per-output-channel weights, native FP8 activations), "int8"
     (W8A8 ConvRot, group-256 rule) or "f16" (dense FP16 weights). `fuse_residual` folds the
-    add_in_place after to_out / ff.net.2 / proj_out into the projection's epilogue."""
+    add_in_place after to_out / ff.net.2 / proj_out into the projection's epilogue.
+    `fuse_layer_norm` runs the three LayerNorms of a transformer block through the library's
+    kernel, fused with the activation quantiser of the projections that read them (to_q / to_k /
+    to_v, attn2.to_q, ff.net.0.proj) for the quantised profiles; without it they are separate
+    PyTorch layer_norm calls and the projections quantise their input themselves."""
 
     def __init__(self, ops: Ops, config: UNetConfig = BASE_1_0, precision: str = "e4m3", seed: int = 0,
                  parameters: Optional[Dict[str, torch.Tensor]] = None, fuse_residual: bool = True,
-                 group_attention_inputs: bool = True, device: Optional[torch.device] = None):
+                 group_attention_inputs: bool = True, device: Optional[torch.device] = None,
+                 fuse_layer_norm: bool = True):
         if precision not in ("e4m3", "e5m2", "int8", "f16"):
             raise CudaError(f"unknown precision profile {precision}")
         self.ops = ops
@@ -245,6 +250,7 @@ class UNetHarness:
         self.precision = precision
         self.fuse_residual = fuse_residual
         self.group_attention_inputs = group_attention_inputs
+        self.fuse_layer_norm = fuse_layer_norm
         self.device = device if device is not None else torch.device("cuda", ops.ctx.device)
         source = parameters if parameters is not None else synthetic_parameters(config, self.device, seed)
         self.projections: Dict[str, Weight] = {}
@@ -288,15 +294,20 @@ class UNetHarness:
         return self.tensors[f"{prefix}.bias"]
 
     def _linear(self, x, prefix, activation=ACT_NONE, residual=None, out=None, bias=True):
+        """x is an FP16 tensor, or the (xq, xq_scales) pair of a fused LayerNorm."""
         self.projection_calls += 1
         b = self._bias(prefix) if bias else None
+        quantised = {}
+        if isinstance(x, tuple):
+            quantised = {"xq": x[0], "xq_scales": x[1]}
+            x = None
         if activation != ACT_NONE:
-            return self.ops.linear_activation(x, self.projections[prefix], b, activation)
+            return self.ops.linear_activation(x, self.projections[prefix], b, activation, **quantised)
         if residual is not None and not self.fuse_residual:
-            y = self.ops.linear(x, self.projections[prefix], b)
+            y = self.ops.linear(x, self.projections[prefix], b, **quantised)
             residual.add_(y)                                   # Ops::add_in_place, FP16
             return residual
-        return self.ops.linear(x, self.projections[prefix], b, residual=residual, out=out)
+        return self.ops.linear(x, self.projections[prefix], b, residual=residual, out=out, **quantised)
 
     def _group_norm(self, x, prefix, eps=1e-5, silu=False):
         y = F.group_norm(x, self.config.norm_groups, self.tensors[f"{prefix}.weight"], self.tensors[f"{prefix}.bias"], eps)
@@ -305,8 +316,15 @@ class UNetHarness:
     def _conv(self, x, prefix, stride=1, padding=1):
         return F.conv2d(x, self.tensors[f"{prefix}.weight"], self.tensors[f"{prefix}.bias"], stride=stride, padding=padding)
 
-    def _layer_norm(self, x, prefix):
-        return F.layer_norm(x, (x.shape[-1],), self.tensors[f"{prefix}.weight"], self.tensors[f"{prefix}.bias"], 1e-5)
+    def _layer_norm(self, x, prefix, consumer: str):
+        """Ops::layer_norm in front of the projection `consumer`. Returns an FP16 tensor, or with the
+        fused quantised form the (xq, xq_scales) pair that projection (and its siblings) take."""
+        gamma, beta = self.tensors[f"{prefix}.weight"], self.tensors[f"{prefix}.bias"]
+        if not self.fuse_layer_norm:
+            return F.layer_norm(x, (x.shape[-1],), gamma, beta, 1e-5)
+        if self.precision == "f16":
+            return self.ops.layer_norm(x, gamma, beta, 1e-5)
+        return self.ops.layer_norm_quantized(x, gamma, beta, self.projections[consumer], 1e-5)
 
     @staticmethod
     def _attention(query, key, value, heads):
@@ -377,11 +395,14 @@ class UNetHarness:
         return hidden + residual
 
     def _transformer_block(self, prefix, hidden, heads):
-        normalized = self._layer_norm(hidden, f"{prefix}.norm1")
         names = [f"{prefix}.attn1.to_q", f"{prefix}.attn1.to_k", f"{prefix}.attn1.to_v"]
+        normalized = self._layer_norm(hidden, f"{prefix}.norm1", names[0])
         if self.group_attention_inputs:
             # to_q / to_k / to_v read the same tensor: one quantisation, one GEMM launch
-            calls = [LinearCall(normalized, self.projections[name]) for name in names]
+            if isinstance(normalized, tuple):
+                calls = [LinearCall(None, self.projections[name], xq=normalized[0], xq_scales=normalized[1]) for name in names]
+            else:
+                calls = [LinearCall(normalized, self.projections[name]) for name in names]
             query, key, value = self.ops.linear_grouped(calls)
             self.projection_calls += 3
         else:
@@ -389,13 +410,13 @@ class UNetHarness:
         attention = self._attention(query, key, value, heads)
         hidden = self._linear(attention, f"{prefix}.attn1.to_out.0", residual=hidden, out=hidden)
 
-        normalized = self._layer_norm(hidden, f"{prefix}.norm2")
+        normalized = self._layer_norm(hidden, f"{prefix}.norm2", f"{prefix}.attn2.to_q")
         query = self._linear(normalized, f"{prefix}.attn2.to_q", bias=False)
         key, value = self._kv[f"{prefix}.attn2.to_k"], self._kv[f"{prefix}.attn2.to_v"]
         attention = self._attention(query, key, value, heads)
         hidden = self._linear(attention, f"{prefix}.attn2.to_out.0", residual=hidden, out=hidden)
 
-        normalized = self._layer_norm(hidden, f"{prefix}.norm3")
+        normalized = self._layer_norm(hidden, f"{prefix}.norm3", f"{prefix}.ff.net.0.proj")
         feed_forward = self._linear(normalized, f"{prefix}.ff.net.0.proj", ACT_GEGLU)
         hidden = self._linear(feed_forward, f"{prefix}.ff.net.2", residual=hidden, out=hidden)
         return hidden

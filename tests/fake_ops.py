@@ -66,6 +66,10 @@ class FakeOps:
             return (value * F.gelu(gate)).to(torch.float16)
         raise NotImplementedError(activation)
 
+    def layer_norm(self, x, gamma, beta, epsilon=1.0e-5, out=None):
+        self.log.append(("layer_norm", x.numel() // x.shape[-1], x.shape[-1], 0, True, 0, False))
+        return F.layer_norm(x.float(), (x.shape[-1],), gamma.float(), beta.float(), epsilon).to(torch.float16)
+
     def linear(self, x, weight, bias=None, *, residual=None, out=None, **_):
         self.log.append(("linear", x.numel() // weight.k, weight.n, weight.k, bias is not None, 0, residual is not None))
         y = self._compute(x, weight, bias, 0, residual)

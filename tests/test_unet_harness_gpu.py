@@ -86,6 +86,22 @@ def test_fused_residual_and_grouping_do_not_change_results(gpu, precision):
     assert np.array_equal(fused, plain)
 
 
+@pytest.mark.parametrize("precision,bound", [("f16", 5e-3), ("e4m3", 3e-2), ("int8", 3e-2)])
+def test_fused_layer_norm_stays_within_rounding(gpu, precision, bound):
+    """The library's LayerNorm (fused with the quantisers for the quantised profiles) against
+    PyTorch's layer_norm in front of self-quantising projections. The two LayerNorms differ in the
+    last FP16 bit of a small share of their outputs; behind a quantiser such a flip moves a byte by
+    one step, so the UNet outputs agree to the quantisation noise, not bit for bit."""
+    pkg, ctx, ops = gpu
+    params = parameters(13)
+    data = inputs(2, seed=14)
+    fused, _ = run_forward(ops, precision, params, data)
+    plain, _ = run_forward(ops, precision, params, data, fuse_layer_norm=False)
+    rms = float(np.sqrt(np.mean((fused - plain) ** 2)) / np.sqrt(np.mean(plain ** 2)))
+    print(f"{precision}: fused vs separate LayerNorm rms rel = {rms:.3e}")
+    assert rms <= bound
+
+
 def test_graph_replay_equals_eager_loop(gpu):
     pkg, ctx, ops = gpu
     params = parameters(9)
