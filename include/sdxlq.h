@@ -264,12 +264,11 @@ size_t sdxlq_workspace_bytes(const sdxlq_linear_desc* descs, size_t count);
  * 0 restores the built-in choice). For tuning sweeps. */
 int sdxlq_context_set_tile_n(sdxlq_context* ctx, int tile_n);
 
-/* Selects the GEMM kernel flavour of grouped launches: 0 (default) runs every tile on one CTA
- * (128 rows); 1 uses CTA pairs (cta_group::2, 256-row tiles, each CTA loading half of the weight
- * rows) for every projection with more than 128 rows; -1 uses pairs only for projections of
- * launches that fill the GPU several times over. Pairs measured no faster than single CTAs on
- * B200 for this path, so they are opt-in; single calls always use single CTAs. For tuning sweeps
- * and tests. */
+/* Selects the GEMM kernel flavour: 0 (default) runs every tile on one CTA (128 rows); 1 uses CTA
+ * pairs (cta_group::2, 256-row tiles, each CTA loading half of the weight rows) for every projection
+ * with more than 128 rows; -1 uses pairs only for projections of launches that fill the GPU several
+ * times over. Results are bit-identical between the flavours. Pairs measured no faster than single
+ * CTAs on B200 for this path, so they are opt-in. For tuning sweeps and tests. */
 int sdxlq_context_set_pair_mode(sdxlq_context* ctx, int mode);
 
 /* Per-kernel device timing. While enabled, every kernel launch of the library is bracketed by a

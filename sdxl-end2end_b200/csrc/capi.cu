@@ -25,7 +25,7 @@
 
 namespace sdxlq {
 cudaError_t launch_umma_gemm(const GemmLaunchParams& params, uint32_t grid, size_t dynamic_smem,
-                             cudaStream_t stream, int device, bool pair, bool early_launch);
+                             cudaStream_t stream, int device, bool pair, bool early_launch, int operand_class);
 size_t umma_gemm_control_bytes();
 cudaError_t launch_small_linear(const void* a, const void* b, const EpilogueParams& ep, uint32_t k_major,
                                 cudaStream_t stream);
@@ -222,9 +222,8 @@ TileChoice choose_tile(const sdxlq_context* ctx, uint32_t m, uint32_t n, bool ge
     // `siblings`: problems of (about) this shape that share the launch (a small inline group)
     const uint64_t tiles_at_widest = static_cast<uint64_t>(siblings) * tiles_m * ((columns + (geglu ? 127 : 255)) / (geglu ? 128 : 256));
     const bool traffic_bound = grouped ? tiles_m >= 2 : tiles_at_widest >= 3ull * sms;
-    // CTA pairs serve grouped launches only: with a single problem in the kernel parameters the pair
-    // flavour mis-scales part of its FP16 output (accumulators are right), so it is not offered there.
-    const bool pair_allowed = grouped && ctx->pair_mode != 0 && m > kTileM && (traffic_bound || ctx->pair_mode == 1);
+    // CTA pairs are opt-in (pair_mode): single calls, inline groups and plans all take them then.
+    const bool pair_allowed = ctx->pair_mode != 0 && m > kTileM && (traffic_bound || ctx->pair_mode == 1);
     if (ctx->forced_tile_n >= 16) {
         const uint32_t forced = std::min<uint32_t>(kMaxTileN, static_cast<uint32_t>(ctx->forced_tile_n));
         const uint32_t pair_step = 32;
@@ -697,9 +696,16 @@ int run_gemm_flavour(sdxlq_context* ctx, const Prepared& prep, int flavour, cons
     params.diagnostic_skip = ctx->diagnostic_skip;
     const uint32_t sms = static_cast<uint32_t>(ctx->sm_count);
     const uint32_t grid = pair ? 2 * std::min<uint32_t>(params.num_tiles, sms / 2) : std::min<uint32_t>(params.num_tiles, sms);
+    // the kernel instance compiled for one operand class when every problem of the launch has it
+    int operand_class = -1;
+    for (const GemmProblem& problem : prep.problems[flavour]) {
+        const int this_class = problem.ep.kind == KIND_I8 ? 0 : (problem.ep.kind == KIND_F16 ? 2 : 1);
+        if (operand_class == -1) operand_class = this_class;
+        else if (operand_class != this_class) { operand_class = -2; break; }
+    }
     LaunchTimer timer(ctx, SDXLQ_KERNEL_GEMM);
     const cudaError_t error = launch_umma_gemm(params, grid, geometry.dynamic_smem, ctx->stream, ctx->device, pair,
-                                               ctx->early_launch && !ctx->profiling);
+                                               ctx->early_launch && !ctx->profiling, operand_class);
     if (error != cudaSuccess) return fail_cuda(ctx, error, "tensor-core GEMM launch");
     return SDXLQ_OK;
 }
@@ -796,9 +802,9 @@ int run_prepared(sdxlq_context* ctx, const Prepared& prep, const sdxlq_group_pla
 }
 
 // True when every kernel of the prepared set can take its operands from the kernel parameters: at
-// most kInlineProblems GEMM problems on single CTAs and one quantiser job per kernel flavour.
+// most kInlineProblems GEMM problems per kernel flavour and one quantiser job per quantiser kernel.
 bool fits_inline(const Prepared& prep) {
-    if (!prep.problems[1].empty() || prep.problems[0].size() > kInlineProblems) return false;
+    if (prep.problems[1].size() > kInlineProblems || prep.problems[0].size() > kInlineProblems) return false;
     for (int f = 0; f < INT8_FLAVOURS; ++f) if (prep.int8[f].jobs.size() > 1) return false;
     return prep.fp8_jobs.size() <= 1;
 }

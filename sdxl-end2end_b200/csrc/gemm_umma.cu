@@ -497,7 +497,12 @@ __device__ __forceinline__ bool issue_tile_mmas(MmaCursor& c, uint32_t tmem_d, u
 //   and write 128 accumulator rows into each CTA's tensor memory. Every TMA load of the pair counts
 //   on the leader's full barrier; the MMA completion is committed to both CTAs' empty / acc_full
 //   barriers; both CTAs' epilogue warps arrive on the leader's acc_empty barriers.
-template <bool kPair>
+//
+// kClass fixes the operand class of every problem of the launch at compile time (0 INT8, 1 FP8, 2 FP16;
+// the host picks the instance when all problems agree, which is every launch of one precision
+// profile), so that the issuer and the epilogue warps carry one arithmetic variant instead of three;
+// -1 keeps the per-tile switch for mixed launches.
+template <bool kPair, int kClass>
 __global__ void __launch_bounds__(kThreads, 1)
 sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
     extern __shared__ __align__(128) uint8_t dynamic_smem[];
@@ -596,7 +601,7 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                 const uint32_t half = tile_n / 2;
                 // bytes that land per stage, over both CTAs of a pair
                 const uint32_t tx_bytes = (kPair ? 2 * kTileM + tile_n : kTileM + tile_n) * kTileKBytes;
-                const int32_t k_step = work.kind == KIND_F16 ? 64 : 128;   // elements per stage
+                const int32_t k_step = (kClass < 0 ? work.kind == KIND_F16 : kClass == 2) ? 64 : 128;   // elements per stage
                 const int32_t row_a = static_cast<int32_t>(work.tile_m * kRowsPerTile + cta_rank * kTileM);
                 const int32_t row_b = static_cast<int32_t>(work.tile_n_index * (geglu ? half : tile_n));
                 const int32_t row_gate = static_cast<int32_t>(work.n_out) + row_b;
@@ -684,9 +689,13 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                 ptx::tc_fence_after();
                 const uint32_t tmem_d = tmem_base + first_quarter * kQuarterColumns;
                 const uint32_t k_blocks = (skip_loads && skip_mma) ? 0u : work.k_blocks;
-                if (work.kind == KIND_I8) ok = issue_tile_mmas<0, kPair>(cursor, tmem_d, work.idesc, k_blocks);
-                else if (work.kind == KIND_F16) ok = issue_tile_mmas<2, kPair>(cursor, tmem_d, work.idesc, k_blocks);
-                else ok = issue_tile_mmas<1, kPair>(cursor, tmem_d, work.idesc, k_blocks);
+                if constexpr (kClass >= 0) {
+                    ok = issue_tile_mmas<kClass, kPair>(cursor, tmem_d, work.idesc, k_blocks);
+                } else {
+                    if (work.kind == KIND_I8) ok = issue_tile_mmas<0, kPair>(cursor, tmem_d, work.idesc, k_blocks);
+                    else if (work.kind == KIND_F16) ok = issue_tile_mmas<2, kPair>(cursor, tmem_d, work.idesc, k_blocks);
+                    else ok = issue_tile_mmas<1, kPair>(cursor, tmem_d, work.idesc, k_blocks);
+                }
                 if (!ok) {
                     raise_abort(control, params.error_word, DEV_TIMEOUT_MMA + 1);
                     break;
@@ -774,6 +783,9 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             ring.parity ^= 1u << first_quarter;
             ptx::tc_fence_after();
             if (skip_epilogue) { /* diagnostic: accumulators are dropped */ }
+            else if constexpr (kClass == 0) epilogue_dispatch<KIND_I8>(activation, tile);
+            else if constexpr (kClass == 1) epilogue_dispatch<KIND_E4M3>(activation, tile);
+            else if constexpr (kClass == 2) epilogue_dispatch<KIND_F16>(activation, tile);
             else if (kind == KIND_I8) epilogue_dispatch<KIND_I8>(activation, tile);
             else if (kind == KIND_F16) epilogue_dispatch<KIND_F16>(activation, tile);
             else epilogue_dispatch<KIND_E4M3>(activation, tile);
@@ -828,22 +840,31 @@ size_t umma_gemm_control_bytes() { return (sizeof(Control) + 1023u + 1023u) / 10
 // flavour, which is launched as clusters of two). The opt-in to more than 48 KB of dynamic shared
 // memory is a per-device, process-wide property of the kernel, not of a context: both flavours are
 // opted into the architectural maximum once per device, so that contexts with different tile
-// geometries on one GPU cannot lower each other's limit.
+// geometries on one GPU cannot lower each other's limit. `operand_class` (0 INT8, 1 FP8, 2 FP16)
+// selects the instance compiled for one operand class when every problem of the launch has it, -1
+// the one that switches per tile.
 cudaError_t launch_umma_gemm(const GemmLaunchParams& params, uint32_t grid, size_t dynamic_smem,
-                             cudaStream_t stream, int device, bool pair, bool early_launch) {
-    auto kernel = pair ? sdxlq_umma_gemm_kernel<true> : sdxlq_umma_gemm_kernel<false>;
+                             cudaStream_t stream, int device, bool pair, bool early_launch, int operand_class) {
+    using Kernel = void (*)(GemmLaunchParams);
+    static const Kernel kernels[2][4] = {
+        {sdxlq_umma_gemm_kernel<false, -1>, sdxlq_umma_gemm_kernel<false, 0>, sdxlq_umma_gemm_kernel<false, 1>,
+         sdxlq_umma_gemm_kernel<false, 2>},
+        {sdxlq_umma_gemm_kernel<true, -1>, sdxlq_umma_gemm_kernel<true, 0>, sdxlq_umma_gemm_kernel<true, 1>,
+         sdxlq_umma_gemm_kernel<true, 2>}};
+    const int instance = (operand_class >= 0 && operand_class <= 2) ? operand_class + 1 : 0;
+    const Kernel kernel = kernels[pair ? 1 : 0][instance];
     constexpr int kMaxDevices = 64;
     constexpr int kSharedMemoryOptIn = 232448;      // 227 KiB per CTA on sm_100
     static std::mutex opt_in_mutex;
-    static bool opted_in[kMaxDevices][2] = {};
+    static bool opted_in[kMaxDevices][2][4] = {};
     if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
     {
         std::lock_guard<std::mutex> lock(opt_in_mutex);
-        if (!opted_in[device][pair ? 1 : 0]) {
+        if (!opted_in[device][pair ? 1 : 0][instance]) {
             const cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                             kSharedMemoryOptIn);
             if (status != cudaSuccess) return status;
-            opted_in[device][pair ? 1 : 0] = true;
+            opted_in[device][pair ? 1 : 0][instance] = true;
         }
     }
     cudaLaunchConfig_t config{};

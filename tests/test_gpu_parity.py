@@ -404,8 +404,8 @@ def test_native_fp8_checkpoint_is_kept_verbatim(gpu):
 @pytest.mark.parametrize("pair_mode", [0, 1, -1])
 def test_grouped_launch_equals_single_calls(gpu, pair_mode):
     """pair_mode 1 / -1 run the 256-row tiles of the plan on CTA pairs (cta_group::2); the single
-    calls they are compared with always run on single CTAs, so the two kernel flavours must agree
-    bit for bit (outputs the fixture allocates start as NaN, so nothing may stay unwritten)."""
+    calls they are compared with are made with pair_mode 0, on single CTAs, so the two kernel flavours
+    must agree bit for bit (outputs the fixture allocates start as NaN, so nothing may stay unwritten)."""
     pkg, ctx, ops = gpu
     ctx.set_pair_mode(pair_mode)
     x1 = dev(H.make_activations(1, 300, 640))
@@ -434,15 +434,34 @@ def test_grouped_launch_equals_single_calls(gpu, pair_mode):
     grouped = [y.clone() for y in plan.run()]
     grouped_again = [y.clone() for y in plan.run()]
     ctx.check()
+    one_shot = ops.linear_grouped([pkg.LinearCall(x1, wq), pkg.LinearCall(x3, wemb, bias_emb)])
+    ctx.set_pair_mode(0)
     for call, y, y2 in zip(calls, grouped, grouped_again):
         single = ops.linear_activation(call.x, call.weight, call.bias, call.activation) if call.activation \
             else ops.linear(call.x, call.weight, call.bias)
         assert torch.equal(y, single)
         assert torch.equal(y2, single)
     plan.close()
-    one_shot = ops.linear_grouped([pkg.LinearCall(x1, wq), pkg.LinearCall(x3, wemb, bias_emb)])
-    ctx.set_pair_mode(0)
     assert torch.equal(one_shot[0], grouped[0]) and torch.equal(one_shot[1], grouped[4])
+
+
+@pytest.mark.parametrize("m,n,k,activation", [(300, 640, 640, 0), (2048, 1280, 1280, 0), (1024, 5120, 640, 4), (513, 256, 2560, 1)])
+def test_cta_pair_flavour_equals_single_cta_for_single_calls(gpu, m, n, k, activation):
+    """One projection per call (its problem record travels in the kernel parameters) on CTA pairs
+    (cta_group::2) against the same call on single CTAs: bit-identical, nothing left unwritten."""
+    pkg, ctx, ops = gpu
+    x = dev(H.make_activations(61, m, k))
+    weight, _, _ = int8_weight(pkg, n, k, 0, 62)
+    bias = dev(H.make_bias(63, n))
+    outputs = []
+    for mode in (0, 1):
+        ctx.set_pair_mode(mode)
+        y = ops.linear_activation(x, weight, bias, activation) if activation else ops.linear(x, weight, bias)
+        ctx.check()
+        outputs.append(y.clone())
+    ctx.set_pair_mode(0)
+    assert not torch.isnan(outputs[1]).any()
+    assert torch.equal(outputs[0], outputs[1])
 
 
 def test_empty_input_is_a_no_op(gpu):
