@@ -13,18 +13,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* pointer) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
 }
 
-__device__ __forceinline__ bool elect_one() {
-    uint32_t predicate = 0;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "elect.sync _|p, 0xffffffff;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}\n"
-        : "=r"(predicate));
-    return predicate != 0;
-}
-
 // ---- mbarrier ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -89,35 +77,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tenso
         : "memory");
 }
 
-__device__ __forceinline__ void tma_store_2d(const void* tensor_map, uint32_t smem_src, int32_t x,
-                                             int32_t y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-        ::"l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(smem_src), "r"(x), "r"(y)
-        : "memory");
-}
-
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-
-template <int Pending>
-__device__ __forceinline__ void tma_store_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(Pending) : "memory");
-}
-
-__device__ __forceinline__ void fence_proxy_async_smem() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
 // Orders a tensor map that was written to global memory by the host (cudaMemcpy) before its
 // first use by this CTA's TMA unit.
 __device__ __forceinline__ void fence_tensormap_acquire(const void* tensor_map) {
     asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;"
                  ::"l"(reinterpret_cast<uint64_t>(tensor_map))
                  : "memory");
-}
-
-__device__ __forceinline__ void prefetch_tensormap(const void* tensor_map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensor_map)) : "memory");
 }
 
 // ---- tcgen05 -----------------------------------------------------------------------------
@@ -152,30 +117,6 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64
         ".reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
-        "}\n"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_f8f6f4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                            uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
-        "}\n"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                         uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
         "}\n"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
@@ -321,7 +262,6 @@ __device__ __forceinline__ void setmaxnreg_inc() {
 // was launched with the programmatic attribute start being scheduled. Both do nothing in a grid
 // launched without such a dependency.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- CTA pairs (cta_group::2) ----------------------------------------------------------------
 // Two CTAs of a cluster work on one 256-row tile: each loads its 128 rows of A and half of the B
@@ -399,20 +339,6 @@ SDXLQ_UMMA_PAIR(umma_f16_pair, "f16")
 __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_address) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_address)
                  : "memory");
-}
-
-// ---- UMMA descriptors ----------------------------------------------------------------------
-// Shared-memory operand descriptor for a K-major tile stored as rows of 128 bytes with the
-// 128-byte swizzle (what a SWIZZLE_128B TMA box of 128-byte rows produces): 8-row groups are
-// 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
-__device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_address) {
-    uint64_t desc = 0;
-    desc |= static_cast<uint64_t>((smem_address & 0x3FFFFu) >> 4);      // start address
-    desc |= static_cast<uint64_t>(1) << 16;                             // leading byte offset (unused)
-    desc |= static_cast<uint64_t>(1024 >> 4) << 32;                     // stride byte offset
-    desc |= static_cast<uint64_t>(1) << 46;                             // descriptor version
-    desc |= static_cast<uint64_t>(2) << 61;                             // SWIZZLE_128B
-    return desc;
 }
 
 // Instruction descriptor for kind::i8 / kind::f8f6f4 / kind::f16, both operands K-major.

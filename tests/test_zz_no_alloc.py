@@ -96,3 +96,35 @@ def test_static_linear_rejects_what_does_not_fit(gpu):
     status, message, y = static_linear(pkg, ops, pkg.LinearCall(dev(xs), small))
     assert status == 0, message
     assert np.array_equal(y.cpu().numpy().view(np.uint16), O.int8_convrot_linear(xs, wq, ws, 256)["out"])
+
+
+def test_static_linear_leaves_device_memory_untouched(gpu):
+    """cudaMemGetInfo before and after a burst of calls through the static entry point: the free
+    figure does not move, i.e. the entry point neither allocates device memory nor grows a pool
+    (outputs and inputs are allocated before the first reading; the first call of the process has
+    already run in the tests above, so module loading is behind us)."""
+    pkg, ctx, ops = gpu
+    cases = []
+    for seed, (m, n, k, group, activation) in enumerate([(300, 1280, 1280, 256, pkg.ACT_NONE), (1024, 2560, 640, 0, pkg.ACT_GEGLU),
+                                                        (154, 640, 2048, 256, pkg.ACT_NONE)]):
+        weight, _, _ = int8_weight(pkg, n, k, group, 70 + seed)
+        x = dev(H.make_activations(70 + seed, m, k))
+        bias = dev(H.make_bias(70 + seed, n))
+        y = torch.empty((m, n // 2 if activation == pkg.ACT_GEGLU else n), dtype=torch.float16, device="cuda")
+        cases.append(pkg.LinearCall(x, weight, bias, activation, y))
+    wq, ws = O.fp8_quantize_weight(H.make_weight(75, 640, 2048).astype(np.float32), 0, True)
+    weight8 = pkg.Weight(dev(wq), pkg.ScalarType.Float8E4M3, 640, 2048, dev(ws), pkg.FP8ScaleMode.PerOutputChannel)
+    cases.append(pkg.LinearCall(dev(H.make_activations(75, 154, 2048, outliers=False)), weight8, None, pkg.ACT_NONE,
+                                torch.empty((154, 640), dtype=torch.float16, device="cuda")))
+    for call in cases:                                     # once before the reading
+        status, message, _ = static_linear(pkg, ops, call)
+        assert status == 0, message
+    torch.cuda.synchronize()
+    free_before, total = torch.cuda.mem_get_info()
+    for _ in range(5):
+        for call in cases:
+            status, message, _ = static_linear(pkg, ops, call)
+            assert status == 0, message
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
