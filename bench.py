@@ -345,6 +345,54 @@ def library_same_shapes(torch, ops, rows, kind, work):
         return {"ms_per_step": None, "tops": None, "what": f"library arm unavailable: {type(error).__name__}: {error}"}
 
 
+def time_norm_quantize(torch, pkg, ops, peaks):
+    """The LayerNorm kernels on the row counts of the UNet loop (UNet batch 16 at 1024^2: 65536 tokens x 640,
+    16384 tokens x 1280), four rotating inputs per shape so that every launch reads from HBM (4 x 84 MB and
+    4 x 42 MB against 132 MB of L2): FP16 LayerNorm, LayerNorm fused with the FP8 / INT8 quantiser, and the
+    stand-alone quantisers for comparison. GB/s are algorithmic bytes (FP16 in/out 2 + 2; FP8 2 + 2 + 1: the
+    tensor-wide maximum needs a pass of its own; INT8 2 + 1) over the CUDA-event time of the launches."""
+    result = {}
+    for rows, width in ((65536, 640), (16384, 1280)):
+        sets = 4
+        xs = [torch.randn(rows, width, device="cuda", dtype=torch.float16) for _ in range(sets)]
+        gamma = torch.ones(width, device="cuda", dtype=torch.float16)
+        beta = torch.zeros(width, device="cuda", dtype=torch.float16)
+        out = torch.empty(rows, width, device="cuda", dtype=torch.float16)
+        fp8 = pkg.Weight(torch.zeros((16, width), dtype=torch.uint8, device="cuda"), pkg.ScalarType.Float8E4M3, 16, width,
+                         torch.ones(1, device="cuda"), pkg.FP8ScaleMode.TensorWide)
+        group = 256 if width % 256 == 0 else 0
+        int8 = pkg.Weight(torch.zeros((16, width), dtype=torch.int8, device="cuda"), pkg.ScalarType.Int8, 16, width,
+                          torch.ones(16, device="cuda"), pkg.FP8ScaleMode.PerOutputChannel, pkg.FP8StorageLayout.RowMajorNK, group)
+        ys = [ops.layer_norm(x, gamma, beta) for x in xs]
+        cases = {
+            "layer_norm_f16": (4, lambda i: ops.layer_norm(xs[i], gamma, beta, out=out)),
+            "layer_norm_to_fp8": (5, lambda i: ops.layer_norm_quantized(xs[i], gamma, beta, fp8)),
+            "layer_norm_to_int8": (3, lambda i: ops.layer_norm_quantized(xs[i], gamma, beta, int8)),
+            "quantize_fp8": (5, lambda i: ops.quantize_fp8(ys[i], pkg.ScalarType.Float8E4M3)),
+            "quantize_int8": (3, lambda i: ops.quantize_int8(ys[i], group)),
+        }
+        shape = {}
+        for name, (bytes_per_element, call) in cases.items():
+            for i in range(sets):
+                call(i)
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            repeats = 10
+            start.record()
+            for r in range(repeats * sets):
+                call(r % sets)
+            stop.record()
+            torch.cuda.synchronize()
+            ms = start.elapsed_time(stop) / (repeats * sets)
+            gbs = rows * width * bytes_per_element / (ms * 1e-3) / 1e9
+            shape[name] = {"ms": ms, "gbs": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"], "bytes_per_element": bytes_per_element}
+        shape["int8_group"] = group
+        result[f"{rows}x{width}"] = shape
+        del xs, ys, out
+    torch.cuda.empty_cache()
+    return result
+
+
 # ------------------------------------------------------------------------------------------------
 # clocks
 # ------------------------------------------------------------------------------------------------
@@ -552,8 +600,9 @@ def unetloop_description(kind: str) -> str:
     names = {"e4m3": "FP8 E4M3 (per-output-channel weight scales, native FP8 activations)",
              "e5m2": "FP8 E5M2 (per-output-channel weight scales, native FP8 activations)",
              "int8": "W8A8 INT8 ConvRot (group 256 rule)", "f16": "FP16"}
-    return (f"synthetic SDXL Base UNet denoising loop, 1024^2, 8 images x CFG 2 (latents [16,4,128,128], context [16,77,2048], "
-            f"pooled [16,1280]), {GENERATION_STEPS} Euler steps per generation, random-init weights; projections {names[kind]}; "
+    batch = 2 * JOB_IMAGES
+    return (f"synthetic SDXL Base UNet denoising loop, 1024^2, {JOB_IMAGES} images x CFG 2 (latents [{batch},4,128,128], "
+            f"context [{batch},77,2048], pooled [{batch},1280]), {GENERATION_STEPS} Euler steps per generation, random-init weights; projections {names[kind]}; "
             "transformer LayerNorms fused with the activation quantisers (library kernel); FP16 convolutions / GroupNorm / "
             "attention (PyTorch)")
 
@@ -636,6 +685,8 @@ def run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks):
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if sampler:
         sampler.mark_start()
+    if args.profiler_range:
+        torch.cuda.profiler.start()         # a profiler attached with "--profile-from-start off" sees exactly these launches
     start.record(stream)
     for step in range(args.steps * repeats):
         if step and step % GENERATION_STEPS == 0:
@@ -643,6 +694,8 @@ def run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks):
         loop.step()
     stop.record(stream)
     torch.cuda.synchronize()
+    if args.profiler_range:
+        torch.cuda.profiler.stop()
     if sampler:
         sampler.mark_stop()
     elapsed_ms = start.elapsed_time(stop) / repeats
@@ -784,6 +837,8 @@ def run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks):
         "roofline": roofline,
         "library": pkg.load_library().sdxlq_build_info().decode(),
     }
+    if args.profile_images:
+        line["profiling_case"] = f"reduced job of {JOB_IMAGES} images for a profiler capture: not a benchmark value"
 
     # ---- the final latents of every rank gathered on rank 0 (the only collective; outside the step) ----
     if distributed:
@@ -816,7 +871,15 @@ def main():
     parser.add_argument("--no-other-workloads", action="store_true")
     parser.add_argument("--no-graph", action="store_true", help="run the UNet loop eagerly instead of replaying a captured step")
     parser.add_argument("--no-library", action="store_true", help="skip the vendor-library comparison on the same shapes")
+    parser.add_argument("--profiler-range", action="store_true",
+                        help="bracket the timed region of the UNet loop with cudaProfilerStart/Stop (for profiler captures)")
+    parser.add_argument("--profile-images", type=int, default=None,
+                        help="profiler captures only: a reduced job of this many images (1, 2 or 4) so that the process holds a "
+                             "few GB; the line it prints is marked and is not a benchmark value")
     args = parser.parse_args()
+    if args.profile_images:
+        global JOB_IMAGES
+        JOB_IMAGES = int(args.profile_images)
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -867,6 +930,10 @@ def main():
                                                             library=(not args.no_library) and name.startswith(("layerset", "geglu")))
                 except Exception as error:       # a side measurement must not lose the headline line
                     others[name] = {"error": f"{type(error).__name__}: {error}"}
+            try:
+                others["norm_quantize"] = time_norm_quantize(torch, pkg, side_ops, peaks)
+            except Exception as error:
+                others["norm_quantize"] = {"error": f"{type(error).__name__}: {error}"}
             side_context.check()
             side_context.close()
             line["other_workloads"] = others
