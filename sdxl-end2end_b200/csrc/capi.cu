@@ -1240,6 +1240,15 @@ int sdxlq_pack_weight_fp8(sdxlq_context* ctx, const void* src, int32_t src_dtype
     return SDXLQ_OK;
 }
 
+#ifdef SDXLQ_DIAGNOSTICS
+// Tuning build: the 64 control words (error word, then the GEMM kernel's cycle counters of its last launch).
+int sdxlq_debug_read_control(sdxlq_context* ctx, uint32_t* out) {
+    if (ctx == nullptr || out == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    cudaStreamSynchronize(ctx->stream);
+    return cudaMemcpy(out, ctx->control, 64 * sizeof(uint32_t), cudaMemcpyDeviceToHost) == cudaSuccess ? SDXLQ_OK : SDXLQ_ERR_CUDA;
+}
+#endif
+
 int sdxlq_profile_enable(sdxlq_context* ctx, int enabled) {
     if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
     ctx->profiling = enabled != 0;

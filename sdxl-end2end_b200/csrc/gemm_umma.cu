@@ -24,6 +24,18 @@
 
 namespace sdxlq {
 
+// Tuning build only: cycle counters of CTA 0's roles, written behind the error word (words 16..47 of the
+// control buffer) when the kernel ends. DIAG_ADD(counter, statement) times the statement.
+#ifdef SDXLQ_DIAGNOSTICS
+#define DIAG_DECL(name) long long name = 0
+#define DIAG_ADD(name, ...) do { const long long diag_t0 = clock64(); __VA_ARGS__; name += clock64() - diag_t0; } while (0)
+#define DIAG_WRITE(index, value) do { if (blockIdx.x == 0) params.error_word[16 + (index)] = static_cast<uint32_t>(value); } while (0)
+#else
+#define DIAG_DECL(name)
+#define DIAG_ADD(name, ...) do { __VA_ARGS__; } while (0)
+#define DIAG_WRITE(index, value)
+#endif
+
 namespace {
 
 constexpr uint32_t kMaxStages = 8;
@@ -185,10 +197,11 @@ __device__ __forceinline__ __half packed_half(const uint32_t word, int index) {
 // 16 FP16 results of one output row, packed two per word -> global memory. `wide` (row pitch and
 // base 32-byte aligned) writes the 32 bytes with one 256-bit store so that each lane fills a
 // whole memory sector; `vector_ok` (16-byte aligned) uses two 128-bit stores.
+template <bool Fast = false>
 __device__ __forceinline__ void store_row_16(__half* y, uint32_t n_out, bool vector_ok, bool wide, uint32_t row,
                                              uint32_t col0, const uint32_t (&words)[8]) {
     __half* destination = y + static_cast<size_t>(row) * n_out + col0;
-    if (col0 + 16 <= n_out && wide) {
+    if (Fast || (col0 + 16 <= n_out && wide)) {
         asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(destination), "r"(words[0]),
                      "r"(words[1]), "r"(words[2]), "r"(words[3]), "r"(words[4]), "r"(words[5]), "r"(words[6]),
                      "r"(words[7])
@@ -206,10 +219,11 @@ __device__ __forceinline__ void store_row_16(__half* y, uint32_t n_out, bool vec
 
 // The 16 residual values that belong to one row's 16 outputs (packed two per word), loaded the way
 // store_row_16 writes them: one 256-bit load, two 128-bit loads, or element by element at the edge.
+template <bool Fast = false>
 __device__ __forceinline__ void load_row_16(const __half* source, uint32_t n_out, bool vector_ok, bool wide,
                                             uint32_t row, uint32_t col0, uint32_t (&words)[8]) {
     const __half* address = source + static_cast<size_t>(row) * n_out + col0;
-    if (col0 + 16 <= n_out && wide) {
+    if (Fast || (col0 + 16 <= n_out && wide)) {
         asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                      : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3]), "=r"(words[4]), "=r"(words[5]),
                        "=r"(words[6]), "=r"(words[7])
@@ -290,6 +304,7 @@ struct EpilogueTile {
     uint32_t chunk_first;           // which of the warps of this TMEM lane quadrant
     uint32_t activation;            // Activation (read by the run-time activation variant)
     uint32_t flags;                 // bit 0 row in range, bit 1 has bias, bit 2 16-byte stores, bit 3 32-byte stores
+                                    // (bits 4-8: tuning switches of the diagnostics build)
 };
 
 // 16 accumulator columns of one row -> 16 FP16 outputs (no GEGLU): dequantise, bias, activation.
@@ -353,40 +368,73 @@ __device__ __forceinline__ void finish_geglu_8(const EpilogueTile& t, uint32_t c
     }
 }
 
-// Drains this warp's share of one accumulator tile in chunks of 16 output columns (the warps of a
-// TMEM lane quadrant take the chunks round-robin): tensor-memory load, wait, finish, store, one chunk
-// at a time, one output row per lane. Measured slower on B200, same GPU, same run: a
-// software-pipelined form (next chunk's load in flight while the current one is finished: larger
-// code, 7 % slower); swapping chunks between the four lanes of a quad with register shuffles so
-// that every store writes 128 contiguous bytes per row (a quarter of the memory transactions, but the
-// shuffles and selects cost more issue slots than the stores save: 10 % slower); more epilogue warps
-// (12 to 24: no gain, the epilogue is not latency-bound per warp).
+// Drains this warp's share of one accumulator tile in chunks of 16 output columns (the warps of a TMEM
+// lane quadrant take the chunks round-robin): tensor-memory load, wait, finish (dequantise, bias,
+// activation), store, one chunk at a time, one output row per lane.
+//
+// Fast = true (the tile lies inside the matrix in N, the output rows take 32-byte stores, no raw
+// accumulators are wanted: every tile of the SDXL projections except a few edge tiles): the edge
+// handling, the narrow stores and the accumulator dump are compiled out, which keeps the instruction
+// stream of the hot loop short and straight (2 to 6 % on the K = 640 GEGLU tiles).
+//
+// Measured on B200 with parts of this function switched off (tuning build, 128 x 256 INT8 tiles, K = 640,
+// main loop running): about 6000 cycles per tile, of which the stores account for 1900, the arithmetic
+// for 1000 and the tensor-memory loads for nothing. Measured slower or no faster, same GPU, same run:
+//  * a software-pipelined form (next chunk's load in flight while the current one is finished: larger
+//    code, 7 % slower);
+//  * swapping chunks between the four lanes of a quad with register shuffles so that every store writes
+//    128 contiguous bytes per row (the shuffles and selects cost more issue slots than the stores save:
+//    10 % slower);
+//  * bulk tensor stores through shared memory, as 32-byte boxes per chunk (slower) and as 64-byte boxes
+//    per pair of chunks with the 64-byte swizzle (conflict-free staging, a quarter of the store requests:
+//    the same time within 2 %, 20 % slower on 128-column tiles) -- the cost of the stores is not the
+//    load/store unit's transaction count;
+//  * 12 or 16 epilogue warps (the time per tile does not change: the epilogue is not latency-bound
+//    per warp).
 // Kind: 0 INT8, 1 FP8 (either format), 3 FP16.
 // Arithmetic per output, as the reference runs it after the GEMM:
 //   y = half_rn(dequantised accumulator)
 //   no activation : __hadd(y, bias), then __hadd(.., residual)  (add_last_dim_bias_kernel, add_in_place_kernel)
 //   SiLU/GELU/QuickGELU : half_rn(act(float(y) + float(bias))) (bias_activation_in_place_kernel)
 //   GEGLU : half_rn((float(y_v) + float(b_v)) * gelu(float(y_g) + float(b_g)))   (bias_geglu_kernel)
-template <uint32_t Kind, uint32_t Act>
+template <uint32_t Kind, uint32_t Act, bool Fast>
 __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
     const bool row_ok = (t.flags & 1u) != 0;
     const bool has_bias = (t.flags & 2u) != 0;
-    const bool store_vector = (t.flags & 4u) != 0;
-    const bool store_wide = (t.flags & 8u) != 0;
+    const bool store_vector = Fast || (t.flags & 4u) != 0;
+    const bool store_wide = Fast || (t.flags & 8u) != 0;
     const float2 a_scale = make_float2(t.a_scale, t.a_scale);
-    int32_t* const acc_out = Kind == KIND_I8 ? t.acc_out : nullptr;
+    int32_t* const acc_out = (Kind == KIND_I8 && !Fast) ? t.acc_out : nullptr;
     constexpr uint32_t kStride = kWarpsPerQuadrant * 16u;
-    if (Act != ACT_GEGLU) {
-        const uint32_t limit = min(t.tile_n, t.n > t.n0 ? t.n - t.n0 : 0u);
-        const __half* const residual = Act == ACT_NONE ? t.residual : nullptr;
-        const bool with_residual = residual != nullptr && row_ok;
-        for (uint32_t c = t.chunk_first * 16u; c < limit; c += kStride) {
-            const uint32_t col0 = t.n0 + c;
+#ifdef SDXLQ_DIAGNOSTICS
+    // tuning build: parts of the epilogue can be switched off to time the others (general variant only)
+    const bool no_store = !Fast && (t.flags & 16u) != 0, no_load = !Fast && (t.flags & 32u) != 0,
+               no_math = !Fast && (t.flags & 64u) != 0;
+    if (!Fast && (t.flags & 128u) != 0) return;             // nothing at all
+    const uint32_t diag_limit = (!Fast && (t.flags & 256u) != 0) ? 32u : 0xFFFFFFFFu;     // one chunk per warp only
+#else
+    constexpr bool no_store = false, no_load = false, no_math = false;
+    constexpr uint32_t diag_limit = 0xFFFFFFFFu;
+#endif
+    const uint32_t columns = Act == ACT_GEGLU ? t.tile_n / 2u : t.tile_n;        // output columns of the tile
+    const uint32_t limit = Fast ? columns : min(diag_limit, min(columns, t.n_out > t.n0 ? t.n_out - t.n0 : 0u));
+    const __half* const residual = Act == ACT_NONE ? t.residual : nullptr;
+    const bool with_residual = residual != nullptr && row_ok;
+
+    for (uint32_t c = t.chunk_first * 16u; c < limit; c += kStride) {
+        const uint32_t col0 = t.n0 + c;
+        uint32_t out_words[8];
+        if (Act != ACT_GEGLU) {
             uint32_t acc[16];
             uint32_t extra[8] = {};
-            ptx::tmem_ld_32x32b_x16(t.tmem_row + c, acc);
-            if (with_residual) load_row_16(residual, t.n_out, store_vector, store_wide, t.row, col0, extra);
-            ptx::tmem_ld_wait(acc);
+            if (no_load) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[i] = c + t.row + static_cast<uint32_t>(i);
+            } else {
+                ptx::tmem_ld_32x32b_x16(t.tmem_row + c, acc);
+            }
+            if (with_residual) load_row_16<Fast>(residual, t.n_out, store_vector, store_wide, t.row, col0, extra);
+            if (!no_load) ptx::tmem_ld_wait(acc);
             if (acc_out != nullptr && row_ok) {
                 int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n + col0;
 #pragma unroll
@@ -394,8 +442,12 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
                     if (col0 + i < t.n) raw[i] = static_cast<int32_t>(acc[i]);
                 }
             }
-            uint32_t out_words[8];
-            finish_chunk_16<Kind, Act>(t, c, acc, a_scale, has_bias, out_words);
+            if (no_math) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) out_words[i] = acc[2 * i] ^ acc[2 * i + 1];
+            } else {
+                finish_chunk_16<Kind, Act>(t, c, acc, a_scale, has_bias, out_words);
+            }
             if (Act == ACT_NONE && with_residual) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -404,19 +456,13 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
                     out_words[i] = *reinterpret_cast<const uint32_t*>(&sum);
                 }
             }
-            if (row_ok) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
-        }
-    } else {
-        const uint32_t half = t.tile_n / 2;
-        const uint32_t limit = min(half, t.n_out > t.n0 ? t.n_out - t.n0 : 0u);
-        for (uint32_t c0 = t.chunk_first * 16u; c0 < limit; c0 += kStride) {
-            const uint32_t col0 = t.n0 + c0;
-            uint32_t out_words[8];
+        } else {
+            const uint32_t half = t.tile_n / 2u;
 #pragma unroll
             for (uint32_t step = 0; step < 2; ++step) {
                 uint32_t value[8], gate[8];
-                ptx::tmem_ld_32x32b_x8(t.tmem_row + c0 + 8u * step, value);
-                ptx::tmem_ld_32x32b_x8(t.tmem_row + half + c0 + 8u * step, gate);
+                ptx::tmem_ld_32x32b_x8(t.tmem_row + c + 8u * step, value);
+                ptx::tmem_ld_32x32b_x8(t.tmem_row + half + c + 8u * step, gate);
                 ptx::tmem_ld_wait(value, gate);
                 if (acc_out != nullptr && row_ok) {
                     int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n;
@@ -428,18 +474,29 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
                         }
                     }
                 }
-                finish_geglu_8<Kind>(t, c0 + 8u * step, half, value, gate, a_scale, out_words + 4 * step);
+                finish_geglu_8<Kind>(t, c + 8u * step, half, value, gate, a_scale, out_words + 4 * step);
             }
-            if (row_ok) store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
+        }
+        if (row_ok && (!no_store || (out_words[0] == 0x7E57C0DEu && out_words[7] == 0x7E57C0DEu))) {
+            store_row_16<Fast>(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
         }
     }
 }
 
 template <uint32_t Kind>
 __device__ __forceinline__ void epilogue_dispatch(uint32_t activation, const EpilogueTile& t) {
-    if (activation == ACT_NONE) epilogue_tile<Kind, ACT_NONE>(t);
-    else if (activation == ACT_GEGLU) epilogue_tile<Kind, ACT_GEGLU>(t);
-    else epilogue_tile<Kind, kActRuntime>(t);
+    const uint32_t columns = activation == ACT_GEGLU ? t.tile_n / 2u : t.tile_n;     // output columns of the tile
+    // bit 3: 32-byte stores; bits 4 and up: tuning switches of the diagnostics build
+    const bool fast = (t.flags & 8u) != 0 && (t.flags >> 4) == 0 && t.acc_out == nullptr && t.n0 + columns <= t.n_out;
+    if (activation == ACT_NONE) {
+        if (fast) epilogue_tile<Kind, ACT_NONE, true>(t);
+        else epilogue_tile<Kind, ACT_NONE, false>(t);
+    } else if (activation == ACT_GEGLU) {
+        if (fast) epilogue_tile<Kind, ACT_GEGLU, true>(t);
+        else epilogue_tile<Kind, ACT_GEGLU, false>(t);
+    } else {
+        epilogue_tile<Kind, kActRuntime, false>(t);
+    }
 }
 
 }  // namespace
@@ -670,18 +727,29 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             cursor.mode = (skip_mma ? 1u : 0u) | (one_mma_per_stage ? 2u : 0u);
             AccumulatorRing ring;
             bool ok = true;
+            DIAG_DECL(diag_acc_empty_wait); DIAG_DECL(diag_issue);
+#ifdef SDXLQ_DIAGNOSTICS
+            const long long diag_begin = clock64();
+#endif
             TileRef next = load_tile(params, first_tile);
             for (uint32_t t = first_tile; ok && t < num_tiles; t += tile_stride) {
                 const TileRef work = next;
                 next = load_tile(params, t + tile_stride);      // in flight while this tile's MMAs are issued
                 uint32_t quarters;
                 const uint32_t first_quarter = ring.place(work.tile_n, quarters);
+#ifdef SDXLQ_DIAGNOSTICS
+                const long long diag_t_wait = clock64();
+#endif
                 for (uint32_t q = first_quarter; ok && q < first_quarter + quarters; ++q) {
                     // the quarter's previous user (if any) has been drained by every epilogue warp
                     ok = ptx::mbar_wait_bounded(ptx::smem_u32(&control->acc_empty[q]), ((ring.parity >> q) & 1u) ^ 1u,
                                                 abort_word, limit);
                     ring.parity ^= 1u << q;
                 }
+#ifdef SDXLQ_DIAGNOSTICS
+                const long long diag_t_issue = clock64();
+                diag_acc_empty_wait += diag_t_issue - diag_t_wait;
+#endif
                 if (!ok) {
                     raise_abort(control, params.error_word, DEV_TIMEOUT_MMA);
                     break;
@@ -707,30 +775,46 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                 } else {
                     ptx::umma_commit(full_bar);
                 }
+#ifdef SDXLQ_DIAGNOSTICS
+                diag_issue += clock64() - diag_t_issue;
+#endif
             }
+#ifdef SDXLQ_DIAGNOSTICS
+            DIAG_WRITE(4, diag_acc_empty_wait); DIAG_WRITE(5, diag_issue); DIAG_WRITE(6, clock64() - diag_begin);
+#endif
         }
     } else {
         // ------------------------------- stagers (warps 2 and 3) ---------------------------
         // Fill the epilogue's operand slot of each tile (tile record, row scales, column scales
         // and bias) while the tile's main loop runs, up to kSlots tiles ahead of the epilogue.
         uint32_t iteration = 0;
+        DIAG_DECL(diag_slot_wait); DIAG_DECL(diag_stage); DIAG_DECL(diag_total);
+#ifdef SDXLQ_DIAGNOSTICS
+        const long long diag_begin = clock64();
+#endif
         TileRef next = load_tile(params, first_tile);
         for (uint32_t t = first_tile; t < num_tiles; t += tile_stride, ++iteration) {
             const TileRef work = next;
             next = load_tile(params, t + tile_stride);
             const uint32_t slot = iteration % kSlots;
             uint32_t ok = 1;
+            DIAG_ADD(diag_slot_wait,
             if (lane == 0) {
                 ok = ptx::mbar_wait_bounded(ptx::smem_u32(&control->slot_free[slot]), ((iteration / kSlots) & 1u) ^ 1u,
                                             abort_word, limit) ? 1u : 0u;
                 if (ok == 0) raise_abort(control, params.error_word, DEV_TIMEOUT_EPILOGUE + 1);
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
+            ok = __shfl_sync(0xffffffffu, ok, 0));
             if (ok == 0) break;
+            DIAG_ADD(diag_stage,
             stage_tile(work, work.tile_m * kRowsPerTile + cta_rank * kTileM, lane, warp - 2u, control, slot);
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&control->staged[slot]));
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&control->staged[slot])));
         }
+#ifdef SDXLQ_DIAGNOSTICS
+        diag_total = clock64() - diag_begin;
+        if (warp == 2 && lane == 0) { DIAG_WRITE(0, diag_slot_wait); DIAG_WRITE(1, diag_stage); DIAG_WRITE(2, diag_total); DIAG_WRITE(3, iteration); }
+#endif
     }
     } else {
         // ------------------------------- epilogue ------------------------------------------
@@ -742,12 +826,23 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
         const uint32_t row_in_cta = quadrant * 32u + lane;
         AccumulatorRing ring;
         uint32_t iteration = 0;
+        DIAG_DECL(diag_staged_wait); DIAG_DECL(diag_acc_wait); DIAG_DECL(diag_work); DIAG_DECL(diag_setup); DIAG_DECL(diag_tail);
+#ifdef SDXLQ_DIAGNOSTICS
+        const long long diag_begin = clock64();
+#endif
         for (uint32_t t = first_tile; t < num_tiles; t += tile_stride, ++iteration) {
             const uint32_t buffer = iteration % kSlots;
+#ifdef SDXLQ_DIAGNOSTICS
+            const long long diag_t_staged = clock64();
+#endif
             if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->staged[buffer]), (iteration / kSlots) & 1u, abort_word, limit)) {
                 raise_abort(control, params.error_word, DEV_TIMEOUT_EPILOGUE);
                 break;
             }
+#ifdef SDXLQ_DIAGNOSTICS
+            const long long diag_t_setup = clock64();
+            diag_staged_wait += diag_t_setup - diag_t_staged;
+#endif
             const TileRef& work = control->header[buffer];
             const uint32_t tile_n = work.tile_n;
             const uint32_t activation = work.activation;
@@ -774,7 +869,15 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             tile.activation = activation;
             tile.flags = (tile.row < work.m ? 1u : 0u) | ((flags & TILE_HAS_BIAS) != 0 ? 2u : 0u) |
                          ((flags & TILE_STORE_16) != 0 ? 4u : 0u) | ((flags & TILE_STORE_32) != 0 ? 8u : 0u);
+#ifdef SDXLQ_DIAGNOSTICS
+            tile.flags |= ((params.diagnostic_skip >> 7) & 31u) << 4;    // 128 no stores, 256 no accumulator loads, 512 no arithmetic,
+                                                                         // 1024 empty epilogue function, 2048 one chunk per warp
+#endif
             tile.a_scale = control->row_scale[buffer][row_in_cta];
+#ifdef SDXLQ_DIAGNOSTICS
+            const long long diag_t_acc = clock64();
+            diag_setup += diag_t_acc - diag_t_setup;
+#endif
             if (!ptx::mbar_wait_bounded(ptx::smem_u32(&control->acc_full[first_quarter]), (ring.parity >> first_quarter) & 1u,
                                         abort_word, limit)) {
                 raise_abort(control, params.error_word, DEV_TIMEOUT_EPILOGUE);
@@ -782,6 +885,10 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             }
             ring.parity ^= 1u << first_quarter;
             ptx::tc_fence_after();
+#ifdef SDXLQ_DIAGNOSTICS
+            const long long diag_t_work = clock64();
+            diag_acc_wait += diag_t_work - diag_t_acc;
+#endif
             if (skip_epilogue) { /* diagnostic: accumulators are dropped */ }
             else if constexpr (kClass == 0) epilogue_dispatch<KIND_I8>(activation, tile);
             else if constexpr (kClass == 1) epilogue_dispatch<KIND_E4M3>(activation, tile);
@@ -789,6 +896,10 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             else if (kind == KIND_I8) epilogue_dispatch<KIND_I8>(activation, tile);
             else if (kind == KIND_F16) epilogue_dispatch<KIND_F16>(activation, tile);
             else epilogue_dispatch<KIND_E4M3>(activation, tile);
+#ifdef SDXLQ_DIAGNOSTICS
+            const long long diag_t_tail = clock64();
+            diag_work += diag_t_tail - diag_t_work;
+#endif
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -799,7 +910,16 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
                 }
                 ptx::mbar_arrive(ptx::smem_u32(&control->slot_free[buffer]));
             }
+#ifdef SDXLQ_DIAGNOSTICS
+            diag_tail += clock64() - diag_t_tail;
+#endif
         }
+#ifdef SDXLQ_DIAGNOSTICS
+        if (warp == kControlWarps && lane == 0) {
+            DIAG_WRITE(8, diag_staged_wait); DIAG_WRITE(9, diag_setup); DIAG_WRITE(10, diag_acc_wait); DIAG_WRITE(11, diag_work);
+            DIAG_WRITE(12, diag_tail); DIAG_WRITE(13, clock64() - diag_begin); DIAG_WRITE(14, iteration);
+        }
+#endif
     }
 
     ptx::tc_fence_before();
