@@ -236,6 +236,33 @@ typedef struct sdxlq_layer_norm_desc {
 } sdxlq_layer_norm_desc;
 int sdxlq_layer_norm(sdxlq_context* ctx, const sdxlq_layer_norm_desc* desc);
 
+/* ---- harness scaffolding (not part of the projection path) --------------------------------- */
+
+/* GroupNorm, optionally followed by SiLU, over channels-last FP16 activations x[batch, rows, channels]
+ * (NHWC memory: rows = height * width): what Ops::group_norm_nchw / group_norm_silu_nchw
+ * (include/sdxl/cuda/ops.hpp:43-52, src/cuda/ops_kernels.cu:258-308) compute, on the layout the
+ * synthetic UNet loop keeps its convolution activations in, so that no layout copy surrounds the
+ * norm. channel_bias (optional, [batch, channels] FP16) is added first with FP16 rounding: the
+ * resnet's add_spatial_bias in front of norm2. y may alias x. channels must be a multiple of
+ * 2 * groups and at most 2560, groups at most 64; SDXLQ_ERR_UNSUPPORTED_SHAPE otherwise. Exists so
+ * that the benchmark's UNet loop does not spend a quarter of its step on layout copies; it is not a
+ * drop-in for the reference's NCHW operator. */
+typedef struct sdxlq_group_norm_desc {
+    const void* x;
+    const void* channel_bias;
+    const void* gamma;           /* FP16 [channels] */
+    const void* beta;            /* FP16 [channels] */
+    void* y;
+    uint64_t batch;
+    uint64_t rows;
+    uint64_t channels;
+    uint32_t groups;
+    int32_t silu;
+    float epsilon;
+    uint32_t reserved;
+} sdxlq_group_norm_desc;
+int sdxlq_group_norm_nhwc(sdxlq_context* ctx, const sdxlq_group_norm_desc* desc);
+
 /* ---- load-time weight packers ------------------------------------------------------------- */
 
 /* upload_or_quantize_int8_weight (int8_convrot.cu:498-577) for a weight already on the device:
@@ -281,7 +308,8 @@ enum {
     SDXLQ_KERNEL_GEMM = 2,
     SDXLQ_KERNEL_SMALL = 3,
     SDXLQ_KERNEL_LAYER_NORM = 4,
-    SDXLQ_KERNEL_CLASSES = 5
+    SDXLQ_KERNEL_HARNESS = 5,         /* sdxlq_group_norm_nhwc */
+    SDXLQ_KERNEL_CLASSES = 6
 };
 typedef struct sdxlq_kernel_times {
     double milliseconds[SDXLQ_KERNEL_CLASSES];

@@ -112,11 +112,20 @@ class _CLayerNormDesc(ctypes.Structure):
     ]
 
 
+class _CGroupNormDesc(ctypes.Structure):
+    """sdxlq_group_norm_desc."""
+    _fields_ = [
+        ("x", ctypes.c_void_p), ("channel_bias", ctypes.c_void_p), ("gamma", ctypes.c_void_p), ("beta", ctypes.c_void_p),
+        ("y", ctypes.c_void_p), ("batch", ctypes.c_uint64), ("rows", ctypes.c_uint64), ("channels", ctypes.c_uint64),
+        ("groups", ctypes.c_uint32), ("silu", ctypes.c_int32), ("epsilon", ctypes.c_float), ("reserved", ctypes.c_uint32),
+    ]
+
+
 class _CKernelTimes(ctypes.Structure):
-    _fields_ = [("milliseconds", ctypes.c_double * 5), ("launches", ctypes.c_uint64 * 5)]
+    _fields_ = [("milliseconds", ctypes.c_double * 6), ("launches", ctypes.c_uint64 * 6)]
 
 
-KERNEL_CLASSES = ("quant_int8", "quant_fp8", "gemm", "small", "layer_norm")
+KERNEL_CLASSES = ("quant_int8", "quant_fp8", "gemm", "small", "layer_norm", "harness")
 
 EXPORTED_SYMBOLS = [
     "sdxlq_context_create", "sdxlq_context_destroy", "sdxlq_context_set_stream", "sdxlq_context_check",
@@ -126,7 +135,7 @@ EXPORTED_SYMBOLS = [
     "sdxlq_pack_weight_int8", "sdxlq_pack_weight_fp8", "sdxlq_valid_convrot_group_size",
     "sdxlq_workspace_bytes", "sdxlq_build_info", "sdxlq_context_set_tile_n",
     "sdxlq_selftest_bounded_wait", "sdxlq_profile_enable", "sdxlq_profile_read", "sdxlq_linear_static",
-    "sdxlq_context_set_pair_mode", "sdxlq_layer_norm",
+    "sdxlq_context_set_pair_mode", "sdxlq_layer_norm", "sdxlq_group_norm_nhwc",
 ]
 
 _lib: Optional[ctypes.CDLL] = None
@@ -179,6 +188,7 @@ def load_library() -> ctypes.CDLL:
     lib.sdxlq_profile_read.argtypes = [vp, ctypes.POINTER(_CKernelTimes)]
     lib.sdxlq_linear_static.argtypes = [ctypes.c_int, vp, ctypes.POINTER(_CLinearDesc), ctypes.c_char_p, sz]
     lib.sdxlq_layer_norm.argtypes = [vp, ctypes.POINTER(_CLayerNormDesc)]
+    lib.sdxlq_group_norm_nhwc.argtypes = [vp, ctypes.POINTER(_CGroupNormDesc)]
     _lib = lib
     return lib
 
@@ -488,6 +498,31 @@ class Ops:
                                int(consumer.type), group, 0, None, xq.data_ptr(), scales.data_ptr())
         self.ctx.raise_for(self._lib.sdxlq_layer_norm(self.ctx.handle, ctypes.byref(desc)))
         return xq, scales
+
+    # -- harness scaffolding: GroupNorm (+ SiLU) on channels-last activations -------------------------------
+    def group_norm_nhwc(self, input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, groups: int,
+                        epsilon: float = 1.0e-5, silu: bool = False,
+                        channel_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Ops::group_norm_nchw / group_norm_silu_nchw (include/sdxl/cuda/ops.hpp:43-52) for a logical
+        [B, C, H, W] FP16 tensor held channels-last (NHWC memory); the result has the same shape and
+        memory format. `channel_bias` [B, C] is added first with FP16 rounding (add_spatial_bias)."""
+        if input.dtype != torch.float16 or input.dim() != 4 or weight.dtype != torch.float16 or bias.dtype != torch.float16:
+            raise CudaError("CUDA group_norm expects an FP16 NCHW tensor")
+        batch, channels, height, width = (int(v) for v in input.shape)
+        if weight.dim() != 1 or bias.dim() != 1 or weight.shape[0] != channels or bias.shape[0] != channels:
+            raise CudaError("CUDA group_norm weight / bias mismatch")
+        if groups <= 0 or channels % groups != 0:
+            raise CudaError("CUDA group_norm channels must be divisible by groups")
+        if not input.is_contiguous(memory_format=torch.channels_last):
+            raise CudaError("group_norm_nhwc expects a channels-last tensor")
+        if channel_bias is not None and (channel_bias.dtype != torch.float16 or tuple(channel_bias.shape) != (batch, channels)
+                                         or not channel_bias.is_contiguous()):
+            raise CudaError("CUDA spatial bias must have shape [batch, channels]")
+        out = torch.empty_like(input, memory_format=torch.channels_last)
+        desc = _CGroupNormDesc(input.data_ptr(), _ptr(channel_bias), weight.data_ptr(), bias.data_ptr(), out.data_ptr(),
+                               batch, height * width, channels, groups, int(silu), epsilon, 0)
+        self.ctx.raise_for(self._lib.sdxlq_group_norm_nhwc(self.ctx.handle, ctypes.byref(desc)))
+        return out
 
     # -- Ops::quantize_fp8 / quantize_e4m3 / quantize_e5m2 ------------------------------------------
     def quantize_fp8(self, input: torch.Tensor, fp8_type: ScalarType) -> Weight:

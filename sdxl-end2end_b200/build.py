@@ -8,8 +8,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBRARY = os.path.join(HERE, "libsdxlq.so")
-SOURCES = ["capi.cu", "gemm_umma.cu", "quantize.cu", "quantize_int8_fast.cu", "linear_small.cu", "layer_norm.cu"]
-HEADERS = ["internal.cuh", "ptx.cuh", "quantize.cuh", "fp8_math.cuh", os.path.join("..", "..", "include", "sdxlq.h")]
+SOURCES = ["capi.cu", "gemm_umma.cu", "quantize.cu", "quantize_int8_fast.cu", "linear_small.cu", "layer_norm.cu", "harness_norm.cu"]
+HEADERS = ["internal.cuh", "ptx.cuh", "quantize.cuh", "fp8_math.cuh", "int8_math.cuh", os.path.join("..", "..", "include", "sdxlq.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -44,6 +44,7 @@ namespace {
 
 constexpr size_t kDefaultWorkspace = size_t(256) << 20;
 constexpr uint32_t kMaxFp8Jobs = 4096;
+constexpr size_t kNormPartialFloats = 256u * 1024u;     // scratch of sdxlq_group_norm_nhwc (1 MiB)
 constexpr size_t kSmemLimit = 232448;      // 227 KiB opt-in shared memory per CTA on sm_100
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -60,6 +61,7 @@ struct sdxlq_context {
     cudaStream_t stream = nullptr;
     uint8_t* workspace = nullptr;
     size_t workspace_bytes = 0;
+    float* norm_partials = nullptr;           // kNormPartialFloats floats: partial sums of sdxlq_group_norm_nhwc
     uint32_t* control = nullptr;           // [0] error word; from word 64: kMaxFp8Jobs amax words, then kMaxFp8Jobs
                                            // reader counters of the FP8 quantiser (all zero between calls)
     int sm_count = 148;
@@ -842,7 +844,9 @@ int sdxlq_context_create(int device, void* stream, size_t workspace_bytes, sdxlq
         delete ctx;
         return SDXLQ_ERR_CUDA;
     }
-    if (cudaEventCreateWithFlags(&ctx->staging_event, cudaEventDisableTiming) != cudaSuccess) {
+    if (cudaEventCreateWithFlags(&ctx->staging_event, cudaEventDisableTiming) != cudaSuccess ||
+        cudaMalloc(&ctx->norm_partials, kNormPartialFloats * sizeof(float)) != cudaSuccess) {
+        if (ctx->staging_event != nullptr) cudaEventDestroy(ctx->staging_event);
         cudaFree(ctx->workspace);
         cudaFree(ctx->control);
         delete ctx;
@@ -877,6 +881,7 @@ void sdxlq_context_destroy(sdxlq_context* ctx) {
     cudaFreeHost(ctx->staging);
     cudaFree(ctx->workspace);
     cudaFree(ctx->control);
+    cudaFree(ctx->norm_partials);
     delete ctx;
 }
 
@@ -1187,6 +1192,50 @@ int sdxlq_layer_norm(sdxlq_context* ctx, const sdxlq_layer_norm_desc* desc) {
     const cudaError_t error = fp8 ? launch_layer_norm_fp8(launch, ctx->stream, ctx->early_launch && !ctx->profiling)
                                   : launch_layer_norm_f16(launch, ctx->stream);
     if (error != cudaSuccess) return fail_cuda(ctx, error, "layer_norm launch");
+    return SDXLQ_OK;
+}
+
+int sdxlq_group_norm_nhwc(sdxlq_context* ctx, const sdxlq_group_norm_desc* desc) {
+    if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    if (desc == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "group_norm: null descriptor");
+    const sdxlq_group_norm_desc& d = *desc;
+    if (d.batch == 0 || d.rows == 0) return SDXLQ_OK;
+    if (d.x == nullptr || d.y == nullptr || d.gamma == nullptr || d.beta == nullptr) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "group_norm: null input, output, weight or bias");
+    }
+    if (d.groups == 0 || d.channels == 0 || d.channels % d.groups != 0) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "CUDA group_norm channels must be divisible by groups");
+    }
+    if (d.groups > 64 || d.channels % (2 * d.groups) != 0 || d.channels > group_norm_max_channels() ||
+        d.batch > 65535 || d.rows > 0x7FFFFFFFull) {
+        return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE,
+                    "group_norm: an even number of channels per group, at most 64 groups and 2560 channels");
+    }
+    if (ctx->norm_partials == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "group_norm needs a context made by sdxlq_context_create");
+    // enough blocks to fill the GPU a few times over; the partial sums of a launch must fit the scratch
+    const uint64_t capacity = kNormPartialFloats / (2ull * d.groups);            // (batch x chunks) pairs of sums
+    uint64_t chunks = std::max<uint64_t>(1, static_cast<uint64_t>(ctx->sm_count) * 4 / d.batch);
+    chunks = std::min<uint64_t>(chunks, std::max<uint64_t>(1, d.rows / 8));
+    chunks = std::min<uint64_t>(chunks, std::max<uint64_t>(1, capacity / d.batch));
+    if (d.batch > capacity) return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE, "group_norm: batch too large for the scratch");
+    GroupNormLaunch launch{};
+    launch.x = static_cast<const __half*>(d.x);
+    launch.channel_bias = static_cast<const __half*>(d.channel_bias);
+    launch.gamma = static_cast<const __half*>(d.gamma);
+    launch.beta = static_cast<const __half*>(d.beta);
+    launch.y = static_cast<__half*>(d.y);
+    launch.partials = ctx->norm_partials;
+    launch.batch = static_cast<uint32_t>(d.batch);
+    launch.rows = static_cast<uint32_t>(d.rows);
+    launch.channels = static_cast<uint32_t>(d.channels);
+    launch.groups = d.groups;
+    launch.rows_per_chunk = static_cast<uint32_t>((d.rows + chunks - 1) / chunks);
+    chunks = (d.rows + launch.rows_per_chunk - 1) / launch.rows_per_chunk;
+    launch.silu = d.silu != 0 ? 1u : 0u;
+    launch.epsilon = d.epsilon;
+    LaunchTimer timer(ctx, SDXLQ_KERNEL_HARNESS, 2);
+    const cudaError_t error = launch_group_norm_nhwc(launch, static_cast<uint32_t>(chunks), ctx->stream);
+    if (error != cudaSuccess) return fail_cuda(ctx, error, "group_norm launch");
     return SDXLQ_OK;
 }
 

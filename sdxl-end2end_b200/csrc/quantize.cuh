@@ -88,4 +88,21 @@ cudaError_t launch_layer_norm_f16(const LayerNormLaunch& launch, cudaStream_t st
 cudaError_t launch_layer_norm_int8(const LayerNormLaunch& launch, cudaStream_t stream);
 cudaError_t launch_layer_norm_fp8(const LayerNormLaunch& launch, cudaStream_t stream, bool early_launch);
 
+// GroupNorm (+ SiLU) over channels-last FP16 activations [batch, rows, channels]: scaffolding of the UNet
+// harness (see harness_norm.cu).
+struct GroupNormLaunch {
+    const __half* x;             // [batch, rows, channels]
+    const __half* channel_bias;  // optional [batch, channels], added (and rounded to FP16) before the norm
+    const __half* gamma;         // [channels]
+    const __half* beta;          // [channels]
+    __half* y;                   // [batch, rows, channels], may alias x
+    float* partials;             // [batch, chunks, groups, 2] scratch
+    uint32_t batch, rows, channels, groups;
+    uint32_t rows_per_chunk;
+    uint32_t silu;
+    float epsilon;
+};
+uint32_t group_norm_max_channels();
+cudaError_t launch_group_norm_nhwc(const GroupNormLaunch& launch, uint32_t chunks, cudaStream_t stream);
+
 }  // namespace sdxlq

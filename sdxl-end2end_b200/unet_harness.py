@@ -237,12 +237,15 @@ class UNetHarness:
     `fuse_layer_norm` runs the three LayerNorms of a transformer block through the library's
     kernel, fused with the activation quantiser of the projections that read them (to_q / to_k /
     to_v, attn2.to_q, ff.net.0.proj) for the quantised profiles; without it they are separate
-    PyTorch layer_norm calls and the projections quantise their input themselves."""
+    PyTorch layer_norm calls and the projections quantise their input themselves.
+    `fuse_group_norm` runs GroupNorm (+ SiLU, + the resnet's time-embedding bias in front of norm2) on the
+    channels-last activations through the library's scaffolding kernel instead of PyTorch's group_norm,
+    which copies a channels-last tensor to NCHW and back around the norm."""
 
     def __init__(self, ops: Ops, config: UNetConfig = BASE_1_0, precision: str = "e4m3", seed: int = 0,
                  parameters: Optional[Dict[str, torch.Tensor]] = None, fuse_residual: bool = True,
                  group_attention_inputs: bool = True, device: Optional[torch.device] = None,
-                 fuse_layer_norm: bool = True):
+                 fuse_layer_norm: bool = True, fuse_group_norm: bool = True):
         if precision not in ("e4m3", "e5m2", "int8", "f16"):
             raise CudaError(f"unknown precision profile {precision}")
         self.ops = ops
@@ -251,6 +254,7 @@ class UNetHarness:
         self.fuse_residual = fuse_residual
         self.group_attention_inputs = group_attention_inputs
         self.fuse_layer_norm = fuse_layer_norm
+        self.fuse_group_norm = fuse_group_norm
         self.device = device if device is not None else torch.device("cuda", ops.ctx.device)
         source = parameters if parameters is not None else synthetic_parameters(config, self.device, seed)
         self.projections: Dict[str, Weight] = {}
@@ -309,8 +313,14 @@ class UNetHarness:
             return residual
         return self.ops.linear(x, self.projections[prefix], b, residual=residual, out=out, **quantised)
 
-    def _group_norm(self, x, prefix, eps=1e-5, silu=False):
-        y = F.group_norm(x, self.config.norm_groups, self.tensors[f"{prefix}.weight"], self.tensors[f"{prefix}.bias"], eps)
+    def _group_norm(self, x, prefix, eps=1e-5, silu=False, channel_bias=None):
+        """Ops::group_norm_nchw / group_norm_silu_nchw; `channel_bias` [B, C] is the add_spatial_bias in front."""
+        gamma, beta = self.tensors[f"{prefix}.weight"], self.tensors[f"{prefix}.bias"]
+        if self.fuse_group_norm and x.dim() == 4 and x.is_contiguous(memory_format=torch.channels_last):
+            return self.ops.group_norm_nhwc(x, gamma, beta, self.config.norm_groups, eps, silu, channel_bias)
+        if channel_bias is not None:
+            x = x + channel_bias[:, :, None, None]
+        y = F.group_norm(x, self.config.norm_groups, gamma, beta, eps)
         return F.silu(y) if silu else y
 
     def _conv(self, x, prefix, stride=1, padding=1):
@@ -386,8 +396,8 @@ class UNetHarness:
     def _resnet(self, prefix, x, projected_temb):
         hidden = self._group_norm(x, f"{prefix}.norm1", silu=True)
         hidden = self._conv(hidden, f"{prefix}.conv1")
-        hidden = hidden + projected_temb[f"{prefix}.time_emb_proj"][:, :, None, None]      # add_spatial_bias
-        hidden = self._group_norm(hidden, f"{prefix}.norm2", silu=True)
+        # add_spatial_bias, then group_norm_silu
+        hidden = self._group_norm(hidden, f"{prefix}.norm2", silu=True, channel_bias=projected_temb[f"{prefix}.time_emb_proj"])
         hidden = self._conv(hidden, f"{prefix}.conv2")
         residual = x
         if f"{prefix}.conv_shortcut.weight" in self.tensors:

@@ -70,6 +70,15 @@ class FakeOps:
         self.log.append(("layer_norm", x.numel() // x.shape[-1], x.shape[-1], 0, True, 0, False))
         return F.layer_norm(x.float(), (x.shape[-1],), gamma.float(), beta.float(), epsilon).to(torch.float16)
 
+    def group_norm_nhwc(self, x, gamma, beta, groups, epsilon=1.0e-5, silu=False, channel_bias=None):
+        self.log.append(("group_norm", x.shape[0], x.shape[1], 0, True, int(silu), channel_bias is not None))
+        if channel_bias is not None:
+            x = (x.float() + channel_bias.float()[:, :, None, None]).to(torch.float16)
+        y = F.group_norm(x.float(), groups, gamma.float(), beta.float(), epsilon)
+        if silu:
+            y = F.silu(y)
+        return y.to(torch.float16).contiguous(memory_format=torch.channels_last)
+
     def linear(self, x, weight, bias=None, *, residual=None, out=None, **_):
         self.log.append(("linear", x.numel() // weight.k, weight.n, weight.k, bias is not None, 0, residual is not None))
         y = self._compute(x, weight, bias, 0, residual)

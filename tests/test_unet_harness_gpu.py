@@ -150,3 +150,48 @@ def test_sharding_by_image_keeps_each_image(gpu):
     alone = torch.cat([denoise([0], [2]), denoise([1], [3])])
     scale = float(together.abs().max())
     assert float((together - alone).abs().max()) <= 2e-2 * scale
+
+
+@pytest.mark.parametrize("batch,channels,size", [(2, 320, 32), (2, 640, 16), (1, 1280, 8), (2, 960, 16), (2, 1920, 8), (1, 2560, 8), (3, 64, 5)])
+@pytest.mark.parametrize("silu,with_bias", [(False, False), (True, False), (True, True)])
+def test_group_norm_nhwc_matches_the_fp32_formula(gpu, batch, channels, size, silu, with_bias):
+    """The harness's channels-last GroupNorm (+ SiLU, + time-embedding bias) against the FP32 formula of the
+    reference's group_norm_kernel (src/cuda/ops_kernels.cu:258-308) evaluated with PyTorch on the NCHW view:
+    every output within 2 FP16 steps of the larger of |y| and |beta| (the statistics are FP32 sums in
+    another order, the variance one-pass), and two runs bit-identical (no atomics)."""
+    pkg, ctx, ops = gpu
+    generator = torch.Generator(device="cuda").manual_seed(17 + channels + size)
+    x = (torch.randn((batch, channels, size, size), generator=generator, device="cuda") * 1.5 + 0.3).half()
+    x = x.contiguous(memory_format=torch.channels_last)
+    gamma = (1.0 + 0.2 * torch.randn(channels, generator=generator, device="cuda")).half()
+    beta = (0.1 * torch.randn(channels, generator=generator, device="cuda")).half()
+    bias = (0.5 * torch.randn((batch, channels), generator=generator, device="cuda")).half() if with_bias else None
+    got = ops.group_norm_nhwc(x, gamma, beta, 32, 1e-5, silu, bias)
+    again = ops.group_norm_nhwc(x, gamma, beta, 32, 1e-5, silu, bias)
+    ctx.check()
+    assert got.is_contiguous(memory_format=torch.channels_last) and torch.equal(got, again)
+    source = x.float()
+    if with_bias:
+        source = (source + bias.float()[:, :, None, None]).half().float()
+    want = torch.nn.functional.group_norm(source.double(), 32, gamma.double(), beta.double(), 1e-5)
+    if silu:
+        want = want * torch.sigmoid(want)
+    bound = 2.0 ** -9 * torch.maximum(want.abs(), beta.double().abs()[None, :, None, None]) + 1e-6
+    assert bool(((got.double() - want).abs() <= bound).all()), float(((got.double() - want).abs() / bound).max())
+
+
+@pytest.mark.parametrize("precision", ["f16", "e4m3"])
+def test_group_norm_kernel_in_the_harness_stays_within_rounding(gpu, precision):
+    """The whole forward with the scaffolding GroupNorm kernel against PyTorch's group_norm. FP16: rounding
+    level. FP8 E4M3 with random weights: a last-bit difference of a norm output can move a tensor-wide
+    maximum, hence the scale and every byte of that tensor by one step; through 70 transformer blocks the
+    two runs then differ by the profile's own quantisation noise (the same size as its distance from the
+    reference's FP32 UNet, see test_forward_matches_the_reference_cpu_unet)."""
+    pkg, ctx, ops = gpu
+    params = parameters(15)
+    data = inputs(2, seed=16)
+    ours, _ = run_forward(ops, precision, params, data)
+    torch_norm, _ = run_forward(ops, precision, params, data, fuse_group_norm=False)
+    rms = float(np.sqrt(np.mean((ours - torch_norm) ** 2)) / np.sqrt(np.mean(torch_norm ** 2)))
+    print(f"{precision}: library GroupNorm vs torch group_norm rms rel = {rms:.3e}")
+    assert rms <= (5e-3 if precision == "f16" else 1.5e-1)

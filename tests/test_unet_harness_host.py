@@ -95,8 +95,8 @@ def test_forward_wiring_matches_the_reference_cpu_unet():
     assert float(np.max(np.abs(got - want))) <= 2e-2 * scale
     # the call inventory: every projection of the configuration exactly once per forward
     count = sum(1 for name, shape in harness.unet_parameter_shapes(MINIATURE).items() if harness.is_projection_weight(name, shape))
-    assert unet.projection_calls == count == len([entry for entry in ops.log if entry[0] != "layer_norm"])
-    fused = [entry for entry in ops.log if entry[6]]
+    assert unet.projection_calls == count == len([entry for entry in ops.log if entry[0] not in ("layer_norm", "group_norm")])
+    fused = [entry for entry in ops.log if entry[6] and entry[0] != "group_norm"]
     blocks = sum(1 for name in unet.projections if name.endswith(".attn1.to_out.0"))
     attention_blocks = sum(1 for name in unet.projections if name.endswith(".proj_out"))
     assert len(fused) == 3 * blocks + attention_blocks          # to_out x2, ff.net.2, proj_out
