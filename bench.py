@@ -6,7 +6,7 @@
 Default workload `unetloop_e4m3`: the synthetic SDXL Base UNet denoising loop at 1024^2 for a fixed
 job of 8 images x CFG 2 (UNet batch 16), FP8 E4M3 projections (per-output-channel weight scales,
 native FP8 activations), the transformer LayerNorms fused with the quantisers of the projections
-they feed, FP16 convolutions / GroupNorm / attention from PyTorch around them, Euler
+they feed, FP16 convolutions / attention from PyTorch and a channels-last GroupNorm kernel around them, Euler
 sampler, sigma schedule of 20 steps. A "step" is one denoising step of the whole job: scale the
 latents, one UNet forward over [uncond | cond], CFG combine, Euler update; every 20 steps a new
 generation starts and the cross-attention K/V projections are recomputed once. With N ranks the
@@ -603,8 +603,8 @@ def unetloop_description(kind: str) -> str:
     batch = 2 * JOB_IMAGES
     return (f"synthetic SDXL Base UNet denoising loop, 1024^2, {JOB_IMAGES} images x CFG 2 (latents [{batch},4,128,128], "
             f"context [{batch},77,2048], pooled [{batch},1280]), {GENERATION_STEPS} Euler steps per generation, random-init weights; projections {names[kind]}; "
-            "transformer LayerNorms fused with the activation quantisers (library kernel); FP16 convolutions / GroupNorm / "
-            "attention (PyTorch)")
+            "transformer LayerNorms fused with the activation quantisers (library kernel); FP16 convolutions / attention "
+            "(PyTorch, channels-last), GroupNorm + SiLU on the channels-last activations (harness kernel of the library)")
 
 
 def run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks):

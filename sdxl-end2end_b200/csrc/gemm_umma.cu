@@ -197,11 +197,10 @@ __device__ __forceinline__ __half packed_half(const uint32_t word, int index) {
 // 16 FP16 results of one output row, packed two per word -> global memory. `wide` (row pitch and
 // base 32-byte aligned) writes the 32 bytes with one 256-bit store so that each lane fills a
 // whole memory sector; `vector_ok` (16-byte aligned) uses two 128-bit stores.
-template <bool Fast = false>
 __device__ __forceinline__ void store_row_16(__half* y, uint32_t n_out, bool vector_ok, bool wide, uint32_t row,
                                              uint32_t col0, const uint32_t (&words)[8]) {
     __half* destination = y + static_cast<size_t>(row) * n_out + col0;
-    if (Fast || (col0 + 16 <= n_out && wide)) {
+    if (col0 + 16 <= n_out && wide) {
         asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(destination), "r"(words[0]),
                      "r"(words[1]), "r"(words[2]), "r"(words[3]), "r"(words[4]), "r"(words[5]), "r"(words[6]),
                      "r"(words[7])
@@ -219,11 +218,10 @@ __device__ __forceinline__ void store_row_16(__half* y, uint32_t n_out, bool vec
 
 // The 16 residual values that belong to one row's 16 outputs (packed two per word), loaded the way
 // store_row_16 writes them: one 256-bit load, two 128-bit loads, or element by element at the edge.
-template <bool Fast = false>
 __device__ __forceinline__ void load_row_16(const __half* source, uint32_t n_out, bool vector_ok, bool wide,
                                             uint32_t row, uint32_t col0, uint32_t (&words)[8]) {
     const __half* address = source + static_cast<size_t>(row) * n_out + col0;
-    if (Fast || (col0 + 16 <= n_out && wide)) {
+    if (col0 + 16 <= n_out && wide) {
         asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                      : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3]), "=r"(words[4]), "=r"(words[5]),
                        "=r"(words[6]), "=r"(words[7])
@@ -372,11 +370,6 @@ __device__ __forceinline__ void finish_geglu_8(const EpilogueTile& t, uint32_t c
 // lane quadrant take the chunks round-robin): tensor-memory load, wait, finish (dequantise, bias,
 // activation), store, one chunk at a time, one output row per lane.
 //
-// Fast = true (the tile lies inside the matrix in N, the output rows take 32-byte stores, no raw
-// accumulators are wanted: every tile of the SDXL projections except a few edge tiles): the edge
-// handling, the narrow stores and the accumulator dump are compiled out, which keeps the instruction
-// stream of the hot loop short and straight (2 to 6 % on the K = 640 GEGLU tiles).
-//
 // Measured on B200 with parts of this function switched off (tuning build, 128 x 256 INT8 tiles, K = 640,
 // main loop running): about 6000 cycles per tile, of which the stores account for 1900, the arithmetic
 // for 1000 and the tensor-memory loads for nothing. Measured slower or no faster, same GPU, same run:
@@ -390,34 +383,37 @@ __device__ __forceinline__ void finish_geglu_8(const EpilogueTile& t, uint32_t c
 //    the same time within 2 %, 20 % slower on 128-column tiles) -- the cost of the stores is not the
 //    load/store unit's transaction count;
 //  * 12 or 16 epilogue warps (the time per tile does not change: the epilogue is not latency-bound
-//    per warp).
+//    per warp);
+//  * a second instance of the two hot variants for interior tiles, with the edge handling, the narrow
+//    stores and the accumulator dump compiled out: 2 to 6 % faster on single K = 640 GEGLU projections,
+//    9 % SLOWER on the UNet loop's projections as a whole (same GPU, same run), so it was taken out;
+//  * kernels compiled for one activation as well as one operand class: no change.
 // Kind: 0 INT8, 1 FP8 (either format), 3 FP16.
 // Arithmetic per output, as the reference runs it after the GEMM:
 //   y = half_rn(dequantised accumulator)
 //   no activation : __hadd(y, bias), then __hadd(.., residual)  (add_last_dim_bias_kernel, add_in_place_kernel)
 //   SiLU/GELU/QuickGELU : half_rn(act(float(y) + float(bias))) (bias_activation_in_place_kernel)
 //   GEGLU : half_rn((float(y_v) + float(b_v)) * gelu(float(y_g) + float(b_g)))   (bias_geglu_kernel)
-template <uint32_t Kind, uint32_t Act, bool Fast>
+template <uint32_t Kind, uint32_t Act>
 __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
     const bool row_ok = (t.flags & 1u) != 0;
     const bool has_bias = (t.flags & 2u) != 0;
-    const bool store_vector = Fast || (t.flags & 4u) != 0;
-    const bool store_wide = Fast || (t.flags & 8u) != 0;
+    const bool store_vector = (t.flags & 4u) != 0;
+    const bool store_wide = (t.flags & 8u) != 0;
     const float2 a_scale = make_float2(t.a_scale, t.a_scale);
-    int32_t* const acc_out = (Kind == KIND_I8 && !Fast) ? t.acc_out : nullptr;
+    int32_t* const acc_out = Kind == KIND_I8 ? t.acc_out : nullptr;
     constexpr uint32_t kStride = kWarpsPerQuadrant * 16u;
 #ifdef SDXLQ_DIAGNOSTICS
-    // tuning build: parts of the epilogue can be switched off to time the others (general variant only)
-    const bool no_store = !Fast && (t.flags & 16u) != 0, no_load = !Fast && (t.flags & 32u) != 0,
-               no_math = !Fast && (t.flags & 64u) != 0;
-    if (!Fast && (t.flags & 128u) != 0) return;             // nothing at all
-    const uint32_t diag_limit = (!Fast && (t.flags & 256u) != 0) ? 32u : 0xFFFFFFFFu;     // one chunk per warp only
+    // tuning build: parts of the epilogue can be switched off to time the others
+    const bool no_store = (t.flags & 16u) != 0, no_load = (t.flags & 32u) != 0, no_math = (t.flags & 64u) != 0;
+    if ((t.flags & 128u) != 0) return;                      // nothing at all
+    const uint32_t diag_limit = (t.flags & 256u) != 0 ? 32u : 0xFFFFFFFFu;     // one chunk per warp only
 #else
     constexpr bool no_store = false, no_load = false, no_math = false;
     constexpr uint32_t diag_limit = 0xFFFFFFFFu;
 #endif
     const uint32_t columns = Act == ACT_GEGLU ? t.tile_n / 2u : t.tile_n;        // output columns of the tile
-    const uint32_t limit = Fast ? columns : min(diag_limit, min(columns, t.n_out > t.n0 ? t.n_out - t.n0 : 0u));
+    const uint32_t limit = min(diag_limit, min(columns, t.n_out > t.n0 ? t.n_out - t.n0 : 0u));
     const __half* const residual = Act == ACT_NONE ? t.residual : nullptr;
     const bool with_residual = residual != nullptr && row_ok;
 
@@ -433,7 +429,7 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
             } else {
                 ptx::tmem_ld_32x32b_x16(t.tmem_row + c, acc);
             }
-            if (with_residual) load_row_16<Fast>(residual, t.n_out, store_vector, store_wide, t.row, col0, extra);
+            if (with_residual) load_row_16(residual, t.n_out, store_vector, store_wide, t.row, col0, extra);
             if (!no_load) ptx::tmem_ld_wait(acc);
             if (acc_out != nullptr && row_ok) {
                 int32_t* raw = acc_out + static_cast<size_t>(t.row) * t.n + col0;
@@ -478,25 +474,16 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
             }
         }
         if (row_ok && (!no_store || (out_words[0] == 0x7E57C0DEu && out_words[7] == 0x7E57C0DEu))) {
-            store_row_16<Fast>(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
+            store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
         }
     }
 }
 
 template <uint32_t Kind>
 __device__ __forceinline__ void epilogue_dispatch(uint32_t activation, const EpilogueTile& t) {
-    const uint32_t columns = activation == ACT_GEGLU ? t.tile_n / 2u : t.tile_n;     // output columns of the tile
-    // bit 3: 32-byte stores; bits 4 and up: tuning switches of the diagnostics build
-    const bool fast = (t.flags & 8u) != 0 && (t.flags >> 4) == 0 && t.acc_out == nullptr && t.n0 + columns <= t.n_out;
-    if (activation == ACT_NONE) {
-        if (fast) epilogue_tile<Kind, ACT_NONE, true>(t);
-        else epilogue_tile<Kind, ACT_NONE, false>(t);
-    } else if (activation == ACT_GEGLU) {
-        if (fast) epilogue_tile<Kind, ACT_GEGLU, true>(t);
-        else epilogue_tile<Kind, ACT_GEGLU, false>(t);
-    } else {
-        epilogue_tile<Kind, kActRuntime, false>(t);
-    }
+    if (activation == ACT_NONE) epilogue_tile<Kind, ACT_NONE>(t);
+    else if (activation == ACT_GEGLU) epilogue_tile<Kind, ACT_GEGLU>(t);
+    else epilogue_tile<Kind, kActRuntime>(t);
 }
 
 }  // namespace
