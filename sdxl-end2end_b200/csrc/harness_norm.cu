@@ -32,46 +32,87 @@ __device__ __forceinline__ float2 load_pair(const __half* row, uint32_t pair, co
     return __half22float2(__floats2half2_rn(v.x + b.x, v.y + b.y));
 }
 
+// Thread mapping shared by both kernels. With P = channels / 2 channel pairs per row:
+//   P <= 320 threads: the block works on R = 320 / P rows at once, thread t on pair t % P of row slot t / P
+//   P >  320        : one row at a time, thread t on pairs t, t + 320, ... (at most four)
+// and every thread keeps about eight loads in flight (rows x pairs), so that enough loads are outstanding to cover the
+// memory latency with four-byte accesses (a warp still reads 128 contiguous bytes per instruction).
+
+struct NormMapping {
+    uint32_t pairs, rows_at_once, slot, first_pair;
+    bool active;
+};
+
+__device__ __forceinline__ NormMapping norm_mapping(uint32_t channels) {
+    NormMapping m;
+    m.pairs = channels / 2;
+    if (m.pairs <= kNormThreads) {
+        m.rows_at_once = kNormThreads / m.pairs;
+        m.slot = threadIdx.x / m.pairs;
+        m.first_pair = threadIdx.x - m.slot * m.pairs;
+        m.active = m.slot < m.rows_at_once;
+    } else {
+        m.rows_at_once = 1;
+        m.slot = 0;
+        m.first_pair = threadIdx.x;
+        m.active = true;
+    }
+    return m;
+}
+
+template <uint32_t kPairsPerThread>
 __global__ void __launch_bounds__(kNormThreads)
 group_norm_stats_kernel(const GroupNormLaunch p) {
-    __shared__ float pair_sums[kNormThreads * kMaxPairsPerThread][2];
+    constexpr uint32_t kUnroll = kPairsPerThread == 1 ? 8 : (kPairsPerThread == 2 ? 4 : 2);
+    __shared__ float pair_sums[kNormThreads * kPairsPerThread][2];     // [row slot][pair]
     const uint32_t batch = blockIdx.y;
     const uint32_t chunk = blockIdx.x;
-    const uint32_t pairs = p.channels / 2;
+    const NormMapping m = norm_mapping(p.channels);
     const uint32_t first_row = chunk * p.rows_per_chunk;
     const uint32_t last_row = min(p.rows, first_row + p.rows_per_chunk);
     const __half* base = p.x + static_cast<size_t>(batch) * p.rows * p.channels;
     const __half* bias_row = p.channel_bias != nullptr ? p.channel_bias + static_cast<size_t>(batch) * p.channels : nullptr;
 
-    float sum[kMaxPairsPerThread] = {}, squares[kMaxPairsPerThread] = {};
-    for (uint32_t row = first_row; row < last_row; ++row) {
-        const __half* source = base + static_cast<size_t>(row) * p.channels;
+    float sum[kPairsPerThread] = {}, squares[kPairsPerThread] = {};
+    if (m.active) {
+        const uint32_t step = m.rows_at_once * kUnroll;
+        for (uint32_t row0 = first_row + m.slot; row0 < last_row; row0 += step) {
 #pragma unroll
-        for (uint32_t i = 0; i < kMaxPairsPerThread; ++i) {
-            const uint32_t pair = threadIdx.x + i * kNormThreads;
-            if (pair < pairs) {
-                const float2 v = load_pair(source, pair, bias_row);
-                sum[i] += v.x + v.y;
-                squares[i] = fmaf(v.x, v.x, fmaf(v.y, v.y, squares[i]));
+            for (uint32_t u = 0; u < kUnroll; ++u) {
+                const uint32_t row = row0 + u * m.rows_at_once;
+                if (row >= last_row) break;
+                const __half* source = base + static_cast<size_t>(row) * p.channels;
+#pragma unroll
+                for (uint32_t i = 0; i < kPairsPerThread; ++i) {
+                    const uint32_t pair = m.first_pair + i * kNormThreads;
+                    if (pair < m.pairs) {
+                        const float2 v = load_pair(source, pair, bias_row);
+                        sum[i] += v.x + v.y;
+                        squares[i] = fmaf(v.x, v.x, fmaf(v.y, v.y, squares[i]));
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < kPairsPerThread; ++i) {
+            const uint32_t pair = m.first_pair + i * kNormThreads;
+            if (pair < m.pairs) {
+                pair_sums[m.slot * m.pairs + pair][0] = sum[i];
+                pair_sums[m.slot * m.pairs + pair][1] = squares[i];
             }
         }
     }
-#pragma unroll
-    for (uint32_t i = 0; i < kMaxPairsPerThread; ++i) {
-        const uint32_t pair = threadIdx.x + i * kNormThreads;
-        if (pair < pairs) {
-            pair_sums[pair][0] = sum[i];
-            pair_sums[pair][1] = squares[i];
-        }
-    }
     __syncthreads();
-    // one thread per group adds its pairs in channel order
+    // one thread per group adds its pairs: row slots in order, channels in order
     if (threadIdx.x < p.groups) {
-        const uint32_t pairs_per_group = pairs / p.groups;
+        const uint32_t pairs_per_group = m.pairs / p.groups;
         float total = 0.0f, total_squares = 0.0f;
-        for (uint32_t j = 0; j < pairs_per_group; ++j) {
-            total += pair_sums[threadIdx.x * pairs_per_group + j][0];
-            total_squares += pair_sums[threadIdx.x * pairs_per_group + j][1];
+        for (uint32_t slot = 0; slot < m.rows_at_once; ++slot) {
+            for (uint32_t j = 0; j < pairs_per_group; ++j) {
+                const uint32_t index = slot * m.pairs + threadIdx.x * pairs_per_group + j;
+                total += pair_sums[index][0];
+                total_squares += pair_sums[index][1];
+            }
         }
         float* out = p.partials + ((static_cast<size_t>(batch) * gridDim.x + chunk) * p.groups + threadIdx.x) * 2;
         out[0] = total;
@@ -79,13 +120,15 @@ group_norm_stats_kernel(const GroupNormLaunch p) {
     }
 }
 
+template <uint32_t kPairsPerThread>
 __global__ void __launch_bounds__(kNormThreads)
 group_norm_apply_kernel(const GroupNormLaunch p) {
+    constexpr uint32_t kUnroll = kPairsPerThread == 1 ? 8 : (kPairsPerThread == 2 ? 4 : 2);
     __shared__ float group_mean[64], group_inverse[64];
     const uint32_t batch = blockIdx.y;
     const uint32_t chunk = blockIdx.x;
-    const uint32_t pairs = p.channels / 2;
-    const uint32_t pairs_per_group = pairs / p.groups;
+    const NormMapping m = norm_mapping(p.channels);
+    const uint32_t pairs_per_group = m.pairs / p.groups;
     if (threadIdx.x < p.groups) {
         double total = 0.0, total_squares = 0.0;
         const float* partial = p.partials + (static_cast<size_t>(batch) * gridDim.x * p.groups + threadIdx.x) * 2;
@@ -100,12 +143,13 @@ group_norm_apply_kernel(const GroupNormLaunch p) {
         group_inverse[threadIdx.x] = rsqrtf(static_cast<float>(variance) + p.epsilon);
     }
     __syncthreads();
+    if (!m.active) return;
 
-    float2 mean[kMaxPairsPerThread], inverse[kMaxPairsPerThread], gamma[kMaxPairsPerThread], beta[kMaxPairsPerThread];
+    float2 mean[kPairsPerThread], inverse[kPairsPerThread], gamma[kPairsPerThread], beta[kPairsPerThread];
 #pragma unroll
-    for (uint32_t i = 0; i < kMaxPairsPerThread; ++i) {
-        const uint32_t pair = threadIdx.x + i * kNormThreads;
-        if (pair < pairs) {
+    for (uint32_t i = 0; i < kPairsPerThread; ++i) {
+        const uint32_t pair = m.first_pair + i * kNormThreads;
+        if (pair < m.pairs) {
             const uint32_t group = pair / pairs_per_group;
             mean[i] = make_float2(group_mean[group], group_mean[group]);
             inverse[i] = make_float2(group_inverse[group], group_inverse[group]);
@@ -118,21 +162,36 @@ group_norm_apply_kernel(const GroupNormLaunch p) {
     const __half* base = p.x + static_cast<size_t>(batch) * p.rows * p.channels;
     __half* out_base = p.y + static_cast<size_t>(batch) * p.rows * p.channels;
     const __half* bias_row = p.channel_bias != nullptr ? p.channel_bias + static_cast<size_t>(batch) * p.channels : nullptr;
-    for (uint32_t row = first_row; row < last_row; ++row) {
-        const __half* source = base + static_cast<size_t>(row) * p.channels;
-        __half* destination = out_base + static_cast<size_t>(row) * p.channels;
+    const uint32_t step = m.rows_at_once * kUnroll;
+    for (uint32_t row0 = first_row + m.slot; row0 < last_row; row0 += step) {
+        float2 v[kUnroll][kPairsPerThread];
 #pragma unroll
-        for (uint32_t i = 0; i < kMaxPairsPerThread; ++i) {
-            const uint32_t pair = threadIdx.x + i * kNormThreads;
-            if (pair < pairs) {
-                const float2 v = load_pair(source, pair, bias_row);
-                float lo = fmaf((v.x - mean[i].x) * inverse[i].x, gamma[i].x, beta[i].x);
-                float hi = fmaf((v.y - mean[i].y) * inverse[i].y, gamma[i].y, beta[i].y);
-                if (p.silu != 0) {
-                    lo = __fdividef(lo, 1.0f + __expf(-lo));
-                    hi = __fdividef(hi, 1.0f + __expf(-hi));
+        for (uint32_t u = 0; u < kUnroll; ++u) {
+            const uint32_t row = row0 + u * m.rows_at_once;
+            const __half* source = base + static_cast<size_t>(row) * p.channels;
+#pragma unroll
+            for (uint32_t i = 0; i < kPairsPerThread; ++i) {
+                const uint32_t pair = m.first_pair + i * kNormThreads;
+                if (row < last_row && pair < m.pairs) v[u][i] = load_pair(source, pair, bias_row);
+            }
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < kUnroll; ++u) {
+            const uint32_t row = row0 + u * m.rows_at_once;
+            if (row >= last_row) break;
+            __half* destination = out_base + static_cast<size_t>(row) * p.channels;
+#pragma unroll
+            for (uint32_t i = 0; i < kPairsPerThread; ++i) {
+                const uint32_t pair = m.first_pair + i * kNormThreads;
+                if (pair < m.pairs) {
+                    float lo = fmaf((v[u][i].x - mean[i].x) * inverse[i].x, gamma[i].x, beta[i].x);
+                    float hi = fmaf((v[u][i].y - mean[i].y) * inverse[i].y, gamma[i].y, beta[i].y);
+                    if (p.silu != 0) {
+                        lo = __fdividef(lo, 1.0f + __expf(-lo));
+                        hi = __fdividef(hi, 1.0f + __expf(-hi));
+                    }
+                    *reinterpret_cast<__half2*>(destination + 2 * pair) = __floats2half2_rn(lo, hi);
                 }
-                *reinterpret_cast<__half2*>(destination + 2 * pair) = __floats2half2_rn(lo, hi);
             }
         }
     }
@@ -144,10 +203,21 @@ uint32_t group_norm_max_channels() { return 2 * kNormThreads * kMaxPairsPerThrea
 
 cudaError_t launch_group_norm_nhwc(const GroupNormLaunch& launch, uint32_t chunks, cudaStream_t stream) {
     const dim3 grid(chunks, launch.batch, 1);
-    group_norm_stats_kernel<<<grid, kNormThreads, 0, stream>>>(launch);
-    cudaError_t status = cudaGetLastError();
+    const uint32_t pairs_per_thread = (launch.channels / 2 + kNormThreads - 1) / kNormThreads;
+    switch (pairs_per_thread) {
+    case 1: group_norm_stats_kernel<1><<<grid, kNormThreads, 0, stream>>>(launch); break;
+    case 2: group_norm_stats_kernel<2><<<grid, kNormThreads, 0, stream>>>(launch); break;
+    case 3: group_norm_stats_kernel<3><<<grid, kNormThreads, 0, stream>>>(launch); break;
+    default: group_norm_stats_kernel<4><<<grid, kNormThreads, 0, stream>>>(launch); break;
+    }
+    const cudaError_t status = cudaGetLastError();
     if (status != cudaSuccess) return status;
-    group_norm_apply_kernel<<<grid, kNormThreads, 0, stream>>>(launch);
+    switch (pairs_per_thread) {
+    case 1: group_norm_apply_kernel<1><<<grid, kNormThreads, 0, stream>>>(launch); break;
+    case 2: group_norm_apply_kernel<2><<<grid, kNormThreads, 0, stream>>>(launch); break;
+    case 3: group_norm_apply_kernel<3><<<grid, kNormThreads, 0, stream>>>(launch); break;
+    default: group_norm_apply_kernel<4><<<grid, kNormThreads, 0, stream>>>(launch); break;
+    }
     return cudaGetLastError();
 }
 

@@ -269,6 +269,14 @@ class UNetHarness:
                 self.tensors[name] = values.to(torch.float16).contiguous(memory_format=torch.channels_last)
             else:
                 self.tensors[name] = values.to(torch.float16).contiguous()
+        # conv1's bias and the time-embedding projection's bias are both added per (image, channel) in front
+        # of norm2: one vector, added once (by the norm kernel's channel bias) instead of twice over the tensor
+        self._temb_bias: Dict[str, torch.Tensor] = {}
+        for name in self.projections:
+            if name.endswith(".time_emb_proj"):
+                prefix = name[: -len(".time_emb_proj")]
+                folded = self.tensors[f"{name}.bias"].float() + self.tensors[f"{prefix}.conv1.bias"].float()
+                self._temb_bias[name] = folded.to(torch.float16).contiguous()
         self.projection_calls = 0          # projections issued by the last forward (K/V cache included)
         self._kv: Dict[str, torch.Tensor] = {}
         self._kv_plan = None
@@ -323,8 +331,9 @@ class UNetHarness:
         y = F.group_norm(x, self.config.norm_groups, gamma, beta, eps)
         return F.silu(y) if silu else y
 
-    def _conv(self, x, prefix, stride=1, padding=1):
-        return F.conv2d(x, self.tensors[f"{prefix}.weight"], self.tensors[f"{prefix}.bias"], stride=stride, padding=padding)
+    def _conv(self, x, prefix, stride=1, padding=1, bias=True):
+        return F.conv2d(x, self.tensors[f"{prefix}.weight"], self.tensors[f"{prefix}.bias"] if bias else None,
+                        stride=stride, padding=padding)
 
     def _layer_norm(self, x, prefix, consumer: str):
         """Ops::layer_norm in front of the projection `consumer`. Returns an FP16 tensor, or with the
@@ -384,7 +393,7 @@ class UNetHarness:
             if self._temb_plan is not None:
                 self._temb_plan.close()
             self._temb_input = activated.clone()
-            calls = [LinearCall(self._temb_input, self.projections[name], self._bias(name)) for name in names]
+            calls = [LinearCall(self._temb_input, self.projections[name], self._temb_bias[name]) for name in names]
             self._temb_plan = self.ops.plan(calls)
             self._temb_outputs = dict(zip(names, [call.y for call in self._temb_plan.calls]))
         self._temb_input.copy_(activated)
@@ -395,7 +404,7 @@ class UNetHarness:
     # -- blocks -------------------------------------------------------------------------------------
     def _resnet(self, prefix, x, projected_temb):
         hidden = self._group_norm(x, f"{prefix}.norm1", silu=True)
-        hidden = self._conv(hidden, f"{prefix}.conv1")
+        hidden = self._conv(hidden, f"{prefix}.conv1", bias=False)           # its bias travels with the time embedding
         # add_spatial_bias, then group_norm_silu
         hidden = self._group_norm(hidden, f"{prefix}.norm2", silu=True, channel_bias=projected_temb[f"{prefix}.time_emb_proj"])
         hidden = self._conv(hidden, f"{prefix}.conv2")
