@@ -263,6 +263,13 @@ typedef struct sdxlq_group_norm_desc {
 } sdxlq_group_norm_desc;
 int sdxlq_group_norm_nhwc(sdxlq_context* ctx, const sdxlq_group_norm_desc* desc);
 
+/* y[r, c] = half(half(x[r, c] + bias[c]) + residual[r, c]) over channels-last FP16 x[rows, channels]: the
+ * bias add of a convolution whose library call leaves the bias out, and the resnet's residual add
+ * (Ops::add, src/cuda/unet.cpp:92), in one pass. channels a multiple of 8, all pointers 16-byte
+ * aligned (SDXLQ_ERR_UNSUPPORTED_SHAPE otherwise); y may alias x or residual. */
+int sdxlq_harness_bias_residual_add(sdxlq_context* ctx, const void* x, const void* bias, const void* residual, void* y,
+                                    uint64_t rows, uint64_t channels);
+
 /* ---- load-time weight packers ------------------------------------------------------------- */
 
 /* upload_or_quantize_int8_weight (int8_convrot.cu:498-577) for a weight already on the device:

@@ -135,7 +135,7 @@ EXPORTED_SYMBOLS = [
     "sdxlq_pack_weight_int8", "sdxlq_pack_weight_fp8", "sdxlq_valid_convrot_group_size",
     "sdxlq_workspace_bytes", "sdxlq_build_info", "sdxlq_context_set_tile_n",
     "sdxlq_selftest_bounded_wait", "sdxlq_profile_enable", "sdxlq_profile_read", "sdxlq_linear_static",
-    "sdxlq_context_set_pair_mode", "sdxlq_layer_norm", "sdxlq_group_norm_nhwc",
+    "sdxlq_context_set_pair_mode", "sdxlq_layer_norm", "sdxlq_group_norm_nhwc", "sdxlq_harness_bias_residual_add",
 ]
 
 _lib: Optional[ctypes.CDLL] = None
@@ -189,6 +189,7 @@ def load_library() -> ctypes.CDLL:
     lib.sdxlq_linear_static.argtypes = [ctypes.c_int, vp, ctypes.POINTER(_CLinearDesc), ctypes.c_char_p, sz]
     lib.sdxlq_layer_norm.argtypes = [vp, ctypes.POINTER(_CLayerNormDesc)]
     lib.sdxlq_group_norm_nhwc.argtypes = [vp, ctypes.POINTER(_CGroupNormDesc)]
+    lib.sdxlq_harness_bias_residual_add.argtypes = [vp, vp, vp, vp, vp, u64, u64]
     _lib = lib
     return lib
 
@@ -522,6 +523,21 @@ class Ops:
         desc = _CGroupNormDesc(input.data_ptr(), _ptr(channel_bias), weight.data_ptr(), bias.data_ptr(), out.data_ptr(),
                                batch, height * width, channels, groups, int(silu), epsilon, 0)
         self.ctx.raise_for(self._lib.sdxlq_group_norm_nhwc(self.ctx.handle, ctypes.byref(desc)))
+        return out
+
+    def bias_residual_add_nhwc(self, input: torch.Tensor, bias: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        """half(half(input + bias[c]) + residual) for channels-last [B, C, H, W] FP16 tensors: a convolution's
+        bias add and Ops::add with the resnet's residual (src/cuda/unet.cpp:92) in one pass."""
+        if input.dtype != torch.float16 or residual.dtype != torch.float16 or bias.dtype != torch.float16 or \
+                input.shape != residual.shape or input.dim() != 4 or bias.shape != (input.shape[1],):
+            raise CudaError("CUDA add requires matching FP16 tensors")
+        if not (input.is_contiguous(memory_format=torch.channels_last) and residual.is_contiguous(memory_format=torch.channels_last)):
+            raise CudaError("bias_residual_add_nhwc expects channels-last tensors")
+        batch, channels, height, width = (int(v) for v in input.shape)
+        out = torch.empty_like(input, memory_format=torch.channels_last)
+        self.ctx.raise_for(self._lib.sdxlq_harness_bias_residual_add(
+            self.ctx.handle, input.data_ptr(), bias.data_ptr(), residual.data_ptr(), out.data_ptr(),
+            batch * height * width, channels))
         return out
 
     # -- Ops::quantize_fp8 / quantize_e4m3 / quantize_e5m2 ------------------------------------------

@@ -1239,6 +1239,25 @@ int sdxlq_group_norm_nhwc(sdxlq_context* ctx, const sdxlq_group_norm_desc* desc)
     return SDXLQ_OK;
 }
 
+int sdxlq_harness_bias_residual_add(sdxlq_context* ctx, const void* x, const void* bias, const void* residual, void* y,
+                                    uint64_t rows, uint64_t channels) {
+    if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;
+    if (rows == 0 || channels == 0) return SDXLQ_OK;
+    if (x == nullptr || bias == nullptr || residual == nullptr || y == nullptr) {
+        return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "CUDA add requires matching FP16 tensors");
+    }
+    const auto aligned = [](const void* pointer) { return reinterpret_cast<uintptr_t>(pointer) % 16 == 0; };
+    if (channels % 8 != 0 || channels > 0x7FFFFFFFull || !aligned(x) || !aligned(bias) || !aligned(residual) || !aligned(y)) {
+        return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE, "bias_residual_add: 16-byte aligned rows of a multiple of 8 channels");
+    }
+    LaunchTimer timer(ctx, SDXLQ_KERNEL_HARNESS);
+    const cudaError_t error = launch_bias_residual_add(static_cast<const __half*>(x), static_cast<const __half*>(bias),
+                                                       static_cast<const __half*>(residual), static_cast<__half*>(y), rows,
+                                                       static_cast<uint32_t>(channels), static_cast<uint32_t>(ctx->sm_count), ctx->stream);
+    if (error != cudaSuccess) return fail_cuda(ctx, error, "bias_residual_add launch");
+    return SDXLQ_OK;
+}
+
 int sdxlq_pack_weight_int8(sdxlq_context* ctx, const void* src, int32_t src_dtype, uint64_t n, uint64_t k,
                            uint32_t convrot_group_size, int8_t* dst, float* scales) {
     if (ctx == nullptr) return SDXLQ_ERR_INVALID_ARGUMENT;

@@ -104,5 +104,7 @@ struct GroupNormLaunch {
 };
 uint32_t group_norm_max_channels();
 cudaError_t launch_group_norm_nhwc(const GroupNormLaunch& launch, uint32_t chunks, cudaStream_t stream);
+cudaError_t launch_bias_residual_add(const __half* x, const __half* bias, const __half* residual, __half* y, uint64_t rows,
+                                     uint32_t channels, uint32_t sm_count, cudaStream_t stream);
 
 }  // namespace sdxlq

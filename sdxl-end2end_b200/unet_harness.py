@@ -407,10 +407,16 @@ class UNetHarness:
         hidden = self._conv(hidden, f"{prefix}.conv1", bias=False)           # its bias travels with the time embedding
         # add_spatial_bias, then group_norm_silu
         hidden = self._group_norm(hidden, f"{prefix}.norm2", silu=True, channel_bias=projected_temb[f"{prefix}.time_emb_proj"])
-        hidden = self._conv(hidden, f"{prefix}.conv2")
         residual = x
         if f"{prefix}.conv_shortcut.weight" in self.tensors:
             residual = self._conv(x, f"{prefix}.conv_shortcut", padding=0)
+        if self.fuse_group_norm and hidden.shape[1] % 8 == 0 and residual.is_contiguous(memory_format=torch.channels_last):
+            hidden = self._conv(hidden, f"{prefix}.conv2", bias=False)
+            if hidden.is_contiguous(memory_format=torch.channels_last):
+                # conv2's bias add and the residual add in one pass
+                return self.ops.bias_residual_add_nhwc(hidden, self.tensors[f"{prefix}.conv2.bias"], residual)
+            return (hidden + self.tensors[f"{prefix}.conv2.bias"][None, :, None, None]) + residual
+        hidden = self._conv(hidden, f"{prefix}.conv2")
         return hidden + residual
 
     def _transformer_block(self, prefix, hidden, heads):

@@ -79,6 +79,10 @@ class FakeOps:
             y = F.silu(y)
         return y.to(torch.float16).contiguous(memory_format=torch.channels_last)
 
+    def bias_residual_add_nhwc(self, x, bias, residual):
+        biased = (x.float() + bias.float()[None, :, None, None]).to(torch.float16)
+        return (biased.float() + residual.float()).to(torch.float16).contiguous(memory_format=torch.channels_last)
+
     def linear(self, x, weight, bias=None, *, residual=None, out=None, **_):
         self.log.append(("linear", x.numel() // weight.k, weight.n, weight.k, bias is not None, 0, residual is not None))
         y = self._compute(x, weight, bias, 0, residual)

@@ -195,3 +195,15 @@ def test_group_norm_kernel_in_the_harness_stays_within_rounding(gpu, precision):
     rms = float(np.sqrt(np.mean((ours - torch_norm) ** 2)) / np.sqrt(np.mean(torch_norm ** 2)))
     print(f"{precision}: library GroupNorm vs torch group_norm rms rel = {rms:.3e}")
     assert rms <= (5e-3 if precision == "f16" else 1.5e-1)
+
+
+def test_bias_residual_add_equals_two_pytorch_adds(gpu):
+    pkg, ctx, ops = gpu
+    generator = torch.Generator(device="cuda").manual_seed(31)
+    x = torch.randn((2, 320, 16, 16), generator=generator, device="cuda").half().contiguous(memory_format=torch.channels_last)
+    residual = torch.randn((2, 320, 16, 16), generator=generator, device="cuda").half().contiguous(memory_format=torch.channels_last)
+    bias = torch.randn(320, generator=generator, device="cuda").half()
+    got = ops.bias_residual_add_nhwc(x, bias, residual)
+    ctx.check()
+    want = (x + bias[None, :, None, None]) + residual          # two FP16 roundings, like the two kernels it replaces
+    assert got.is_contiguous(memory_format=torch.channels_last) and torch.equal(got, want)
