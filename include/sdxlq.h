@@ -103,6 +103,18 @@ typedef struct sdxlq_linear_desc {
      * folded into the epilogue. May alias y (the hidden state updated in place). Requires
      * activation == NONE. */
     const void* residual;
+    /* Hand-over of the FP8 activation quantiser's maximum between two projections (the GEGLU output of
+     * ff.net.0.proj is the input of ff.net.2): quantize_tensor_fp8 (fp8_kernels.cu:157-190) reads its
+     * input once for max |x| and once for the cast; the first read is saved when the kernel that wrote
+     * x already knows the maximum.
+     *   y_amax  optional device word (uint32): receives max |y| over this call's FP16 output as the bit
+     *           pattern of the FP32 value, by atomic maximum. Zero it once after allocation; the
+     *           consuming call puts it back to zero.
+     *   x_amax  optional device word filled by the producer of x: FP8 weights only, ignored otherwise;
+     *           the quantiser of this call skips its maximum pass, reads the word and clears it.
+     * Results are bit-identical to the calls without the words. */
+    void* y_amax;
+    const void* x_amax;
 } sdxlq_linear_desc;
 
 /* sdxl::cuda::INT8ExecutionStats (runtime.hpp:106-112). Every INT8 Linear here runs on the

@@ -89,6 +89,8 @@ class _CLinearDesc(ctypes.Structure):
         ("xq_scales", ctypes.c_void_p),
         ("acc_out", ctypes.c_void_p),
         ("residual", ctypes.c_void_p),
+        ("y_amax", ctypes.c_void_p),
+        ("x_amax", ctypes.c_void_p),
     ]
 
 
@@ -288,6 +290,8 @@ class LinearCall:
     xq_scales: Optional[torch.Tensor] = None
     acc_out: Optional[torch.Tensor] = None
     residual: Optional[torch.Tensor] = None
+    y_amax: Optional[torch.Tensor] = None      # one int32 device word: receives max |y| (FP32 bits)
+    x_amax: Optional[torch.Tensor] = None      # the word a producer filled for x (FP8 weights)
     keep: list = field(default_factory=list)
 
 
@@ -408,17 +412,18 @@ class Ops:
                 raise CudaError("CUDA add requires matching FP16 tensors")
         return _CLinearDesc(_ptr(x), m, weight.c_struct(), _ptr(call.bias), int(call.activation), 0,
                             _ptr(call.y), _ptr(call.xq), _ptr(call.xq_scales), _ptr(call.acc_out),
-                            _ptr(call.residual))
+                            _ptr(call.residual), _ptr(call.y_amax), _ptr(call.x_amax))
 
     # -- Ops::linear / Ops::linear_activation ----------------------------------------------------
     def linear(self, input: torch.Tensor, weight: Weight, bias: Optional[torch.Tensor] = None, *,
                xq: Optional[torch.Tensor] = None, xq_scales: Optional[torch.Tensor] = None,
                acc_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-               residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+               residual: Optional[torch.Tensor] = None, y_amax: Optional[torch.Tensor] = None,
+               x_amax: Optional[torch.Tensor] = None) -> torch.Tensor:
         """`residual` folds the Ops::add_in_place that follows the projection in the reference's
         transformer block (src/cuda/unet.cpp:118, 132, 147) into the epilogue; pass out=residual to
         update the hidden state in place."""
-        call = LinearCall(input, weight, bias, ACT_NONE, out, xq, xq_scales, acc_out, residual)
+        call = LinearCall(input, weight, bias, ACT_NONE, out, xq, xq_scales, acc_out, residual, y_amax, x_amax)
         desc = self._desc(call)
         self.ctx.raise_for(self._lib.sdxlq_linear(self.ctx.handle, ctypes.byref(desc)))
         return call.y
@@ -427,8 +432,9 @@ class Ops:
                           activation: int, *, xq: Optional[torch.Tensor] = None,
                           xq_scales: Optional[torch.Tensor] = None,
                           acc_out: Optional[torch.Tensor] = None,
-                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        call = LinearCall(input, weight, bias, int(activation), out, xq, xq_scales, acc_out)
+                          out: Optional[torch.Tensor] = None, y_amax: Optional[torch.Tensor] = None,
+                          x_amax: Optional[torch.Tensor] = None) -> torch.Tensor:
+        call = LinearCall(input, weight, bias, int(activation), out, xq, xq_scales, acc_out, None, y_amax, x_amax)
         desc = self._desc(call)
         self.ctx.raise_for(self._lib.sdxlq_linear(self.ctx.handle, ctypes.byref(desc)))
         return call.y

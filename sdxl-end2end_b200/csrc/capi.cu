@@ -415,8 +415,10 @@ int int8_quantiser_launches(const Prepared& prep) {
     return launches;
 }
 
-void add_fp8_job(Prepared& prep, const void* x, uint64_t count, uint32_t fmt, uint8_t* q, float* scale_out) {
+void add_fp8_job(Prepared& prep, const void* x, uint64_t count, uint32_t fmt, uint8_t* q, float* scale_out,
+                 uint32_t* amax_in = nullptr) {
     QuantFp8Job job{};
+    job.amax_in = amax_in;
     job.x = x;
     job.q = q;
     job.scale_out = scale_out;
@@ -511,7 +513,8 @@ int prepare(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count, bo
                         if (prep.fp8_jobs.size() >= kMaxFp8Jobs) {
                             return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE, "too many distinct FP8 inputs in one grouped call");
                         }
-                        add_fp8_job(prep, d.x, static_cast<uint64_t>(d.m) * w.k, kind == KIND_E4M3 ? 0 : 1, q, s);
+                        add_fp8_job(prep, d.x, static_cast<uint64_t>(d.m) * w.k, kind == KIND_E4M3 ? 0 : 1, q, s,
+                                    static_cast<uint32_t*>(const_cast<void*>(d.x_amax)));
                     }
                     found = shared_inputs.emplace(key, std::make_pair(static_cast<const void*>(q), static_cast<const float*>(s))).first;
                 }
@@ -527,6 +530,7 @@ int prepare(sdxlq_context* ctx, const sdxlq_linear_desc* descs, size_t count, bo
         ep.w_scales = w.scales;
         ep.bias = static_cast<const __half*>(d.bias);
         ep.residual = static_cast<const __half*>(d.residual);
+        ep.y_amax = static_cast<uint32_t*>(d.y_amax);
         ep.m = static_cast<uint32_t>(d.m);
         ep.n = static_cast<uint32_t>(w.n);
         ep.k = static_cast<uint32_t>(w.k);
@@ -788,8 +792,11 @@ int run_prepared(sdxlq_context* ctx, const Prepared& prep, const sdxlq_group_pla
     if (status != SDXLQ_OK) return status;
     if (!prep.fp8_jobs.empty()) {
         const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, tables != nullptr ? tables->device_fp8_jobs : nullptr);
-        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8, 2);
-        const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream, ctx->early_launch && !ctx->profiling);
+        bool every_job_has_its_maximum = true;
+        for (const QuantFp8Job& job : prep.fp8_jobs) every_job_has_its_maximum = every_job_has_its_maximum && job.amax_in != nullptr;
+        LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8, every_job_has_its_maximum ? 1 : 2);
+        const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream, ctx->early_launch && !ctx->profiling,
+                                                      every_job_has_its_maximum);
         if (error != cudaSuccess) return fail_cuda(ctx, error, "FP8 activation quantise launch");
     }
     for (int flavour = 0; flavour < 2; ++flavour) {
@@ -1108,7 +1115,7 @@ int sdxlq_quantize_act_fp8(sdxlq_context* ctx, const void* x_f16, uint64_t count
     add_fp8_job(prep, x_f16, count, fmt == SDXLQ_FP8_E4M3 ? 0 : 1, q, scale);
     const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, nullptr);
     LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8, 2);
-    const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream, ctx->early_launch && !ctx->profiling);
+    const cudaError_t error = launch_fp8_quantize(launch, prep.fp8_blocks, ctx->stream, ctx->early_launch && !ctx->profiling, false);
     if (error != cudaSuccess) return fail_cuda(ctx, error, "FP8 activation quantise launch");
     return SDXLQ_OK;
 }

@@ -292,6 +292,7 @@ struct EpilogueTile {
     __half* y;
     int32_t* acc_out;
     const __half* residual;         // [M, n_out] added after the bias, or null (may alias y)
+    uint32_t* amax_out;             // word that receives max |y| of the problem's output, or null
     const float* column_scale;      // shared memory
     const float* column_bias;       // shared memory, FP32
     const __half* column_bias_half; // shared memory, FP16
@@ -416,6 +417,9 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
     const uint32_t limit = min(diag_limit, min(columns, t.n_out > t.n0 ? t.n_out - t.n0 : 0u));
     const __half* const residual = Act == ACT_NONE ? t.residual : nullptr;
     const bool with_residual = residual != nullptr && row_ok;
+    // max |y| over this lane's outputs of the tile, for the FP8 quantiser of the projection that reads y
+    const bool want_amax = t.amax_out != nullptr;
+    __half2 running_max = __float2half2_rn(0.0f);
 
     for (uint32_t c = t.chunk_first * 16u; c < limit; c += kStride) {
         const uint32_t col0 = t.n0 + c;
@@ -476,6 +480,17 @@ __device__ __forceinline__ void epilogue_tile(const EpilogueTile& t) {
         if (row_ok && (!no_store || (out_words[0] == 0x7E57C0DEu && out_words[7] == 0x7E57C0DEu))) {
             store_row_16(t.y, t.n_out, store_vector, store_wide, t.row, col0, out_words);
         }
+        if (want_amax && row_ok) {
+            // columns past the matrix edge hold zeros (scale 0, bias 0), so they cannot win the maximum
+#pragma unroll
+            for (int i = 0; i < 8; ++i) running_max = __hmax2(running_max, __habs2(*reinterpret_cast<const __half2*>(&out_words[i])));
+        }
+    }
+    if (want_amax) {
+        float maximum = fmaxf(__low2float(running_max), __high2float(running_max));
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, offset));
+        if ((threadIdx.x & 31u) == 0 && maximum > 0.0f) atomicMax(t.amax_out, __float_as_uint(maximum));
     }
 }
 
@@ -841,6 +856,8 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
             if ((flags & TILE_RAW_ACCUMULATORS) != 0) tile.acc_out = tile_problem(params, work)->ep.acc_out;
             tile.residual = nullptr;
             if ((flags & TILE_HAS_RESIDUAL) != 0) tile.residual = tile_problem(params, work)->ep.residual;
+            tile.amax_out = nullptr;
+            if ((flags & TILE_OUTPUT_AMAX) != 0) tile.amax_out = tile_problem(params, work)->ep.y_amax;
             tile.column_scale = control->column_scale[buffer];
             tile.column_bias = control->column_bias[buffer];
             tile.column_bias_half = control->column_bias_half[buffer];

@@ -35,6 +35,7 @@ struct EpilogueParams {
     const float* w_scales;       // [N] or [1]; FP16: unused
     const __half* bias;          // [N] or null
     const __half* residual;      // optional [M, N] added to the biased projection (may alias y)
+    uint32_t* y_amax;            // optional word: atomic maximum of |y| (FP32 bit pattern) over this problem's output
     uint32_t m, n, k;
     uint32_t n_out;              // n, or n / 2 for GEGLU
     uint32_t kind;               // GemmKind
@@ -54,7 +55,7 @@ struct alignas(64) GemmProblem {
     uint32_t tiles_n;
     uint32_t k_blocks;           // ceil(K bytes / 128)
     uint32_t idesc;              // UMMA instruction descriptor
-    uint32_t pad[3];
+    uint32_t pad[1];
 };
 
 // One tile of a launch: everything the three kernel roles need to start on it, in one 64-byte
@@ -67,6 +68,7 @@ enum TileFlags : uint16_t {
     TILE_STORE_32 = 8,          // y rows 32-byte aligned and n_out % 16 == 0
     TILE_RAW_ACCUMULATORS = 16, // the problem also wants its INT32 accumulators (ep.acc_out)
     TILE_HAS_RESIDUAL = 32,     // ep.residual is added after the bias (no activation)
+    TILE_OUTPUT_AMAX = 64,      // ep.y_amax receives the maximum of |y|
 };
 
 struct alignas(64) TileRef {
@@ -107,7 +109,7 @@ __host__ __device__ inline TileRef make_tile_ref(const GemmProblem& problem, uin
                                     (ep.kind != KIND_F16 && ep.w_scale_per_channel != 0 ? TILE_SCALE_PER_CHANNEL : 0) |
                                     (ep.vector_store_ok != 0 ? TILE_STORE_16 : 0) | (store_32 ? TILE_STORE_32 : 0) |
                                     (ep.acc_out != nullptr ? TILE_RAW_ACCUMULATORS : 0) |
-                                    (ep.residual != nullptr ? TILE_HAS_RESIDUAL : 0));
+                                    (ep.residual != nullptr ? TILE_HAS_RESIDUAL : 0) | (ep.y_amax != nullptr ? TILE_OUTPUT_AMAX : 0));
     r.m = ep.m;
     r.n = ep.n;
     r.w_scales = ep.w_scales;

@@ -83,6 +83,8 @@ sdxlq_small_linear_kernel(const __grid_constant__ SmallLinearParams p) {
         if (ep.residual != nullptr) result = __hadd(result, ep.residual[static_cast<size_t>(row) * ep.n_out + col]);
     }
     ep.y[static_cast<size_t>(row) * ep.n_out + col] = result;
+    // the maximum of |y| for the consumer's FP8 quantiser (bit patterns of non-negative floats order like integers)
+    if (ep.y_amax != nullptr) atomicMax(ep.y_amax, __float_as_uint(fabsf(__half2float(result))));
 }
 
 cudaError_t launch_small_linear(const void* a, const void* b, const EpilogueParams& ep, uint32_t k_major,

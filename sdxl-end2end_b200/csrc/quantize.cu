@@ -319,6 +319,7 @@ fp8_amax_kernel(const __grid_constant__ QuantFp8Launch launch) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // lets the cast kernel be scheduled early
     const uint32_t job_index = find_job_index(launch, blockIdx.x);
     const QuantFp8Job& job = launch.jobs == nullptr ? launch.single : launch.jobs[job_index];
+    if (job.amax_in != nullptr) return;                                  // the producer of x left the maximum
     const uint32_t local_block = blockIdx.x - job.first_block;
     const __half* source = static_cast<const __half*>(job.x);
     const size_t count = job.count;
@@ -372,10 +373,11 @@ fp8_cast_kernel(const __grid_constant__ QuantFp8Launch launch) {
     // a captured graph) finds both words zero without any host-side bookkeeping.
     __shared__ uint32_t maximum_bits;
     if (threadIdx.x == 0) {
-        maximum_bits = *reinterpret_cast<volatile uint32_t*>(launch.amax_bits + job_index);
+        uint32_t* const word = job.amax_in != nullptr ? job.amax_in : launch.amax_bits + job_index;
+        maximum_bits = *reinterpret_cast<volatile uint32_t*>(word);
         __threadfence();
         if (atomicAdd(launch.done_counts + job_index, 1u) == job.num_blocks - 1u) {
-            launch.amax_bits[job_index] = 0;
+            *word = 0;
             launch.done_counts[job_index] = 0;
         }
     }
@@ -416,10 +418,14 @@ fp8_cast_kernel(const __grid_constant__ QuantFp8Launch launch) {
     }
 }
 
-cudaError_t launch_fp8_quantize(const QuantFp8Launch& launch, uint32_t blocks, cudaStream_t stream, bool early_launch) {
-    fp8_amax_kernel<<<blocks, 256, 0, stream>>>(launch);
-    cudaError_t status = cudaGetLastError();
-    if (status != cudaSuccess) return status;
+cudaError_t launch_fp8_quantize(const QuantFp8Launch& launch, uint32_t blocks, cudaStream_t stream, bool early_launch,
+                                bool skip_maximum_pass) {
+    // skip_maximum_pass: every job of the launch carries its maximum (amax_in), nothing to reduce
+    if (!skip_maximum_pass) {
+        fp8_amax_kernel<<<blocks, 256, 0, stream>>>(launch);
+        const cudaError_t status = cudaGetLastError();
+        if (status != cudaSuccess) return status;
+    }
     // The cast kernel needs the maxima of the kernel above. Launched with the programmatic-dependency
     // attribute it is scheduled while that kernel drains and waits (griddepcontrol.wait) before it
     // reads them; without the attribute the wait does nothing and the stream orders the two.

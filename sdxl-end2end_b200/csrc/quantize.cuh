@@ -45,6 +45,8 @@ struct QuantFp8Job {
     uint32_t vector_ok;
     uint32_t first_block;
     uint32_t num_blocks;
+    uint32_t* amax_in;           // optional: the maximum of |x| as FP32 bits, filled by the producer of x; the
+                                 // maximum kernel skips the job, the cast kernel reads this word and clears it
 };
 
 struct QuantFp8Launch {
@@ -59,7 +61,8 @@ struct QuantFp8Launch {
 
 cudaError_t launch_rotate_quantize_int8(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
                                         cudaStream_t stream);
-cudaError_t launch_fp8_quantize(const QuantFp8Launch& launch, uint32_t blocks, cudaStream_t stream, bool early_launch);
+cudaError_t launch_fp8_quantize(const QuantFp8Launch& launch, uint32_t blocks, cudaStream_t stream, bool early_launch,
+                                bool skip_maximum_pass);
 cudaError_t launch_fp8_weight_pack(const void* source, int32_t dtype, uint32_t n, uint32_t k, uint32_t fmt,
                                    uint32_t per_channel, uint32_t k_major, uint8_t* destination,
                                    float* scales, cudaStream_t stream);

@@ -277,6 +277,7 @@ class UNetHarness:
                 prefix = name[: -len(".time_emb_proj")]
                 folded = self.tensors[f"{name}.bias"].float() + self.tensors[f"{prefix}.conv1.bias"].float()
                 self._temb_bias[name] = folded.to(torch.float16).contiguous()
+        self._amax_word = torch.zeros(1, dtype=torch.int32, device=self.device)    # zero between uses: the reader clears it
         self.projection_calls = 0          # projections issued by the last forward (K/V cache included)
         self._kv: Dict[str, torch.Tensor] = {}
         self._kv_plan = None
@@ -305,13 +306,18 @@ class UNetHarness:
     def _bias(self, prefix: str) -> torch.Tensor:
         return self.tensors[f"{prefix}.bias"]
 
-    def _linear(self, x, prefix, activation=ACT_NONE, residual=None, out=None, bias=True):
-        """x is an FP16 tensor, or the (xq, xq_scales) pair of a fused LayerNorm."""
+    def _linear(self, x, prefix, activation=ACT_NONE, residual=None, out=None, bias=True, y_amax=None, x_amax=None):
+        """x is an FP16 tensor, or the (xq, xq_scales) pair of a fused LayerNorm. y_amax / x_amax: the word
+        through which a projection hands the maximum of its output to the FP8 quantiser of the next one."""
         self.projection_calls += 1
         b = self._bias(prefix) if bias else None
         quantised = {}
+        if y_amax is not None:
+            quantised["y_amax"] = y_amax
+        if x_amax is not None:
+            quantised["x_amax"] = x_amax
         if isinstance(x, tuple):
-            quantised = {"xq": x[0], "xq_scales": x[1]}
+            quantised.update({"xq": x[0], "xq_scales": x[1]})
             x = None
         if activation != ACT_NONE:
             return self.ops.linear_activation(x, self.projections[prefix], b, activation, **quantised)
@@ -442,8 +448,10 @@ class UNetHarness:
         hidden = self._linear(attention, f"{prefix}.attn2.to_out.0", residual=hidden, out=hidden)
 
         normalized = self._layer_norm(hidden, f"{prefix}.norm3", f"{prefix}.ff.net.0.proj")
-        feed_forward = self._linear(normalized, f"{prefix}.ff.net.0.proj", ACT_GEGLU)
-        hidden = self._linear(feed_forward, f"{prefix}.ff.net.2", residual=hidden, out=hidden)
+        # FP8: ff.net.0.proj's epilogue leaves max |GEGLU output| for the quantiser of ff.net.2
+        word = self._amax_word if self.precision in ("e4m3", "e5m2") else None
+        feed_forward = self._linear(normalized, f"{prefix}.ff.net.0.proj", ACT_GEGLU, y_amax=word)
+        hidden = self._linear(feed_forward, f"{prefix}.ff.net.2", residual=hidden, out=hidden, x_amax=word)
         return hidden
 
     def _transformer2d(self, prefix, x, depth, heads):

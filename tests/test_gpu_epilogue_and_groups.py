@@ -235,3 +235,35 @@ def test_contexts_with_different_tile_geometries_share_a_gpu(gpu, pkg):
         ctx_a.check()
         assert torch.equal(again, want_wide)
     ctx_b.close()
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+@pytest.mark.parametrize("m,n,k,activation", [(300, 2560, 640, 4), (256, 640, 640, 0), (37, 72, 40, 0)])
+def test_output_maximum_hand_over_to_the_fp8_quantiser(gpu, fmt, m, n, k, activation):
+    """y_amax: the producing projection leaves max |y| (FP32 bits) in a device word; x_amax: the consuming
+    FP8 projection skips its maximum pass, reads the word and clears it. Bit-identical to the plain calls;
+    the last shape runs on the small-shape kernel (row pitch not a multiple of 16 bytes)."""
+    pkg, ctx, ops = gpu
+    x = dev(H.make_activations(81, m, k, outliers=False))
+    first = H.make_weight(82, n, k)
+    n_mid = n // 2 if activation == 4 else n
+    second = H.make_weight(83, 320, n_mid)
+    weights = []
+    for w in (first, second):
+        wq, ws = O.fp8_quantize_weight(w.astype(np.float32), fmt, True)
+        weights.append(pkg.Weight(dev(wq), pkg.ScalarType(fmt), w.shape[0], w.shape[1], dev(ws), pkg.FP8ScaleMode.PerOutputChannel))
+    bias = dev(H.make_bias(84, n))
+    word = torch.zeros(1, dtype=torch.int32, device="cuda")
+    plain_mid = ops.linear_activation(x, weights[0], bias, activation) if activation else ops.linear(x, weights[0], bias)
+    plain_out = ops.linear(plain_mid, weights[1], None)
+    for _ in range(2):                                   # twice: the word must be back at zero after each use
+        mid = ops.linear_activation(x, weights[0], bias, activation, y_amax=word) if activation \
+            else ops.linear(x, weights[0], bias, y_amax=word)
+        ctx.check()
+        assert torch.equal(mid, plain_mid)
+        want_bits = plain_mid.float().abs().max().view(torch.int32)
+        assert int(word.item()) == int(want_bits.item())
+        out = ops.linear(mid, weights[1], None, x_amax=word)
+        ctx.check()
+        assert int(word.item()) == 0
+        assert torch.equal(out, plain_out)
