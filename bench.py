@@ -783,11 +783,16 @@ def run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks):
     achieved = step_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     # quantised inputs of one step: every projection input that is not the text context, once per key
     quant_inputs = {}
+    handed_over = {}               # FP8: inputs whose maximum arrives from the producing projection's epilogue
     for p in projections:
         if ".attn2.to_k" in p.name or ".attn2.to_v" in p.name:
             continue
-        quant_inputs.setdefault(p.input_key, (p.m, p.k))
-    quant_bytes = quantiser_bytes(quant_inputs.values(), kind)
+        if kind in ("e4m3", "e5m2") and p.name.endswith(".ff.net.2"):
+            handed_over.setdefault(p.input_key, (p.m, p.k))
+        else:
+            quant_inputs.setdefault(p.input_key, (p.m, p.k))
+    # 2 + 1 bytes per element where the maximum pass is skipped, 2 + 2 + 1 otherwise
+    quant_bytes = quantiser_bytes(quant_inputs.values(), kind) + float(sum(m * k * 3 for (m, k) in handed_over.values()))
     rows_table = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in projections
                   if not (".attn2.to_k" in p.name or ".attn2.to_v" in p.name)]
     roofline = {
