@@ -129,12 +129,27 @@ group_norm_apply_kernel(const GroupNormLaunch p) {
     const uint32_t chunk = blockIdx.x;
     const NormMapping m = norm_mapping(p.channels);
     const uint32_t pairs_per_group = m.pairs / p.groups;
-    if (threadIdx.x < p.groups) {
+    // Partial sums of this batch element, added in a fixed order by eight threads per group (thread l of a
+    // group takes chunks l, l + 8, ...), then the eight results in order: deterministic, and the chain of
+    // dependent additions is an eighth as long as with one thread per group.
+    __shared__ double lane_sums[64][8][2];
+    if (threadIdx.x < p.groups * 8u) {
+        const uint32_t group = threadIdx.x >> 3, part = threadIdx.x & 7u;
         double total = 0.0, total_squares = 0.0;
-        const float* partial = p.partials + (static_cast<size_t>(batch) * gridDim.x * p.groups + threadIdx.x) * 2;
-        for (uint32_t c = 0; c < gridDim.x; ++c) {
+        const float* partial = p.partials + (static_cast<size_t>(batch) * gridDim.x * p.groups + group) * 2;
+        for (uint32_t c = part; c < gridDim.x; c += 8) {
             total += static_cast<double>(partial[static_cast<size_t>(c) * p.groups * 2]);
             total_squares += static_cast<double>(partial[static_cast<size_t>(c) * p.groups * 2 + 1]);
+        }
+        lane_sums[group][part][0] = total;
+        lane_sums[group][part][1] = total_squares;
+    }
+    __syncthreads();
+    if (threadIdx.x < p.groups) {
+        double total = 0.0, total_squares = 0.0;
+        for (uint32_t part = 0; part < 8; ++part) {
+            total += lane_sums[threadIdx.x][part][0];
+            total_squares += lane_sums[threadIdx.x][part][1];
         }
         const double count = static_cast<double>(p.rows) * (2.0 * pairs_per_group);
         const double mean = total / count;
