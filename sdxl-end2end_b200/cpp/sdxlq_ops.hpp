@@ -162,6 +162,63 @@ public:
         return outputs;
     }
 
+    // Ops::layer_norm (include/sdxl/cuda/ops.hpp:39-42, src/cuda/ops_kernels.cu:1425-1470): FP16 in, FP16 out.
+    [[nodiscard]] TensorRef layer_norm(const TensorRef& input, const TensorRef& weight, const TensorRef& bias,
+                                       float epsilon = 1.0e-5F) const {
+        sdxlq_layer_norm_desc desc = describe_norm(input, weight, bias, epsilon);
+        TensorRef output = input;
+        output.data = allocate_(input.elements() * sizeof(std::uint16_t));
+        desc.out_dtype = SDXLQ_FP16;
+        desc.y = output.data;
+        runtime_->check(sdxlq_layer_norm(runtime_->context(), &desc));
+        return output;
+    }
+
+    // Ops::layer_norm fused with the activation quantiser of the projection(s) that read the result
+    // (to_q / to_k / to_v, attn2.to_q, ff.net.0.proj; src/cuda/unet.cpp:108-112, 121-124, 135-138): the
+    // normalised FP16 tensor is never written. The result carries the quantised rows and their scale(s)
+    // in the form `consumer` wants; pass it to linear_quantized.
+    struct QuantizedActivations {
+        void* data = nullptr;            // INT8 or FP8 [rows, width]
+        float* scales = nullptr;         // [rows] (INT8) or [1] (FP8)
+        std::vector<std::size_t> shape;
+    };
+    [[nodiscard]] QuantizedActivations layer_norm_quantized(const TensorRef& input, const TensorRef& weight,
+                                                            const TensorRef& bias, const TensorRef& consumer,
+                                                            float epsilon = 1.0e-5F) const {
+        sdxlq_layer_norm_desc desc = describe_norm(input, weight, bias, epsilon);
+        if (consumer.rank() != 2 || consumer.size(1) != desc.width) throw CudaError("CUDA linear feature mismatch");
+        if (consumer.type != ScalarType::Int8 && !is_fp8(consumer.type)) {
+            throw CudaError("layer_norm_quantized wants an INT8 or FP8 projection weight");
+        }
+        QuantizedActivations result;
+        result.shape = input.shape;
+        result.data = allocate_(input.elements());
+        result.scales = static_cast<float*>(allocate_((consumer.type == ScalarType::Int8 ? desc.rows : 1) * sizeof(float)));
+        desc.out_dtype = static_cast<std::int32_t>(consumer.type);
+        desc.convrot_group_size = static_cast<std::uint32_t>(consumer.convrot_group_size);
+        desc.xq = result.data;
+        desc.xq_scales = result.scales;
+        runtime_->check(sdxlq_layer_norm(runtime_->context(), &desc));
+        return result;
+    }
+
+    // Ops::linear / linear_activation on rows that layer_norm_quantized (or quantize_*) produced.
+    [[nodiscard]] TensorRef linear_quantized(const QuantizedActivations& input, const TensorRef& weight,
+                                             const TensorRef* bias = nullptr,
+                                             LinearActivation activation = LinearActivation::None) const {
+        TensorRef shape_only;
+        shape_only.shape = input.shape;
+        shape_only.data = input.data;                   // only the shape is read: xq replaces x below
+        TensorRef output;
+        sdxlq_linear_desc desc = describe(shape_only, weight, bias, activation, output);
+        desc.x = nullptr;
+        desc.xq = input.data;
+        desc.xq_scales = input.scales;
+        runtime_->check(sdxlq_linear(runtime_->context(), &desc));
+        return output;
+    }
+
     // Ops::quantize_fp8 / quantize_e4m3 / quantize_e5m2 (src/cuda/ops_blas.cpp:231-242).
     [[nodiscard]] TensorRef quantize_fp8(const TensorRef& input, ScalarType fp8_type) const {
         if (input.type != ScalarType::Float16 || !is_fp8(fp8_type)) {
@@ -235,6 +292,26 @@ private:
     }
 
     // Validates like Ops::linear, allocates the output and fills the C descriptor.
+    // The checks of Ops::layer_norm (src/cuda/ops_kernels.cu:1425-1440), with its messages.
+    [[nodiscard]] static sdxlq_layer_norm_desc describe_norm(const TensorRef& input, const TensorRef& weight,
+                                                             const TensorRef& bias, float epsilon) {
+        if (input.type != ScalarType::Float16 || weight.type != ScalarType::Float16 || bias.type != ScalarType::Float16 ||
+            input.rank() < 1 || weight.rank() != 1 || bias.rank() != 1) {
+            throw CudaError("CUDA layer_norm expects an FP16 input with rank-1 FP16 weight and bias");
+        }
+        const std::size_t width = input.shape.back();
+        if (width == 0) throw CudaError("layer_norm requires a non-empty last dimension");
+        if (weight.size(0) != width || bias.size(0) != width) throw CudaError("CUDA layer_norm width mismatch");
+        sdxlq_layer_norm_desc desc{};
+        desc.x = input.data;
+        desc.rows = input.elements() / width;
+        desc.width = width;
+        desc.gamma = weight.data;
+        desc.beta = bias.data;
+        desc.epsilon = epsilon;
+        return desc;
+    }
+
     [[nodiscard]] sdxlq_linear_desc describe(const TensorRef& input, const TensorRef& weight, const TensorRef* bias,
                                              LinearActivation activation, TensorRef& output,
                                              bool allocate_output = true) const {

@@ -134,6 +134,26 @@ int main(int argc, char** argv) {
         const std::uint64_t calls = runtime.int8_execution_stats().linear_calls;
         out.write(reinterpret_cast<const char*>(&calls), sizeof(calls));
 
+        // LayerNorm in front of the projection: the fused form (quantised rows straight out of the norm)
+        // against layer_norm followed by linear, bit for bit
+        if (precision != 2 && k <= 2048 && activation == sdxlq::LinearActivation::None) {
+            std::vector<std::uint16_t> gamma_host(k, 0x3C00), beta_host(x.begin(), x.begin() + static_cast<std::ptrdiff_t>(k));
+            sdxlq::TensorRef gamma = upload(arena, gamma_host, {k});
+            sdxlq::TensorRef beta = upload(arena, beta_host, {k});
+            const sdxlq::TensorRef normalised = ops.layer_norm(input, gamma, beta);
+            const sdxlq::TensorRef separate = ops.linear(normalised, weight, &bias);
+            const sdxlq::Ops::QuantizedActivations rows = ops.layer_norm_quantized(input, gamma, beta, weight);
+            const sdxlq::TensorRef fused = ops.linear_quantized(rows, weight, &bias);
+            runtime.synchronize();
+            std::vector<std::uint16_t> a(m * n), c(m * n);
+            check(cudaMemcpy(a.data(), separate.data, a.size() * 2, cudaMemcpyDeviceToHost), "download");
+            check(cudaMemcpy(c.data(), fused.data, c.size() * 2, cudaMemcpyDeviceToHost), "download");
+            if (a != c) {
+                std::cerr << "fused LayerNorm projection differs from layer_norm + linear\n";
+                return 7;
+            }
+        }
+
         // error behaviour: the reference's message for a feature mismatch
         sdxlq::TensorRef wrong = input;
         wrong.shape = {m, k + 1};
