@@ -255,8 +255,9 @@ int sdxlq_layer_norm(sdxlq_context* ctx, const sdxlq_layer_norm_desc* desc);
  * (include/sdxl/cuda/ops.hpp:43-52, src/cuda/ops_kernels.cu:258-308) compute, on the layout the
  * synthetic UNet loop keeps its convolution activations in, so that no layout copy surrounds the
  * norm. channel_bias (optional, [batch, channels] FP16) is added first with FP16 rounding: the
- * resnet's add_spatial_bias in front of norm2. y may alias x. channels must be a multiple of
- * 2 * groups and at most 2560, groups at most 64; SDXLQ_ERR_UNSUPPORTED_SHAPE otherwise. Exists so
+ * resnet's add_spatial_bias in front of norm2. y may alias x. channels must be a multiple of 8 and of
+ * groups, at most 3072, with 16-byte aligned tensors; groups at most 64, batch at most 1024;
+ * SDXLQ_ERR_UNSUPPORTED_SHAPE otherwise. Exists so
  * that the benchmark's UNet loop does not spend a quarter of its step on layout copies; it is not a
  * drop-in for the reference's NCHW operator. */
 typedef struct sdxlq_group_norm_desc {

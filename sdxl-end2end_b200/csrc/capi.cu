@@ -44,7 +44,10 @@ namespace {
 
 constexpr size_t kDefaultWorkspace = size_t(256) << 20;
 constexpr uint32_t kMaxFp8Jobs = 4096;
-constexpr size_t kNormPartialFloats = 256u * 1024u;     // scratch of sdxlq_group_norm_nhwc (1 MiB)
+constexpr size_t kNormPartialFloats = 256u * 1024u;     // scratch of sdxlq_group_norm_nhwc: partial sums (1 MiB) ...
+constexpr size_t kNormMaxBatch = 1024;                  // ... then [batch, 64, 2] final statistics and [batch] counters
+constexpr size_t kNormScratchBytes = kNormPartialFloats * sizeof(float) + kNormMaxBatch * 64 * 2 * sizeof(float) +
+                                     kNormMaxBatch * sizeof(uint32_t);
 constexpr size_t kSmemLimit = 232448;      // 227 KiB opt-in shared memory per CTA on sm_100
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -852,7 +855,8 @@ int sdxlq_context_create(int device, void* stream, size_t workspace_bytes, sdxlq
         return SDXLQ_ERR_CUDA;
     }
     if (cudaEventCreateWithFlags(&ctx->staging_event, cudaEventDisableTiming) != cudaSuccess ||
-        cudaMalloc(&ctx->norm_partials, kNormPartialFloats * sizeof(float)) != cudaSuccess) {
+        cudaMalloc(&ctx->norm_partials, kNormScratchBytes) != cudaSuccess ||
+        cudaMemset(ctx->norm_partials, 0, kNormScratchBytes) != cudaSuccess) {
         if (ctx->staging_event != nullptr) cudaEventDestroy(ctx->staging_event);
         cudaFree(ctx->workspace);
         cudaFree(ctx->control);
@@ -1213,10 +1217,11 @@ int sdxlq_group_norm_nhwc(sdxlq_context* ctx, const sdxlq_group_norm_desc* desc)
     if (d.groups == 0 || d.channels == 0 || d.channels % d.groups != 0) {
         return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "CUDA group_norm channels must be divisible by groups");
     }
-    if (d.groups > 64 || d.channels % (2 * d.groups) != 0 || d.channels > group_norm_max_channels() ||
-        d.batch > 65535 || d.rows > 0x7FFFFFFFull) {
+    const auto aligned = [](const void* pointer) { return pointer == nullptr || reinterpret_cast<uintptr_t>(pointer) % 16 == 0; };
+    if (d.groups > 64 || d.channels % 8 != 0 || d.channels > group_norm_max_channels() || d.batch > kNormMaxBatch ||
+        d.rows > 0x7FFFFFFFull || !aligned(d.x) || !aligned(d.y) || !aligned(d.gamma) || !aligned(d.beta) || !aligned(d.channel_bias)) {
         return fail(ctx, SDXLQ_ERR_UNSUPPORTED_SHAPE,
-                    "group_norm: an even number of channels per group, at most 64 groups and 2560 channels");
+                    "group_norm: a multiple of 8 channels (at most 3072) with 16-byte aligned rows, at most 64 groups and 1024 images");
     }
     if (ctx->norm_partials == nullptr) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "group_norm needs a context made by sdxlq_context_create");
     // enough blocks to fill the GPU a few times over; the partial sums of a launch must fit the scratch
@@ -1232,6 +1237,8 @@ int sdxlq_group_norm_nhwc(sdxlq_context* ctx, const sdxlq_group_norm_desc* desc)
     launch.beta = static_cast<const __half*>(d.beta);
     launch.y = static_cast<__half*>(d.y);
     launch.partials = ctx->norm_partials;
+    launch.finals = ctx->norm_partials + kNormPartialFloats;
+    launch.counters = reinterpret_cast<uint32_t*>(ctx->norm_partials + kNormPartialFloats + kNormMaxBatch * 64 * 2);
     launch.batch = static_cast<uint32_t>(d.batch);
     launch.rows = static_cast<uint32_t>(d.rows);
     launch.channels = static_cast<uint32_t>(d.channels);

@@ -100,6 +100,8 @@ struct GroupNormLaunch {
     const __half* beta;          // [channels]
     __half* y;                   // [batch, rows, channels], may alias x
     float* partials;             // [batch, chunks, groups, 2] scratch
+    float* finals;               // [batch, 64, 2] scratch: mean and inverse standard deviation per group
+    uint32_t* counters;          // [batch] blocks of the statistics launch that are done; zero between launches
     uint32_t batch, rows, channels, groups;
     uint32_t rows_per_chunk;
     uint32_t silu;

@@ -330,7 +330,8 @@ class UNetHarness:
     def _group_norm(self, x, prefix, eps=1e-5, silu=False, channel_bias=None):
         """Ops::group_norm_nchw / group_norm_silu_nchw; `channel_bias` [B, C] is the add_spatial_bias in front."""
         gamma, beta = self.tensors[f"{prefix}.weight"], self.tensors[f"{prefix}.bias"]
-        if self.fuse_group_norm and x.dim() == 4 and x.is_contiguous(memory_format=torch.channels_last):
+        if self.fuse_group_norm and x.dim() == 4 and x.shape[1] % 8 == 0 and x.shape[1] <= 3072 and \
+                x.is_contiguous(memory_format=torch.channels_last):
             return self.ops.group_norm_nhwc(x, gamma, beta, self.config.norm_groups, eps, silu, channel_bias)
         if channel_bias is not None:
             x = x + channel_bias[:, :, None, None]
