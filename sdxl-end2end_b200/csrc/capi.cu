@@ -44,7 +44,8 @@ namespace {
 
 constexpr size_t kDefaultWorkspace = size_t(256) << 20;
 constexpr uint32_t kMaxFp8Jobs = 4096;
-constexpr size_t kNormPartialFloats = 256u * 1024u;     // scratch of sdxlq_group_norm_nhwc: partial sums (1 MiB) ...
+constexpr size_t kNormPartialFloats = 256u * 1024u;     // scratch of sdxlq_group_norm_nhwc: partial sums (1 MiB; also the
+                                                        // row statistics between the two LayerNorm -> FP8 launches) ...
 constexpr size_t kNormMaxBatch = 1024;                  // ... then [batch, 64, 2] final statistics and [batch] counters
 constexpr size_t kNormScratchBytes = kNormPartialFloats * sizeof(float) + kNormMaxBatch * 64 * 2 * sizeof(float) +
                                      kNormMaxBatch * sizeof(uint32_t);
@@ -376,13 +377,15 @@ int add_int8_job(sdxlq_context* ctx, Prepared& prep, const void* x, bool x_is_f3
 
 // Launches the INT8 activation quantisers of a prepared set: one launch per kernel flavour (and
 // per rotation group size). `tables` holds the device copies of the job tables, or nulls.
-int run_int8_quantisers(sdxlq_context* ctx, const Prepared& prep, QuantInt8Job* const tables[INT8_FLAVOURS]) {
+int run_int8_quantisers(sdxlq_context* ctx, const Prepared& prep, QuantInt8Job* const tables[INT8_FLAVOURS],
+                        uint16_t* const block_tables[INT8_FLAVOURS] = nullptr) {
     for (int flavour = 0; flavour < INT8_FLAVOURS; ++flavour) {
         const Int8JobSet& set = prep.int8[flavour];
         if (set.jobs.empty()) continue;
         cudaStream_t stream = ctx->stream;
         QuantInt8Launch launch{};
         launch.jobs = tables != nullptr ? tables[flavour] : nullptr;
+        launch.block_jobs = launch.jobs != nullptr && block_tables != nullptr ? block_tables[flavour] : nullptr;
         launch.num_jobs = static_cast<uint32_t>(set.jobs.size());
         launch.single = set.jobs[0];
         if (launch.jobs == nullptr && set.jobs.size() != 1) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "internal: job table missing");
@@ -661,8 +664,10 @@ GemmGeometry gemm_geometry(uint32_t max_cta_b_rows) {
 
 // The launch header of the FP8 activation quantiser: one amax word and one reader counter per job,
 // both zero when a call starts (the cast kernel puts them back, see fp8_cast_kernel).
-QuantFp8Launch bind_fp8(sdxlq_context* ctx, const std::vector<QuantFp8Job>& jobs, const QuantFp8Job* device_jobs) {
+QuantFp8Launch bind_fp8(sdxlq_context* ctx, const std::vector<QuantFp8Job>& jobs, const QuantFp8Job* device_jobs,
+                        const uint16_t* block_jobs = nullptr) {
     QuantFp8Launch launch{};
+    launch.block_jobs = device_jobs != nullptr ? block_jobs : nullptr;
     launch.amax_bits = ctx->control + 64;
     launch.done_counts = ctx->control + 64 + kMaxFp8Jobs;
     launch.jobs = device_jobs;
@@ -743,6 +748,9 @@ struct sdxlq_group_plan {
     TileRef* device_tiles[2] = {nullptr, nullptr};
     QuantInt8Job* device_int8_jobs[INT8_FLAVOURS] = {nullptr, nullptr, nullptr};
     QuantFp8Job* device_fp8_jobs = nullptr;
+    // the job of every block of the grouped quantiser launches (a block would otherwise search the job table)
+    uint16_t* device_int8_block_jobs[INT8_FLAVOURS] = {nullptr, nullptr, nullptr};
+    uint16_t* device_fp8_block_jobs = nullptr;
     int device = 0;
     const sdxlq_context* owner = nullptr;    // the tables hold addresses inside this context's workspace
 };
@@ -752,8 +760,19 @@ namespace {
 // Device tables of a prepared set, laid out back to back in one slab (128-byte aligned sections;
 // tensor maps need 64).
 struct TableLayout {
-    size_t problems[2], tiles[2], int8_jobs[INT8_FLAVOURS], fp8_jobs, total;
+    size_t problems[2], tiles[2], int8_jobs[INT8_FLAVOURS], fp8_jobs, int8_block_jobs[INT8_FLAVOURS], fp8_block_jobs, total;
 };
+
+// Block -> job tables exist for launches of 2 to 65536 jobs (16-bit entries).
+template <typename Job>
+bool wants_block_table(const std::vector<Job>& jobs) { return jobs.size() > 1 && jobs.size() <= 65536; }
+
+template <typename Job>
+void fill_block_table(const std::vector<Job>& jobs, uint16_t* table) {
+    for (size_t j = 0; j < jobs.size(); ++j) {
+        for (uint32_t b = 0; b < jobs[j].num_blocks; ++b) table[jobs[j].first_block + b] = static_cast<uint16_t>(j);
+    }
+}
 
 TableLayout layout_tables(const Prepared& prep) {
     TableLayout layout{};
@@ -763,6 +782,10 @@ TableLayout layout_tables(const Prepared& prep) {
     for (int f = 0; f < 2; ++f) layout.tiles[f] = place(prep.tiles[f].size() * sizeof(TileRef));
     for (int f = 0; f < INT8_FLAVOURS; ++f) layout.int8_jobs[f] = place(prep.int8[f].jobs.size() * sizeof(QuantInt8Job));
     layout.fp8_jobs = place(prep.fp8_jobs.size() * sizeof(QuantFp8Job));
+    for (int f = 0; f < INT8_FLAVOURS; ++f) {
+        layout.int8_block_jobs[f] = place(wants_block_table(prep.int8[f].jobs) ? prep.int8[f].blocks * sizeof(uint16_t) : 0);
+    }
+    layout.fp8_block_jobs = place(wants_block_table(prep.fp8_jobs) ? prep.fp8_blocks * sizeof(uint16_t) : 0);
     layout.total = std::max<size_t>(offset, 128);
     return layout;
 }
@@ -774,6 +797,10 @@ void fill_tables(const Prepared& prep, const TableLayout& layout, uint8_t* image
     for (int f = 0; f < 2; ++f) { copy(layout.problems[f], prep.problems[f]); copy(layout.tiles[f], prep.tiles[f]); }
     for (int f = 0; f < INT8_FLAVOURS; ++f) copy(layout.int8_jobs[f], prep.int8[f].jobs);
     copy(layout.fp8_jobs, prep.fp8_jobs);
+    for (int f = 0; f < INT8_FLAVOURS; ++f) {
+        if (wants_block_table(prep.int8[f].jobs)) fill_block_table(prep.int8[f].jobs, reinterpret_cast<uint16_t*>(image + layout.int8_block_jobs[f]));
+    }
+    if (wants_block_table(prep.fp8_jobs)) fill_block_table(prep.fp8_jobs, reinterpret_cast<uint16_t*>(image + layout.fp8_block_jobs));
 }
 
 void bind_tables(sdxlq_group_plan* plan, const TableLayout& layout, uint8_t* slab) {
@@ -787,14 +814,21 @@ void bind_tables(sdxlq_group_plan* plan, const TableLayout& layout, uint8_t* sla
         plan->device_int8_jobs[f] = prep.int8[f].jobs.empty() ? nullptr : reinterpret_cast<QuantInt8Job*>(slab + layout.int8_jobs[f]);
     }
     plan->device_fp8_jobs = prep.fp8_jobs.empty() ? nullptr : reinterpret_cast<QuantFp8Job*>(slab + layout.fp8_jobs);
+    for (int f = 0; f < INT8_FLAVOURS; ++f) {
+        plan->device_int8_block_jobs[f] =
+            wants_block_table(prep.int8[f].jobs) ? reinterpret_cast<uint16_t*>(slab + layout.int8_block_jobs[f]) : nullptr;
+    }
+    plan->device_fp8_block_jobs = wants_block_table(prep.fp8_jobs) ? reinterpret_cast<uint16_t*>(slab + layout.fp8_block_jobs) : nullptr;
 }
 
 // Quantisers, GEMM flavours and small-shape kernels of a prepared set, in stream order.
 int run_prepared(sdxlq_context* ctx, const Prepared& prep, const sdxlq_group_plan* tables) {
-    int status = run_int8_quantisers(ctx, prep, tables != nullptr ? tables->device_int8_jobs : nullptr);
+    int status = run_int8_quantisers(ctx, prep, tables != nullptr ? tables->device_int8_jobs : nullptr,
+                                     tables != nullptr ? tables->device_int8_block_jobs : nullptr);
     if (status != SDXLQ_OK) return status;
     if (!prep.fp8_jobs.empty()) {
-        const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, tables != nullptr ? tables->device_fp8_jobs : nullptr);
+        const QuantFp8Launch launch = bind_fp8(ctx, prep.fp8_jobs, tables != nullptr ? tables->device_fp8_jobs : nullptr,
+                                               tables != nullptr ? tables->device_fp8_block_jobs : nullptr);
         bool every_job_has_its_maximum = true;
         for (const QuantFp8Job& job : prep.fp8_jobs) every_job_has_its_maximum = every_job_has_its_maximum && job.amax_in != nullptr;
         LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_FP8, every_job_has_its_maximum ? 1 : 2);
@@ -1199,6 +1233,10 @@ int sdxlq_layer_norm(sdxlq_context* ctx, const sdxlq_layer_norm_desc* desc) {
     launch.amax_bits = ctx->control + 64;
     launch.done_count = ctx->control + 64 + kMaxFp8Jobs;
     launch.fmt = d.out_dtype == SDXLQ_FP8_E5M2 ? 1u : 0u;
+    // the normalisation scratch doubles as the rows' (mean, inverse deviation) between the two FP8 launches
+    if (fp8 && ctx->norm_partials != nullptr && d.rows * sizeof(float2) <= kNormPartialFloats * sizeof(float)) {
+        launch.row_stats = reinterpret_cast<float2*>(ctx->norm_partials);
+    }
     LaunchTimer timer(ctx, SDXLQ_KERNEL_LAYER_NORM, fp8 ? 2 : 1);
     const cudaError_t error = fp8 ? launch_layer_norm_fp8(launch, ctx->stream, ctx->early_launch && !ctx->profiling)
                                   : launch_layer_norm_f16(launch, ctx->stream);

@@ -22,6 +22,7 @@
 
 #include "quantize.cuh"
 #include "fp8_math.cuh"
+#include "int8_math.cuh"
 
 namespace sdxlq {
 
@@ -63,6 +64,7 @@ __device__ __forceinline__ float bf3(float a, float b, float c, float d) { retur
 
 __device__ __forceinline__ const QuantInt8Job& find_job(const QuantInt8Launch& launch, uint32_t block) {
     if (launch.jobs == nullptr) return launch.single;
+    if (launch.block_jobs != nullptr) return launch.jobs[launch.block_jobs[block]];
     uint32_t lo = 0, hi = launch.num_jobs;          // last job with first_block <= block
     while (hi - lo > 1) {
         const uint32_t mid = (lo + hi) >> 1;
@@ -304,6 +306,7 @@ namespace {
 
 __device__ __forceinline__ uint32_t find_job_index(const QuantFp8Launch& launch, uint32_t block) {
     if (launch.jobs == nullptr) return 0;
+    if (launch.block_jobs != nullptr) return launch.block_jobs[block];
     uint32_t lo = 0, hi = launch.num_jobs;
     while (hi - lo > 1) {
         const uint32_t mid = (lo + hi) >> 1;
@@ -325,17 +328,25 @@ fp8_amax_kernel(const __grid_constant__ QuantFp8Launch launch) {
     const size_t count = job.count;
     float local = 0.0f;
     if (job.vector_ok) {
+        // Four 16-byte loads in flight per thread; the maximum of FP16 values is one of them, so it is
+        // taken in half precision (NaN never wins, as with fmaxf).
         const size_t vectors = count / 8;
-        for (size_t index = static_cast<size_t>(local_block) * blockDim.x + threadIdx.x; index < vectors;
-             index += static_cast<size_t>(job.num_blocks) * blockDim.x) {
-            const uint4 raw = reinterpret_cast<const uint4*>(source)[index];
-            const __half2* pairs = reinterpret_cast<const __half2*>(&raw);
+        const size_t step = static_cast<size_t>(job.num_blocks) * blockDim.x;
+        const uint4* const vector_source = reinterpret_cast<const uint4*>(source);
+        __half2 maximum2 = __float2half2_rn(0.0f);
+        for (size_t index = static_cast<size_t>(local_block) * blockDim.x + threadIdx.x; index < vectors; index += 4 * step) {
+            uint4 raw[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __half22float2(pairs[i]);
-                local = fmaxf(local, fmaxf(fabsf(f.x), fabsf(f.y)));
+            for (int u = 0; u < 4; ++u) {
+                raw[u] = index + u * step < vectors ? __ldg(vector_source + index + u * step) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                maximum2 = __hmax2(maximum2, __hmax2(__habs2(as_half2(raw[u].x)), __habs2(as_half2(raw[u].y))));
+                maximum2 = __hmax2(maximum2, __hmax2(__habs2(as_half2(raw[u].z)), __habs2(as_half2(raw[u].w))));
             }
         }
+        local = fmaxf(__low2float(maximum2), __high2float(maximum2));
         if (local_block == 0) {
             for (size_t index = vectors * 8 + threadIdx.x; index < count; index += blockDim.x) {
                 local = fmaxf(local, fabsf(__half2float(source[index])));
@@ -390,20 +401,32 @@ fp8_cast_kernel(const __grid_constant__ QuantFp8Launch launch) {
     const size_t count = job.count;
     const uint32_t fmt = job.fmt;
     if (job.vector_ok) {
+        // Four 16-byte loads in flight per thread, walking the tensor from its end to its start: what
+        // the maximum kernel read last is what may still sit in L2.
         const size_t vectors = count / 8;
-        for (size_t index = static_cast<size_t>(local_block) * blockDim.x + threadIdx.x; index < vectors;
-             index += static_cast<size_t>(job.num_blocks) * blockDim.x) {
-            const uint4 raw = reinterpret_cast<const uint4*>(source)[index];
-            const __half2* pairs = reinterpret_cast<const __half2*>(&raw);
-            uint32_t packed[2];
+        const size_t step = static_cast<size_t>(job.num_blocks) * blockDim.x;
+        const uint4* const vector_source = reinterpret_cast<const uint4*>(source);
+        const float2 inverse_scale2 = make_float2(inverse_scale, inverse_scale);
+        for (size_t index = static_cast<size_t>(local_block) * blockDim.x + threadIdx.x; index < vectors; index += 4 * step) {
+            uint4 raw[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __half22float2(pairs[i]);
-                const uint32_t two = encode_fp8x2(__fmul_rn(f.x, inverse_scale), __fmul_rn(f.y, inverse_scale), fmt);
-                if ((i & 1) == 0) packed[i >> 1] = two & 0xFFFFu;
-                else packed[i >> 1] |= (two & 0xFFFFu) << 16;
+            for (int u = 0; u < 4; ++u) {
+                raw[u] = index + u * step < vectors ? __ldg(vector_source + (vectors - 1 - (index + u * step))) : make_uint4(0u, 0u, 0u, 0u);
             }
-            reinterpret_cast<uint2*>(destination)[index] = make_uint2(packed[0], packed[1]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (index + u * step >= vectors) break;
+                const uint32_t words[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+                uint32_t packed[2];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 scaled = __fmul2_rn(__half22float2(as_half2(words[i])), inverse_scale2);
+                    const uint32_t two = encode_fp8x2(scaled.x, scaled.y, fmt);
+                    if ((i & 1) == 0) packed[i >> 1] = two & 0xFFFFu;
+                    else packed[i >> 1] |= (two & 0xFFFFu) << 16;
+                }
+                reinterpret_cast<uint2*>(destination)[vectors - 1 - (index + u * step)] = make_uint2(packed[0], packed[1]);
+            }
         }
         if (local_block == 0) {
             for (size_t index = vectors * 8 + threadIdx.x; index < count; index += blockDim.x) {

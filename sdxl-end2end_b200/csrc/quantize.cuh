@@ -30,6 +30,7 @@ struct QuantInt8Job {
 
 struct QuantInt8Launch {
     const QuantInt8Job* jobs;    // device table (grouped) or null (`single` is used)
+    const uint16_t* block_jobs;  // grouped: the job of every block of the launch, or null (the block searches `jobs`)
     uint32_t num_jobs;
     uint32_t pad;
     QuantInt8Job single;
@@ -51,6 +52,7 @@ struct QuantFp8Job {
 
 struct QuantFp8Launch {
     const QuantFp8Job* jobs;     // device table (grouped) or null
+    const uint16_t* block_jobs;  // grouped: the job of every block of the launch, or null (the block searches `jobs`)
     uint32_t num_jobs;
     uint32_t pad;
     uint32_t* amax_bits;         // one scratch word per job, all zero on entry of the amax kernel
@@ -72,7 +74,8 @@ cudaError_t launch_fill_f32(float* values, uint32_t count, float value, cudaStre
 // aligned rows), one warp per row with the row in registers. Three outputs:
 //   FP16            y[rows, width]
 //   FP8             q[rows, width] in `fmt` with one tensor-wide dynamic scale: a statistics launch that only
-//                   reduces max |y| into *amax_bits, then a launch that normalises again and casts
+//                   reduces max |y| into *amax_bits (and leaves the rows' statistics in row_stats), then a
+//                   launch that normalises again and casts
 //   INT8            q[rows, width] with per-row scales scale_out[rows], no rotation
 struct LayerNormLaunch {
     const __half* x;
@@ -83,6 +86,8 @@ struct LayerNormLaunch {
     float* scale_out;
     uint32_t* amax_bits;         // zero on entry; put back to zero by the cast launch
     uint32_t* done_count;        // zero on entry; put back to zero by the cast launch
+    float2* row_stats;           // optional [rows] scratch: (mean, inverse deviation) from the statistics launch
+                                 // to the cast launch; null: the cast launch reduces every row again
     uint32_t rows, width;
     uint32_t fmt;                // 0 = E4M3, 1 = E5M2
     float epsilon;

@@ -20,6 +20,7 @@ namespace {
 
 __device__ __forceinline__ const QuantInt8Job& find_job(const QuantInt8Launch& launch, uint32_t block) {
     if (launch.jobs == nullptr) return launch.single;
+    if (launch.block_jobs != nullptr) return launch.jobs[launch.block_jobs[block]];
     uint32_t lo = 0, hi = launch.num_jobs;          // last job with first_block <= block
     while (hi - lo > 1) {
         const uint32_t mid = (lo + hi) >> 1;

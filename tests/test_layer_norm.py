@@ -58,7 +58,7 @@ def test_oracle_layer_norm_constant_rows_give_beta():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("rows,width", [(1, 8), (37, 640), (513, 1280), (9, 2048), (4096, 640), (77, 768), (2, 320)])
+@pytest.mark.parametrize("rows,width", [(1, 8), (37, 640), (513, 1280), (9, 2048), (4096, 640), (77, 768), (2, 320), (20011, 640), (7001, 2048)])
 def test_layer_norm_f16_matches_oracle_and_reference_device_code(gpu, rows, width):
     pkg, ctx, ops = gpu
     x, gamma, beta = make_case(11, rows, width)
@@ -81,8 +81,10 @@ def test_layer_norm_f16_matches_oracle_and_reference_device_code(gpu, rows, widt
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("fmt", [0, 1])
-@pytest.mark.parametrize("rows,width", [(37, 640), (513, 1280), (2048, 640), (3, 2048)])
+@pytest.mark.parametrize("rows,width", [(37, 640), (513, 1280), (2048, 640), (3, 2048), (20011, 640), (9001, 1280), (131073 + 5, 64)])
 def test_layer_norm_fp8_equals_layer_norm_then_quantiser(gpu, fmt, rows, width):
+    # 20011 / 9001 rows: several rows per warp (the warps' rings wrap around, the cast launch walks backwards);
+    # 131078 rows: more than the scratch for the rows' statistics holds, the cast launch reduces the rows again
     pkg, ctx, ops = gpu
     x, gamma, beta = make_case(12 + fmt, rows, width)
     consumer = pkg.Weight(torch.zeros((16, width), dtype=torch.uint8, device="cuda"), pkg.ScalarType(fmt), 16, width,
