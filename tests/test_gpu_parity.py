@@ -89,6 +89,24 @@ def test_int8_quantiser_edge_values(gpu):
         assert np.array_equal(xq.cpu().numpy()[finite_rows], want_q[finite_rows])
 
 
+def test_int8_quantiser_non_finite_values_in_rotated_rows(gpu):
+    """A NaN or an infinity poisons its own group of 256 (NaN -> 0, +-inf -> +-127 / -128 after the rotation, as the
+    reference's cast gives them); the row's scale comes from its finite values and the other groups are exact."""
+    pkg, ctx, ops = gpu
+    x = H.make_activations(91, 6, 1280)
+    x[1, 300] = np.inf
+    x[2, 700] = np.nan
+    x[3, 5] = -np.inf
+    x[3, 1279] = np.nan
+    x[4, 256] = np.float16(65504.0)
+    xq, scales = ops.quantize_int8(dev(x), 256)
+    ctx.check()
+    with np.errstate(invalid="ignore", over="ignore"):
+        want_q, want_s = O.int8_quantize_rows(x.astype(np.float32), 256)
+    assert np.array_equal(scales.cpu().numpy().view(np.uint32), want_s.view(np.uint32))
+    assert np.array_equal(xq.cpu().numpy(), want_q)
+
+
 def test_int8_quantiser_accepts_fp32_input(gpu):
     pkg, ctx, ops = gpu
     x = np.random.default_rng(5).standard_normal((33, 1280)).astype(np.float32)
