@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(kMaxNormThreads)
 group_norm_stats_kernel(const GroupNormLaunch p) {
     __shared__ float channel_sums[kMaxNormThreads * 8][2];      // [row slot][channel]
     __shared__ uint32_t ticket;
-    __shared__ double lane_sums[64][4][2];
+    __shared__ double lane_sums[64][8][2];
     const uint32_t batch = blockIdx.y;
     const uint32_t chunk = blockIdx.x;
     const uint32_t vectors = p.channels / 8;
@@ -114,21 +114,33 @@ group_norm_stats_kernel(const GroupNormLaunch p) {
         out[1] = total_squares;
     }
     // The block that finishes last for this batch element turns the partial sums into mean and inverse
-    // standard deviation per group. Its additions run in a fixed order: four threads per group take the
-    // chunks l, l + 4, ..., then the four results are added in order, in double precision.
+    // standard deviation per group. Its additions run in a fixed order: L threads per group (8 when the
+    // block has that many, else 4 or 2) take the chunks l, l + L, ... with four loads in flight each, then the
+    // L results are added in order, in double precision.
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) ticket = atomicAdd(p.counters + batch, 1u);
     __syncthreads();
     if (ticket != gridDim.x - 1u) return;
     __threadfence();
-    if (threadIdx.x < p.groups * 4u) {                    // a block has at least 193 threads
-        const uint32_t group = threadIdx.x >> 2, part = threadIdx.x & 3u;
+    // a block has at least 193 threads and a launch at most 64 groups: 2 lanes always fit
+    const uint32_t lanes = p.groups * 8u <= blockDim.x ? 8u : p.groups * 4u <= blockDim.x ? 4u : 2u;
+    if (threadIdx.x < p.groups * lanes) {
+        const uint32_t group = threadIdx.x / lanes, part = threadIdx.x % lanes;
         double total = 0.0, total_squares = 0.0;
-        const float* partial = p.partials + (static_cast<size_t>(batch) * gridDim.x * p.groups + group) * 2;
-        for (uint32_t c = part; c < gridDim.x; c += 4) {
-            total += static_cast<double>(__ldcg(partial + static_cast<size_t>(c) * p.groups * 2));
-            total_squares += static_cast<double>(__ldcg(partial + static_cast<size_t>(c) * p.groups * 2 + 1));
+        const float2* partial = reinterpret_cast<const float2*>(p.partials) + static_cast<size_t>(batch) * gridDim.x * p.groups + group;
+        for (uint32_t c = part; c < gridDim.x; c += 4u * lanes) {
+            float2 value[4];
+#pragma unroll
+            for (uint32_t u = 0; u < 4; ++u) {
+                const uint32_t chunk_index = c + u * lanes;
+                value[u] = chunk_index < gridDim.x ? __ldcg(partial + static_cast<size_t>(chunk_index) * p.groups) : make_float2(0.0f, 0.0f);
+            }
+#pragma unroll
+            for (uint32_t u = 0; u < 4; ++u) {
+                total += static_cast<double>(value[u].x);
+                total_squares += static_cast<double>(value[u].y);
+            }
         }
         lane_sums[group][part][0] = total;
         lane_sums[group][part][1] = total_squares;
@@ -136,7 +148,7 @@ group_norm_stats_kernel(const GroupNormLaunch p) {
     __syncthreads();
     if (threadIdx.x < p.groups) {
         double total = 0.0, total_squares = 0.0;
-        for (uint32_t part = 0; part < 4; ++part) {
+        for (uint32_t part = 0; part < lanes; ++part) {
             total += lane_sums[threadIdx.x][part][0];
             total_squares += lane_sums[threadIdx.x][part][1];
         }

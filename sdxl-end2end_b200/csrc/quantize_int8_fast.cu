@@ -274,6 +274,18 @@ rotated_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
 // The 2^-4 normalisation is folded into the maximum and into the inverse scale: scaling by a power
 // of two is exact (rotated FP16 data is a multiple of 2^-24, nowhere near the FP32 subnormals), so
 // fl(fl(x * 2^-4) * (1 / s)) = fl(x * (2^-4 / s)) bit for bit.
+//
+// Measured on B200 (X[16384, 1280] and X[8192, 2560], 23 to 24 us, 0.42 to 0.53 of the copy bandwidth): the
+// kernel is bound by instruction issue and dependency latency at 13 to 16 warps per SM (64 FP32 values
+// and their successors per thread: 114 to 126 registers), not by memory. Tried and no faster, same GPU:
+//  * a persistent grid that copies the next tile into a second staging buffer while it works on the
+//    current one (loads fully overlapped; 11 % slower: more registers live across the loop);
+//  * stage 3 on the packed pipe after regrouping neighbouring values into pairs, the integer cast as
+//    fl(x / s) + 1.5 * 2^23 instead of cvt.rni (the conversion pipe goes from 29 % to 2 % busy, but the
+//    regrouping moves cost more issue slots than the packed adds save: 13.4 against 11.8 million warp
+//    instructions, same time). Note for anyone who retries the cast: a packed add.rn.f32x2 placed behind a
+//    packed mul.rn.f32x2 was contracted into one packed fma (a single rounding; 5 of 2.6 million results off
+//    by one at ties), the scalar add.rn.f32 was not.
 // ------------------------------------------------------------------------------------------------
 namespace {
 
@@ -281,13 +293,6 @@ __device__ __forceinline__ void cp_async_16(uint32_t smem_address, const void* g
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_address), "l"(global_address) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
-// max(a, b, c) in one instruction; a NaN in any operand gives NaN.
-__device__ __forceinline__ float max3_nan(float a, float b, float c) {
-    float result;
-    asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(result) : "f"(a), "f"(b), "f"(c));
-    return result;
-}
 
 // in-place radix-4 butterfly on four packed values
 __device__ __forceinline__ void butterfly2(float2& a, float2& b, float2& c, float2& d) {
@@ -366,19 +371,12 @@ rotated256_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) butterfly2(p[h][g], p[h][g + 4], p[h][g + 8], p[h][g + 12]);
     }
-    // ---- stage 3: index bits 4 (y, the pair) and 5 (h) ----
-    // The four inputs of a butterfly are the halves of p[0][l] and p[1][l]; two neighbouring l are
-    // regrouped into pairs (l even, l odd) so that this stage runs packed as well, and its outputs
-    // t[2 h + y][m] = (l = 2 m, l = 2 m + 1) are already the runs the exchange and stage 4 work on.
-    float2 t[4][8];
+    // ---- stage 3: index bits 4 (the pair) and 5 (h), scalar ----
 #pragma unroll
-    for (int m = 0; m < 8; ++m) {
-        const float2 a = make_float2(p[0][2 * m].x, p[0][2 * m + 1].x), b = make_float2(p[0][2 * m].y, p[0][2 * m + 1].y);
-        const float2 c = make_float2(p[1][2 * m].x, p[1][2 * m + 1].x), d = make_float2(p[1][2 * m].y, p[1][2 * m + 1].y);
-        t[0][m] = bf0(a, b, c, d);
-        t[1][m] = bf1(a, b, c, d);
-        t[2][m] = bf2(a, b, c, d);
-        t[3][m] = bf3(a, b, c, d);
+    for (int l = 0; l < 16; ++l) {
+        const float a = p[0][l].x, b = p[0][l].y, c = p[1][l].x, d = p[1][l].y;
+        p[0][l] = make_float2(sbf0(a, b, c, d), sbf1(a, b, c, d));
+        p[1][l] = make_float2(sbf2(a, b, c, d), sbf3(a, b, c, d));
     }
     // ---- exchange inside the quad ----
     // Destination thread D (quad lane q' = bits 5-4) keeps 16 units of four floats: unit 4 w + r
@@ -395,8 +393,10 @@ rotated256_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
                     const uint32_t unit = (4u * w + quad_lane) ^ (destination & 7u);
-                    const float2 first = t[2 * h + y][2 * w], second = t[2 * h + y][2 * w + 1];
-                    *reinterpret_cast<float4*>(area + unit * 4u) = make_float4(first.x, first.y, second.x, second.y);
+                    float4 value;
+                    if (y == 0) value = make_float4(p[h][4 * w].x, p[h][4 * w + 1].x, p[h][4 * w + 2].x, p[h][4 * w + 3].x);
+                    else value = make_float4(p[h][4 * w].y, p[h][4 * w + 1].y, p[h][4 * w + 2].y, p[h][4 * w + 3].y);
+                    *reinterpret_cast<float4*>(area + unit * 4u) = value;
                 }
             }
         }
@@ -420,12 +420,10 @@ rotated256_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
         for (int z = 0; z < 2; ++z) {
             butterfly2(w2[w][0][z], w2[w][1][z], w2[w][2][z], w2[w][3][z]);
 #pragma unroll
-            for (int r = 0; r < 4; ++r) local_max = max3_nan(local_max, fabsf(w2[w][r][z].x), fabsf(w2[w][r][z].y));
+            for (int r = 0; r < 4; ++r) local_max = fmaxf(local_max, fmaxf(fabsf(w2[w][r][z].x), fabsf(w2[w][r][z].y)));
         }
     }
-    // the maximum above lets a NaN through, so this also sends a thread that holds a NaN down the slow paths
-    const bool all_finite = local_max <= 3.402823466e+38f;
-    if (!all_finite) {                                // an infinity: the maximum runs over finite values only
+    if (!(local_max <= 3.402823466e+38f)) {           // an infinity: the maximum runs over finite values only
         local_max = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
@@ -453,37 +451,15 @@ rotated256_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
     const float2 inverse2 = make_float2(inverse_scale, inverse_scale);
     if (thread_in_row == 0) job.scales[row] = scale;
     int8_t* destination = job.xq + static_cast<size_t>(row) * k + (thread_in_row >> 2) * 256u + quad_lane * 16u;
-    if (all_finite) {
-        // |x * (1 / scale)| <= 127 (1 + 2^-22) for every finite value of the row, so rn(x / scale) lies in
-        // [-127, 127] and needs no clamp: adding 1.5 * 2^23 to the rounded product rounds it to the nearest
-        // integer (ties to even, like cvt.rni) and leaves that in the low bits of the sum, whose low byte is
-        // the INT8 result (the conversion instruction runs at a quarter of the rate of an add). The add is the
-        // scalar instruction on purpose: a packed add.rn.f32x2 behind the packed multiply was contracted into one
-        // packed fma by the assembler (one rounding instead of two: 5 of 2.6 million results off by one at ties).
-        const float2 magic2 = make_float2(12582912.0f, 12582912.0f);
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            uint32_t words[4];
+    for (int r = 0; r < 4; ++r) {
+        uint32_t words[4];
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float2 pf = __fmul2_rn(w2[w][r][0], inverse2), ps = __fmul2_rn(w2[w][r][1], inverse2);
-                const float2 first = make_float2(__fadd_rn(pf.x, 12582912.0f), __fadd_rn(pf.y, 12582912.0f));
-                const float2 second = make_float2(__fadd_rn(ps.x, 12582912.0f), __fadd_rn(ps.y, 12582912.0f));
-                words[w] = pack_bytes(__float_as_uint(first.x), __float_as_uint(first.y), __float_as_uint(second.x), __float_as_uint(second.y));
-            }
-            *reinterpret_cast<uint4*>(destination + 64 * r) = make_uint4(words[0], words[1], words[2], words[3]);
+        for (int w = 0; w < 4; ++w) {
+            const float2 first = __fmul2_rn(w2[w][r][0], inverse2), second = __fmul2_rn(w2[w][r][1], inverse2);
+            words[w] = pack_bytes(quantize_s8(first.x), quantize_s8(first.y), quantize_s8(second.x), quantize_s8(second.y));
         }
-    } else {
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            uint32_t words[4];
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float2 first = __fmul2_rn(w2[w][r][0], inverse2), second = __fmul2_rn(w2[w][r][1], inverse2);
-                words[w] = pack_bytes(quantize_s8(first.x), quantize_s8(first.y), quantize_s8(second.x), quantize_s8(second.y));
-            }
-            *reinterpret_cast<uint4*>(destination + 64 * r) = make_uint4(words[0], words[1], words[2], words[3]);
-        }
+        *reinterpret_cast<uint4*>(destination + 64 * r) = make_uint4(words[0], words[1], words[2], words[3]);
     }
 }
 
