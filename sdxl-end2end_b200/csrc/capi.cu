@@ -31,11 +31,11 @@ cudaError_t launch_small_linear(const void* a, const void* b, const EpiloguePara
                                 cudaStream_t stream);
 cudaError_t launch_bounded_wait_probe(uint32_t* error_word, long long limit_cycles, cudaStream_t stream);
 cudaError_t launch_int8_plain_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t max_vectors,
-                                   cudaStream_t stream);
+                                   cudaStream_t stream, bool early_launch);
 cudaError_t launch_int8_rotated256_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
-                                        cudaStream_t stream);
+                                        cudaStream_t stream, bool early_launch);
 cudaError_t launch_int8_rotated_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
-                                     uint32_t stages, cudaStream_t stream);
+                                     uint32_t stages, cudaStream_t stream, bool early_launch);
 }  // namespace sdxlq
 
 using namespace sdxlq;
@@ -390,19 +390,20 @@ int run_int8_quantisers(sdxlq_context* ctx, const Prepared& prep, QuantInt8Job* 
         launch.single = set.jobs[0];
         if (launch.jobs == nullptr && set.jobs.size() != 1) return fail(ctx, SDXLQ_ERR_INVALID_ARGUMENT, "internal: job table missing");
         cudaError_t error = cudaSuccess;
+        const bool early = ctx->early_launch && !ctx->profiling;     // may be scheduled while the kernel before it drains
         LaunchTimer timer(ctx, SDXLQ_KERNEL_QUANT_INT8);
         if (flavour == INT8_GENERIC) {
-            error = launch_rotate_quantize_int8(launch, set.blocks, set.threads, stream);
+            error = launch_rotate_quantize_int8(launch, set.blocks, set.threads, stream, early);
         } else if (flavour == INT8_PLAIN) {
-            error = launch_int8_plain_rows(launch, set.blocks, set.max_vectors, stream);
+            error = launch_int8_plain_rows(launch, set.blocks, set.max_vectors, stream, early);
         } else {
             for (uint32_t stages = 1; stages <= 4 && error == cudaSuccess; ++stages) {
                 if (set.stage_mask & (1u << stages)) {
-                    error = launch_int8_rotated_rows(launch, set.blocks, set.threads, stages, stream);
+                    error = launch_int8_rotated_rows(launch, set.blocks, set.threads, stages, stream, early);
                 }
             }
             if (error == cudaSuccess && (set.stage_mask & (1u << 5))) {
-                error = launch_int8_rotated256_rows(launch, set.blocks, set.threads, stream);
+                error = launch_int8_rotated256_rows(launch, set.blocks, set.threads, stream, early);
             }
         }
         if (error != cudaSuccess) return fail_cuda(ctx, error, "INT8 activation quantise launch");
@@ -1191,7 +1192,7 @@ int sdxlq_layer_norm(sdxlq_context* ctx, const sdxlq_layer_norm_desc* desc) {
             launch.q = static_cast<uint8_t*>(d.xq);
             launch.scale_out = d.xq_scales;
             LaunchTimer timer(ctx, SDXLQ_KERNEL_LAYER_NORM);
-            const cudaError_t error = launch_layer_norm_int8(launch, ctx->stream);
+            const cudaError_t error = launch_layer_norm_int8(launch, ctx->stream, ctx->early_launch && !ctx->profiling);
             if (error != cudaSuccess) return fail_cuda(ctx, error, "layer_norm launch");
             return SDXLQ_OK;
         }
@@ -1204,7 +1205,7 @@ int sdxlq_layer_norm(sdxlq_context* ctx, const sdxlq_layer_norm_desc* desc) {
             // the sizes of this model) and the throughput rotation kernels read it from there
             launch.y = reinterpret_cast<__half*>(ctx->workspace);
             LaunchTimer timer(ctx, SDXLQ_KERNEL_LAYER_NORM);
-            const cudaError_t error = launch_layer_norm_f16(launch, ctx->stream);
+            const cudaError_t error = launch_layer_norm_f16(launch, ctx->stream, ctx->early_launch && !ctx->profiling);
             if (error != cudaSuccess) return fail_cuda(ctx, error, "layer_norm launch");
             source = ctx->workspace;
             gamma = beta = nullptr;
@@ -1239,7 +1240,7 @@ int sdxlq_layer_norm(sdxlq_context* ctx, const sdxlq_layer_norm_desc* desc) {
     }
     LaunchTimer timer(ctx, SDXLQ_KERNEL_LAYER_NORM, fp8 ? 2 : 1);
     const cudaError_t error = fp8 ? launch_layer_norm_fp8(launch, ctx->stream, ctx->early_launch && !ctx->profiling)
-                                  : launch_layer_norm_f16(launch, ctx->stream);
+                                  : launch_layer_norm_f16(launch, ctx->stream, ctx->early_launch && !ctx->profiling);
     if (error != cudaSuccess) return fail_cuda(ctx, error, "layer_norm launch");
     return SDXLQ_OK;
 }

@@ -629,6 +629,9 @@ sdxlq_umma_gemm_kernel(const __grid_constant__ GemmLaunchParams params) {
     // kernels before this one wrote (quantised activations, their scales): wait for them to
     // complete when this grid was launched early; no effect otherwise.
     ptx::grid_dependency_wait();
+    // ... and let the kernel behind this one (a quantiser, a LayerNorm) be scheduled: it fills the SMs as this
+    // grid's CTAs leave them and waits for this grid's completion before it touches global memory.
+    ptx::grid_launch_dependents();
 
     if (warp < kControlWarps) {
     ptx::setmaxnreg_dec<kControlRegisters>();

@@ -64,9 +64,11 @@ __device__ __forceinline__ uint32_t word_of(const uint4& raw, int i) {
 template <int kVectors, int Mode>
 __global__ void __launch_bounds__(256, kVectors > 5 ? 2 : 3)
 layer_norm_rows_kernel(const __grid_constant__ LayerNormLaunch p) {
-    // A kernel launched behind this one with the programmatic-dependency attribute may begin its
-    // set-up now; it waits for this kernel's completion before it reads the results.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // The cast launch of the FP8 form is scheduled while the statistics launch runs: it reads the rows (complete
+    // since before the statistics launch released it) and only waits for that launch's maximum further down.
+    // Every other form first waits for the kernels before it, then releases the kernel behind it.
+    if constexpr (Mode == LN_FP8_CAST || Mode == LN_FP8_CAST_SAVED) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    else wait_for_prior_kernels_then_release_next();
     constexpr uint32_t kRowVectors = kVectors * 32;
     __shared__ float4 gamma_beta[4][kRowVectors];         // gamma 0-3, gamma 4-7, beta 0-3, beta 4-7 of each vector
     __shared__ uint32_t maximum_bits;
@@ -91,7 +93,7 @@ layer_norm_rows_kernel(const __grid_constant__ LayerNormLaunch p) {
             into[j] = (inside && vector < vectors) ? __ldg(source + vector) : make_uint4(0, 0, 0, 0);
         }
     };
-    request(first, raw);                // the input does not depend on the launch before this one
+    request(first, raw);                // (cast launch: the rows were complete before the statistics launch released it)
 
     for (uint32_t vector = threadIdx.x; vector < vectors; vector += blockDim.x) {
         const uint4 g = reinterpret_cast<const uint4*>(p.gamma)[vector];
@@ -283,16 +285,16 @@ cudaError_t launch_mode(const LayerNormLaunch& launch, cudaStream_t stream, bool
 
 }  // namespace
 
-cudaError_t launch_layer_norm_f16(const LayerNormLaunch& launch, cudaStream_t stream) {
-    return launch_mode<LN_F16>(launch, stream, false);
+cudaError_t launch_layer_norm_f16(const LayerNormLaunch& launch, cudaStream_t stream, bool early_launch) {
+    return launch_mode<LN_F16>(launch, stream, early_launch);
 }
 
-cudaError_t launch_layer_norm_int8(const LayerNormLaunch& launch, cudaStream_t stream) {
-    return launch_mode<LN_INT8>(launch, stream, false);
+cudaError_t launch_layer_norm_int8(const LayerNormLaunch& launch, cudaStream_t stream, bool early_launch) {
+    return launch_mode<LN_INT8>(launch, stream, early_launch);
 }
 
 cudaError_t launch_layer_norm_fp8(const LayerNormLaunch& launch, cudaStream_t stream, bool early_launch) {
-    const cudaError_t status = launch_mode<LN_FP8_STATS>(launch, stream, false);
+    const cudaError_t status = launch_mode<LN_FP8_STATS>(launch, stream, early_launch);
     if (status != cudaSuccess) return status;
     // The cast launch needs the maximum of the launch above: with the programmatic-dependency
     // attribute it is scheduled while that one drains and waits (griddepcontrol.wait) before it reads

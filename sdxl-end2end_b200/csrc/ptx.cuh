@@ -262,6 +262,7 @@ __device__ __forceinline__ void setmaxnreg_inc() {
 // was launched with the programmatic attribute start being scheduled. Both do nothing in a grid
 // launched without such a dependency.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- CTA pairs (cta_group::2) ----------------------------------------------------------------
 // Two CTAs of a cluster work on one 256-row tile: each loads its 128 rows of A and half of the B

@@ -272,9 +272,7 @@ __device__ __forceinline__ void rotate_quantize_rows(const QuantInt8Job& job, ui
 __global__ void __launch_bounds__(256, 2)
 rotate_quantize_int8_kernel(const __grid_constant__ QuantInt8Launch launch) {
     __shared__ uint32_t row_max_bits[64];
-    // a GEMM launched with the programmatic-dependency attribute may begin its set-up now; it
-    // waits for this kernel to complete before it reads the results
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    wait_for_prior_kernels_then_release_next();
     const QuantInt8Job& job = find_job(launch, blockIdx.x);
     const uint32_t local_block = blockIdx.x - job.first_block;
     if (job.x_is_f32) rotate_quantize_rows<float, false>(job, local_block, row_max_bits, nullptr);
@@ -287,16 +285,17 @@ __global__ void __launch_bounds__(256, 1)
 normalize_rotate_quantize_int8_kernel(const __grid_constant__ QuantInt8Launch launch) {
     __shared__ uint32_t row_max_bits[64];
     __shared__ float row_partials[256];
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    wait_for_prior_kernels_then_release_next();
     const QuantInt8Job& job = find_job(launch, blockIdx.x);
     rotate_quantize_rows<__half, true>(job, blockIdx.x - job.first_block, row_max_bits, row_partials);
 }
 
 cudaError_t launch_rotate_quantize_int8(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
-                                        cudaStream_t stream) {
-    if (launch.single.gamma != nullptr) normalize_rotate_quantize_int8_kernel<<<blocks, threads, 0, stream>>>(launch);
-    else rotate_quantize_int8_kernel<<<blocks, threads, 0, stream>>>(launch);
-    return cudaGetLastError();
+                                        cudaStream_t stream, bool early_launch) {
+    if (launch.single.gamma != nullptr) {
+        return launch_behind(normalize_rotate_quantize_int8_kernel, blocks, threads, 0, stream, early_launch, launch);
+    }
+    return launch_behind(rotate_quantize_int8_kernel, blocks, threads, 0, stream, early_launch, launch);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -319,7 +318,7 @@ __device__ __forceinline__ uint32_t find_job_index(const QuantFp8Launch& launch,
 
 __global__ void __launch_bounds__(256)
 fp8_amax_kernel(const __grid_constant__ QuantFp8Launch launch) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // lets the cast kernel be scheduled early
+    wait_for_prior_kernels_then_release_next();      // the cast kernel may be scheduled while this one runs
     const uint32_t job_index = find_job_index(launch, blockIdx.x);
     const QuantFp8Job& job = launch.jobs == nullptr ? launch.single : launch.jobs[job_index];
     if (job.amax_in != nullptr) return;                                  // the producer of x left the maximum
@@ -374,8 +373,7 @@ fp8_amax_kernel(const __grid_constant__ QuantFp8Launch launch) {
 
 __global__ void __launch_bounds__(256)
 fp8_cast_kernel(const __grid_constant__ QuantFp8Launch launch) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // see rotate_quantize_int8_kernel
-    asm volatile("griddepcontrol.wait;" ::: "memory");                   // the maxima of fp8_amax_kernel are complete
+    wait_for_prior_kernels_then_release_next();      // the maxima of fp8_amax_kernel (or of the producer of x) are complete
     const uint32_t job_index = find_job_index(launch, blockIdx.x);
     const QuantFp8Job& job = launch.jobs == nullptr ? launch.single : launch.jobs[job_index];
     const uint32_t local_block = blockIdx.x - job.first_block;
@@ -445,23 +443,13 @@ cudaError_t launch_fp8_quantize(const QuantFp8Launch& launch, uint32_t blocks, c
                                 bool skip_maximum_pass) {
     // skip_maximum_pass: every job of the launch carries its maximum (amax_in), nothing to reduce
     if (!skip_maximum_pass) {
-        fp8_amax_kernel<<<blocks, 256, 0, stream>>>(launch);
-        const cudaError_t status = cudaGetLastError();
+        const cudaError_t status = launch_behind(fp8_amax_kernel, blocks, 256, 0, stream, early_launch, launch);
         if (status != cudaSuccess) return status;
     }
     // The cast kernel needs the maxima of the kernel above. Launched with the programmatic-dependency
-    // attribute it is scheduled while that kernel drains and waits (griddepcontrol.wait) before it
-    // reads them; without the attribute the wait does nothing and the stream orders the two.
-    cudaLaunchConfig_t config{};
-    config.gridDim = dim3(blocks, 1, 1);
-    config.blockDim = dim3(256, 1, 1);
-    config.stream = stream;
-    cudaLaunchAttribute attribute{};
-    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute.val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = early_launch ? &attribute : nullptr;
-    config.numAttrs = early_launch ? 1 : 0;
-    return cudaLaunchKernelEx(&config, fp8_cast_kernel, launch);
+    // attribute it is scheduled while that kernel runs and waits (griddepcontrol.wait) before it reads
+    // them; without the attribute the wait does nothing and the stream orders the two.
+    return launch_behind(fp8_cast_kernel, blocks, 256, 0, stream, early_launch, launch);
 }
 
 // ------------------------------------------------------------------------------------------

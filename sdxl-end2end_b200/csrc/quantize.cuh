@@ -61,8 +61,37 @@ struct QuantFp8Launch {
     QuantFp8Job single;
 };
 
+// Programmatic dependent launch, as every kernel of the projection path uses it: a kernel first waits for
+// the kernels before it (griddepcontrol.wait: they have completed and their memory is visible), touching
+// no global memory but constants before that, and then lets the kernel behind it be scheduled
+// (griddepcontrol.launch_dependents), so that the next kernel's launch and set-up overlap this kernel's
+// run. Waiting before triggering means that whatever a kernel finds complete, its dependents do too.
+// Both instructions do nothing in a launch without the attribute.
+__device__ __forceinline__ void wait_for_prior_kernels_then_release_next() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Launches `kernel`; `dependent` adds the programmatic-dependency attribute (the kernel may be scheduled
+// while the kernel before it on the stream drains, see above).
+template <typename... Params, typename... Args>
+inline cudaError_t launch_behind(void (*kernel)(Params...), uint32_t blocks, uint32_t threads, size_t dynamic_smem,
+                                 cudaStream_t stream, bool dependent, const Args&... args) {
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(blocks, 1, 1);
+    config.blockDim = dim3(threads, 1, 1);
+    config.dynamicSmemBytes = dynamic_smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = dependent ? &attribute : nullptr;
+    config.numAttrs = dependent ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, args...);
+}
+
 cudaError_t launch_rotate_quantize_int8(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
-                                        cudaStream_t stream);
+                                        cudaStream_t stream, bool early_launch);
 cudaError_t launch_fp8_quantize(const QuantFp8Launch& launch, uint32_t blocks, cudaStream_t stream, bool early_launch,
                                 bool skip_maximum_pass);
 cudaError_t launch_fp8_weight_pack(const void* source, int32_t dtype, uint32_t n, uint32_t k, uint32_t fmt,
@@ -92,8 +121,8 @@ struct LayerNormLaunch {
     uint32_t fmt;                // 0 = E4M3, 1 = E5M2
     float epsilon;
 };
-cudaError_t launch_layer_norm_f16(const LayerNormLaunch& launch, cudaStream_t stream);
-cudaError_t launch_layer_norm_int8(const LayerNormLaunch& launch, cudaStream_t stream);
+cudaError_t launch_layer_norm_f16(const LayerNormLaunch& launch, cudaStream_t stream, bool early_launch);
+cudaError_t launch_layer_norm_int8(const LayerNormLaunch& launch, cudaStream_t stream, bool early_launch);
 cudaError_t launch_layer_norm_fp8(const LayerNormLaunch& launch, cudaStream_t stream, bool early_launch);
 
 // GroupNorm (+ SiLU) over channels-last FP16 activations [batch, rows, channels]: scaffolding of the UNet

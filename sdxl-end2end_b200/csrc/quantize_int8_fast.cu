@@ -29,9 +29,6 @@ __device__ __forceinline__ const QuantInt8Job& find_job(const QuantInt8Launch& l
     return launch.jobs[lo];
 }
 
-// A GEMM launched with the programmatic-dependency attribute may start its set-up once every block
-// of this kernel has got here; it waits for this kernel's completion before it reads the results.
-__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 }  // namespace
 
@@ -41,7 +38,7 @@ __device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontr
 template <int MaxVectors>
 __global__ void __launch_bounds__(256)
 plain_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
-    launch_dependents();
+    wait_for_prior_kernels_then_release_next();
     const QuantInt8Job& job = find_job(launch, blockIdx.x);
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t row = (blockIdx.x - job.first_block) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -116,7 +113,7 @@ template <int Stages>
 __global__ void __launch_bounds__(256, 2)
 rotated_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
     __shared__ uint32_t row_max_bits[64];
-    launch_dependents();
+    wait_for_prior_kernels_then_release_next();
     const QuantInt8Job& job = find_job(launch, blockIdx.x);
     if (job.stages != Stages || job.pad != 0) return;   // one launch per group size; pad = 1: rotated256_rows_kernel
     const uint32_t local_block = blockIdx.x - job.first_block;
@@ -306,7 +303,7 @@ __global__ void __launch_bounds__(256, 2)
 rotated256_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
     extern __shared__ __align__(16) uint8_t dynamic_smem[];
     __shared__ uint32_t row_max_bits[64];
-    launch_dependents();
+    wait_for_prior_kernels_then_release_next();
     const QuantInt8Job& job = find_job(launch, blockIdx.x);
     if (job.stages != 4 || job.pad == 0) return;      // other group sizes / alignments: rotated_rows_kernel
     const uint32_t thread = threadIdx.x;
@@ -464,27 +461,25 @@ rotated256_rows_kernel(const __grid_constant__ QuantInt8Launch launch) {
 }
 
 cudaError_t launch_int8_plain_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t max_vectors,
-                                   cudaStream_t stream) {
-    if (max_vectors <= 3) plain_rows_kernel<3><<<blocks, 256, 0, stream>>>(launch);
-    else if (max_vectors <= 10) plain_rows_kernel<10><<<blocks, 256, 0, stream>>>(launch);
-    else plain_rows_kernel<20><<<blocks, 256, 0, stream>>>(launch);
-    return cudaGetLastError();
+                                   cudaStream_t stream, bool early_launch) {
+    if (max_vectors <= 3) return launch_behind(plain_rows_kernel<3>, blocks, 256, 0, stream, early_launch, launch);
+    if (max_vectors <= 10) return launch_behind(plain_rows_kernel<10>, blocks, 256, 0, stream, early_launch, launch);
+    return launch_behind(plain_rows_kernel<20>, blocks, 256, 0, stream, early_launch, launch);
 }
 
 cudaError_t launch_int8_rotated_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
-                                     uint32_t stages, cudaStream_t stream) {
+                                     uint32_t stages, cudaStream_t stream, bool early_launch) {
     switch (stages) {
-    case 1: rotated_rows_kernel<1><<<blocks, threads, 0, stream>>>(launch); break;
-    case 2: rotated_rows_kernel<2><<<blocks, threads, 0, stream>>>(launch); break;
-    case 3: rotated_rows_kernel<3><<<blocks, threads, 0, stream>>>(launch); break;
-    default: rotated_rows_kernel<4><<<blocks, threads, 0, stream>>>(launch); break;
+    case 1: return launch_behind(rotated_rows_kernel<1>, blocks, threads, 0, stream, early_launch, launch);
+    case 2: return launch_behind(rotated_rows_kernel<2>, blocks, threads, 0, stream, early_launch, launch);
+    case 3: return launch_behind(rotated_rows_kernel<3>, blocks, threads, 0, stream, early_launch, launch);
+    default: return launch_behind(rotated_rows_kernel<4>, blocks, threads, 0, stream, early_launch, launch);
     }
-    return cudaGetLastError();
 }
 
 // Groups of 256 with 16-byte aligned outputs (jobs marked with pad = 1).
 cudaError_t launch_int8_rotated256_rows(const QuantInt8Launch& launch, uint32_t blocks, uint32_t threads,
-                                        cudaStream_t stream) {
+                                        cudaStream_t stream, bool early_launch) {
     const size_t dynamic_smem = static_cast<size_t>(threads) * (128u + 256u);
     static bool opted_in[64] = {};
     int device = 0;
@@ -495,8 +490,7 @@ cudaError_t launch_int8_rotated256_rows(const QuantInt8Launch& launch, uint32_t 
         if (status != cudaSuccess) return status;
         if (device >= 0 && device < 64) opted_in[device] = true;
     }
-    rotated256_rows_kernel<<<blocks, threads, dynamic_smem, stream>>>(launch);
-    return cudaGetLastError();
+    return launch_behind(rotated256_rows_kernel, blocks, threads, dynamic_smem, stream, early_launch, launch);
 }
 
 }  // namespace sdxlq
