@@ -630,6 +630,10 @@ def run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks):
     largest = max(local_batch * 16384 * 640, local_batch * 4096 * 2560, local_batch * 1024 * 5120)
     context = pkg.Context(local_rank, workspace_bytes=int(largest * 1.05) + (64 << 20))
     ops = pkg.Ops(context)
+    # The loop's convolutions are PyTorch / cuDNN scaffolding: let cuDNN time its algorithms per shape once (during
+    # the warm-up steps, before the graph capture). Its heuristic choice at one or two images per GPU was a
+    # kernel that took 0.5 ms per launch: a fifth of the step.
+    torch.backends.cudnn.benchmark = not args.no_cudnn_autotune
     unet = harness.UNetHarness(ops, harness.BASE_1_0, precision=kind, seed=0)
     loop = harness.EulerDenoiser(unet, images, 1024, 1024, GENERATION_STEPS, guidance_scale=5.0, use_graph=not args.no_graph)
 
@@ -873,6 +877,7 @@ def main():
     parser.add_argument("--e2e-steps", type=int, default=None)
     parser.add_argument("--min-seconds", type=float, default=1.0, help="the K steps are repeated until the timed region lasts this long")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-cudnn-autotune", action="store_true", help="UNet loop: leave torch.backends.cudnn.benchmark off")
     parser.add_argument("--no-other-workloads", action="store_true")
     parser.add_argument("--no-graph", action="store_true", help="run the UNet loop eagerly instead of replaying a captured step")
     parser.add_argument("--no-library", action="store_true", help="skip the vendor-library comparison on the same shapes")
