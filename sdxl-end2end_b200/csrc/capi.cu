@@ -316,13 +316,16 @@ struct Prepared {
 
 using QuantKey = std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>;
 
+// Block size of a single rotated / general quantiser launch: the best share of working threads, with the
+// preference for 128-thread blocks that choose_quantiser_block gives grouped launches (measured 8 % faster at
+// equal fill: X[16384, 1280] 20.2 us with 128 threads, 21.8 with 160, 22.9 with 256).
 uint32_t best_int8_block(uint32_t threads_per_row) {
     uint32_t best = 256;
     double best_use = -1.0;
     for (uint32_t threads = 128; threads <= 256; threads += 32) {
         const uint32_t rows = threads / threads_per_row;
         if (rows == 0) continue;
-        const double use = static_cast<double>(rows * threads_per_row) / threads;
+        const double use = static_cast<double>(rows * threads_per_row) / threads * (threads == 128 ? 1.08 : 1.0);
         if (use > best_use + 1e-9) { best_use = use; best = threads; }
     }
     return best;
