@@ -350,7 +350,8 @@ def time_norm_quantize(torch, pkg, ops, peaks):
     16384 tokens x 1280), four rotating inputs per shape so that every launch reads from HBM (4 x 84 MB and
     4 x 42 MB against 132 MB of L2): FP16 LayerNorm, LayerNorm fused with the FP8 / INT8 quantiser, and the
     stand-alone quantisers for comparison. GB/s are algorithmic bytes (FP16 in/out 2 + 2; FP8 2 + 2 + 1: the
-    tensor-wide maximum needs a pass of its own; INT8 2 + 1) over the CUDA-event time of the launches."""
+    tensor-wide maximum needs a pass of its own; INT8 2 + 1) over the CUDA-event time of replayed graphs of the
+    launches (device time without the host's cost per call)."""
     result = {}
     for rows, width in ((65536, 640), (16384, 1280)):
         sets = 4
@@ -376,14 +377,24 @@ def time_norm_quantize(torch, pkg, ops, peaks):
             for i in range(sets):
                 call(i)
             torch.cuda.synchronize()
+            # One pass over the rotating inputs captured as a graph and replayed: device time only (a call through
+            # the Python mirror allocates its outputs and costs the host 15 to 20 us, more than some of these kernels).
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                ops.ctx.set_stream(torch.cuda.current_stream())
+                held = [call(i) for i in range(sets)]
+            ops.ctx.set_stream(torch.cuda.current_stream())
+            graph.replay()
+            torch.cuda.synchronize()
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             repeats = 10
             start.record()
-            for r in range(repeats * sets):
-                call(r % sets)
+            for r in range(repeats):
+                graph.replay()
             stop.record()
             torch.cuda.synchronize()
             ms = start.elapsed_time(stop) / (repeats * sets)
+            del graph, held
             gbs = rows * width * bytes_per_element / (ms * 1e-3) / 1e9
             shape[name] = {"ms": ms, "gbs": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"], "bytes_per_element": bytes_per_element}
         shape["int8_group"] = group
