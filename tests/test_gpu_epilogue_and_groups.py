@@ -201,6 +201,75 @@ def test_calls_can_be_captured_and_replayed(gpu):
     ctx.check()
 
 
+@pytest.mark.parametrize("kind", ["e4m3", "int8"])
+def test_dependent_launches_do_not_change_a_block(gpu, pkg, monkeypatch, kind):
+    """Every kernel of the path is launched as a programmatic dependent of the one before it (it may be scheduled
+    while that one still runs and waits before it touches memory). A chain shaped like a transformer block
+    (LayerNorm -> q/k/v -> out + residual -> LayerNorm -> GEGLU -> ff.net.2 + residual, the quantisers in
+    between reusing the same scratch) must give the same bits with the attribute, without it, and in a replayed
+    graph, repeat after repeat."""
+    _, ctx, ops = gpu
+    m, c = 4096, 640
+    if kind == "e4m3":
+        make = lambda n, k, seed: fp8_weight(pkg, n, k, seed)
+        group = 0
+    else:
+        make = lambda n, k, seed: int8_weight(pkg, n, k, 64, seed)[0]
+        group = 64
+    w_qkv = [make(c, c, 70 + i) for i in range(3)]
+    w_out, w_ff0, w_ff2 = make(c, c, 73), make(2 * 4 * c, c, 74), make(c, 4 * c, 75)
+    bias_out, bias_ff0, bias_ff2 = dev(H.make_bias(76, c)), dev(H.make_bias(77, 8 * c)), dev(H.make_bias(78, c))
+    gamma = dev((1.0 + 0.1 * np.random.default_rng(79).standard_normal(c)).astype(np.float16))
+    beta = dev((0.1 * np.random.default_rng(80).standard_normal(c)).astype(np.float16))
+    x0 = dev(H.make_activations(81, m, c))
+
+    def block(operator, hidden):
+        xq, scales = operator.layer_norm_quantized(hidden, gamma, beta, w_qkv[0], 1e-5)
+        q, k, v = operator.linear_grouped([pkg.LinearCall(hidden, w, xq=xq, xq_scales=scales) for w in w_qkv])
+        mixed = (q.float() * 0.5 + k.float() * 0.25 + v.float() * 0.25).half()       # stands in for the attention
+        hidden = operator.linear(mixed, w_out, bias_out, residual=hidden)
+        xq, scales = operator.layer_norm_quantized(hidden, gamma, beta, w_ff0, 1e-5)
+        gated = operator.linear_activation(hidden, w_ff0, bias_ff0, pkg.ACT_GEGLU, xq=xq, xq_scales=scales)
+        return operator.linear(gated, w_ff2, bias_ff2, residual=hidden)
+
+    def run(operator, repeats):
+        hidden = x0
+        for _ in range(repeats):
+            hidden = block(operator, hidden)
+        return hidden
+
+    monkeypatch.setenv("SDXLQ_EARLY_LAUNCH", "0")
+    plain_context = pkg.Context(0, workspace_bytes=64 << 20)
+    monkeypatch.delenv("SDXLQ_EARLY_LAUNCH")
+    plain = pkg.Ops(plain_context)
+    want = run(plain, 4).clone()
+    plain_context.check()
+    got = run(ops, 4)
+    ctx.check()
+    assert torch.isfinite(want.float()).all()
+    assert torch.equal(got, want)
+    # replayed graph on the session's context
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ctx.set_stream(side)
+        run(ops, 1)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(graph):
+        ctx.set_stream(torch.cuda.current_stream())
+        held = run(ops, 4)
+    ctx.set_stream(torch.cuda.current_stream())
+    for _ in range(5):
+        held.zero_()
+        graph.replay()
+    torch.cuda.synchronize()
+    ctx.check()
+    assert torch.equal(held, want)
+    plain_context.close()
+
+
 # ------------------------------------------------------------------------------------------------
 # several contexts on one GPU
 # ------------------------------------------------------------------------------------------------
