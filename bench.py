@@ -826,6 +826,19 @@ def run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks):
             quant_inputs.setdefault(p.input_key, (p.m, p.k))
     # 2 + 1 bytes per element where the maximum pass is skipped, 2 + 2 + 1 otherwise
     quant_bytes = quantiser_bytes(quant_inputs.values(), kind) + float(sum(m * k * 3 for (m, k) in handed_over.values()))
+    # the same bytes by kernel family: inputs that come out of a LayerNorm (to_q / to_k / to_v of attn1, attn2.to_q,
+    # ff.net.0.proj) are quantised by the fused LayerNorm kernels, the rest by the stand-alone quantisers
+    norm_fed = {p.input_key for p in projections
+                if p.name.endswith((".attn1.to_q", ".attn1.to_k", ".attn1.to_v", ".attn2.to_q", ".ff.net.0.proj"))}
+    norm_bytes = quantiser_bytes([shape for key, shape in quant_inputs.items() if key in norm_fed], kind)
+    alone_bytes = quant_bytes - norm_bytes
+    alone_ms = quant_ms - (norm_ms if kind != "f16" else 0.0)
+
+    def family(bytes_moved, ms):
+        if ms <= 0 or bytes_moved <= 0:
+            return None
+        return {"bytes_per_step": bytes_moved, "ms_per_step": ms, "achieved": bytes_moved / (ms * 1e-3) / 1e9,
+                "frac": bytes_moved / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
     rows_table = [(p.name, p.m, p.n, p.k, p.bias, p.activation, p.input_key) for p in projections
                   if not (".attn2.to_k" in p.name or ".attn2.to_v" in p.name)]
     roofline = {
@@ -852,7 +865,11 @@ def run_unet_loop(args, torch, dist, pkg, rank, local_rank, world, peaks):
         "quantize_kernel": {"bound": "hbm", "bytes_per_step": quant_bytes, "ms_per_step": quant_ms,
                             "achieved": quant_bytes / (quant_ms * 1e-3) / 1e9 if quant_ms > 0 else None,
                             "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                            "frac": (quant_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]) if quant_ms > 0 else None},
+                            "frac": (quant_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]) if quant_ms > 0 else None,
+                            "by_kernel_family": {"layer_norm_fused": family(norm_bytes, norm_ms if kind != "f16" else 0.0),
+                                                 "stand_alone": family(alone_bytes, alone_ms)},
+                            "per_kernel": "other_workloads.norm_quantize times every LayerNorm / quantiser kernel alone at "
+                                          "this job's sizes (replayed graphs: device time)"},
     }
     projection_ms = gemm_ms + quant_ms
     line = {
