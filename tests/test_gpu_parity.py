@@ -89,6 +89,22 @@ def test_int8_quantiser_edge_values(gpu):
         assert np.array_equal(xq.cpu().numpy()[finite_rows], want_q[finite_rows])
 
 
+def test_int8_quantiser_ties_after_rotation(gpu):
+    """These activations hold five values whose rotated, scaled product rounds to an exact x.5 in FP32 although
+    the exact product does not: the cast must round the FP32 product (ties to even), not the exact one — a
+    multiply fused with the rounding step gives the neighbouring integer there."""
+    pkg, ctx, ops = gpu
+    x = H.make_activations(12544, 2048, 1280)
+    xq, scales = ops.quantize_int8(dev(x), 256)
+    ctx.check()
+    want_q, want_s = O.int8_quantize_rows(x.astype(np.float32), 256)
+    rotated = O.hadamard_rows(x.astype(np.float32), 256)
+    scaled = (rotated * np.float32(0.0625)) * (np.float32(1.0) / want_s)[:, None]
+    assert int(np.sum(np.abs(scaled - np.trunc(scaled)) == 0.5)) >= 5          # the ties are there
+    assert np.array_equal(scales.cpu().numpy().view(np.uint32), want_s.view(np.uint32))
+    assert np.array_equal(xq.cpu().numpy(), want_q)
+
+
 def test_int8_quantiser_non_finite_values_in_rotated_rows(gpu):
     """A NaN or an infinity poisons its own group of 256 (NaN -> 0, +-inf -> +-127 / -128 after the rotation, as the
     reference's cast gives them); the row's scale comes from its finite values and the other groups are exact."""
